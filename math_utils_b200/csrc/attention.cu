@@ -1,0 +1,267 @@
+// Attention over the paged key/value cache, on CUDA cores, for any element type.
+//
+// Cache of one layer: pages of `page_tokens` positions,
+//     kv[page][0 = keys | 1 = values][kv_head][position in page][head_dim]
+// and a block table `block_table[s][i]` = page that holds positions
+// [i * page_tokens, (i + 1) * page_tokens) of the s-th sequence of the step
+// (`tok_seq[t]` says which sequence token t belongs to, `tok_pos[t]` where).
+//
+// mu_kv_append   copies this step's keys and values into their pages.
+// mu_attention   one warp per (query token, head, key split): scores over the
+//                keys first..position (a window cuts `first`), max-subtracted
+//                softmax, weighted values; everything in float32 whatever the
+//                storage type.  It serves whole prompts (each query sees the
+//                keys the same step appended before it) and single-token
+//                steps; with n_splits > 1 each warp takes a slice of the keys
+//                and writes an unnormalised partial (max, sum, values) that
+//                mu_attention_merge combines.
+// The formulas are those of include/ai/Kernels.hpp:132-161; the split and merge
+// follow the idea of src/gpu/Kernels.metal:284-345.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace mu {
+
+template <typename TE>
+__global__ void kv_append_kernel(const TE* __restrict__ k, long long ldk, const TE* __restrict__ v,
+                                 long long ldv, const int* __restrict__ tok_pos,
+                                 const int* __restrict__ tok_seq,
+                                 const int* __restrict__ block_table, int max_pages, int page_tokens,
+                                 int n_kv_heads, int head_dim, TE* __restrict__ kv) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const long long page = block_table[(long long)tok_seq[t] * max_pages + pos / page_tokens];
+    const int off = pos % page_tokens;
+    const int width = n_kv_heads * head_dim;
+    const long long head_stride = (long long)page_tokens * head_dim;
+    TE* kdst = kv + (page * 2 + 0) * n_kv_heads * head_stride + (long long)off * head_dim;
+    TE* vdst = kv + (page * 2 + 1) * n_kv_heads * head_stride + (long long)off * head_dim;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const int h = i / head_dim, d = i % head_dim;
+        kdst[h * head_stride + d] = k[(long long)t * ldk + i];
+        vdst[h * head_stride + d] = v[(long long)t * ldv + i];
+    }
+}
+
+__device__ __forceinline__ float dot_row(const float* qs, const float* krow, int head_dim) {
+    float s = 0.0f;
+    for (int d = 0; d < head_dim; d += 4) {
+        const float4 kk = *reinterpret_cast<const float4*>(krow + d);
+        s = fmaf(qs[d], kk.x, s);
+        s = fmaf(qs[d + 1], kk.y, s);
+        s = fmaf(qs[d + 2], kk.z, s);
+        s = fmaf(qs[d + 3], kk.w, s);
+    }
+    return s;
+}
+__device__ __forceinline__ float dot_row(const float* qs, const __nv_bfloat16* krow, int head_dim) {
+    float s = 0.0f;
+    for (int d = 0; d < head_dim; d += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p[i]);
+            s = fmaf(qs[d + 2 * i], f.x, s);
+            s = fmaf(qs[d + 2 * i + 1], f.y, s);
+        }
+    }
+    return s;
+}
+
+constexpr int ATT_WARPS = 4;
+
+template <typename TE, int DPL>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_kernel(const TE* __restrict__ q, long long ldq, TE* __restrict__ out, long long ldo,
+                 const TE* __restrict__ kv, const int* __restrict__ block_table, int max_pages,
+                 int page_tokens, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                 int n_tokens, int n_heads, int n_kv_heads,
+                 int head_dim, float scale, int window, int n_splits, int split_keys,
+                 float* __restrict__ part_o, float* __restrict__ part_ml) {
+    __shared__ float q_smem[ATT_WARPS][DPL * 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * ATT_WARPS + warp;
+    if (item >= (long long)n_tokens * n_heads) return;          // whole warps leave together
+    const int split = blockIdx.y;
+    const int t = (int)(item / n_heads), h = (int)(item % n_heads);
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int pos = tok_pos[t];
+    const int* pages = block_table + (long long)tok_seq[t] * max_pages;
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    int lo = first, hi = pos + 1;
+    if (n_splits > 1) {
+        lo = max(first, split * split_keys);
+        hi = min(pos + 1, (split + 1) * split_keys);
+    }
+    float* qs = q_smem[warp];
+    for (int d = lane; d < head_dim; d += 32) qs[d] = to_float(q[(long long)t * ldq + h * head_dim + d]);
+    __syncwarp();
+
+    const long long head_stride = (long long)page_tokens * head_dim;
+    const long long page_stride = 2ll * n_kv_heads * head_stride;
+    const long long k_base = (long long)kvh * head_stride;
+    const long long v_base = ((long long)n_kv_heads + kvh) * head_stride;
+
+    float m = -INFINITY, l = 0.0f;
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+
+    for (int base = lo; base < hi; base += 32) {
+        const int j = base + lane;
+        const bool valid = j < hi;
+        long long row_off = 0;        // offset of this key's row inside its page's head block
+        float s = -INFINITY;
+        if (valid) {
+            const long long page = pages[j / page_tokens];
+            row_off = page * page_stride + (long long)(j % page_tokens) * head_dim;
+            s = dot_row(qs, kv + row_off + k_base, head_dim) * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);           // 0 on the first chunk (m = -inf)
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+        m = m_new;
+        const int n_here = min(32, hi - base);
+        for (int jj = 0; jj < n_here; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const long long off = __shfl_sync(0xffffffffu, row_off, jj);
+            const TE* vrow = kv + off + v_base;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < head_dim) acc[i] = fmaf(pj, to_float(vrow[d]), acc[i]);
+            }
+        }
+    }
+
+    if (n_splits == 1) {
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) out[(long long)t * ldo + h * head_dim + d] = from_float<TE>(acc[i] * inv);
+        }
+    } else {
+        const long long slot_idx = item * n_splits + split;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) part_o[slot_idx * head_dim + d] = acc[i];
+        }
+        if (lane == 0) {
+            part_ml[slot_idx * 2] = m;
+            part_ml[slot_idx * 2 + 1] = l;
+        }
+    }
+}
+
+template <typename TE>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       TE* __restrict__ out, long long ldo, int n_tokens, int n_heads,
+                                       int head_dim, int n_splits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)n_tokens * n_heads) return;
+    const int t = (int)(item / n_heads), h = (int)(item % n_heads);
+    const float* ml = part_ml + item * n_splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = ml[2 * s];
+        if (ms != -INFINITY) l += ml[2 * s + 1] * expf(ms - m);
+    }
+    const float inv = 1.0f / l;
+    for (int d = lane; d < head_dim; d += 32) {
+        float o = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = ml[2 * s];
+            if (ms != -INFINITY) o = fmaf(part_o[(item * n_splits + s) * head_dim + d], expf(ms - m), o);
+        }
+        out[(long long)t * ldo + h * head_dim + d] = from_float<TE>(o * inv);
+    }
+}
+
+}  // namespace mu
+
+static int check_paged(int page_tokens, int n_kv_heads, int head_dim, int max_pages) {
+    if (page_tokens <= 0 || n_kv_heads <= 0 || max_pages <= 0) return MU_ERR_BAD_ARGUMENT;
+    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;
+    return MU_OK;
+}
+
+MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long long ldv,
+                           const int* tok_pos, const int* tok_seq,
+                           const int* block_table, int max_pages, int page_tokens, int n_tokens,
+                           int n_kv_heads, int head_dim, void* kv, int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (int e = check_paged(page_tokens, n_kv_heads, head_dim, max_pages)) return e;
+    if (!k || !v || !kv || !tok_pos || !tok_seq || !block_table) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = n_kv_heads * head_dim >= 256 ? 256 : 128;
+    if (is_bf16)
+        mu::kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(
+            (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq,
+            block_table, max_pages, page_tokens, n_kv_heads, head_dim, (__nv_bfloat16*)kv);
+    else
+        mu::kv_append_kernel<float><<<n_tokens, threads, 0, s>>>(
+            (const float*)k, ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table,
+            max_pages, page_tokens, n_kv_heads, head_dim, (float*)kv);
+    MU_CHECK_LAUNCH();
+    return MU_OK;
+}
+
+// n_splits > 1 needs part_o [n_tokens * n_heads * n_splits * head_dim] and
+// part_ml [n_tokens * n_heads * n_splits * 2] floats of scratch, and split s takes
+// the keys [s * split_keys, (s + 1) * split_keys).
+MU_EXPORT int mu_attention(const void* q, long long ldq, void* out, long long ldo, const void* kv,
+                           const int* block_table, int max_pages, int page_tokens,
+                           const int* tok_pos, const int* tok_seq, int n_tokens,
+                           int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                           int n_splits, int split_keys, float* part_o, float* part_ml,
+                           int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (int e = check_paged(page_tokens, n_kv_heads, head_dim, max_pages)) return e;
+    if (n_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0) return MU_ERR_BAD_ARGUMENT;
+    if (!q || !out || !kv || !tok_pos || !tok_seq || !block_table) return MU_ERR_BAD_ARGUMENT;
+    if (n_splits < 1 || n_splits > 65535) return MU_ERR_BAD_ARGUMENT;
+    if (n_splits > 1 && (!part_o || !part_ml || split_keys <= 0)) return MU_ERR_BAD_ARGUMENT;
+    const long long items = (long long)n_tokens * n_heads;
+    dim3 grid((unsigned)((items + mu::ATT_WARPS - 1) / mu::ATT_WARPS), n_splits);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int dpl = (head_dim + 31) / 32;
+#define MU_ATT(TE, DPL)                                                                          \
+    mu::attention_kernel<TE, DPL><<<grid, mu::ATT_WARPS * 32, 0, s>>>(                            \
+        (const TE*)q, ldq, (TE*)out, ldo, (const TE*)kv, block_table, max_pages, page_tokens,    \
+        tok_pos, tok_seq, n_tokens, n_heads, n_kv_heads, head_dim, scale, window,      \
+        n_splits, split_keys, part_o, part_ml)
+#define MU_ATT_T(TE)                     \
+    do {                                 \
+        if (dpl <= 1) MU_ATT(TE, 1);     \
+        else if (dpl <= 2) MU_ATT(TE, 2);\
+        else if (dpl <= 4) MU_ATT(TE, 4);\
+        else MU_ATT(TE, 8);              \
+    } while (0)
+    if (is_bf16) MU_ATT_T(__nv_bfloat16);
+    else MU_ATT_T(float);
+#undef MU_ATT_T
+#undef MU_ATT
+    MU_CHECK_LAUNCH();
+    if (n_splits > 1) {
+        const int warps = 4;
+        const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+        if (is_bf16)
+            mu::attention_merge_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, s>>>(
+                part_o, part_ml, (__nv_bfloat16*)out, ldo, n_tokens, n_heads, head_dim, n_splits);
+        else
+            mu::attention_merge_kernel<float><<<blocks, warps * 32, 0, s>>>(
+                part_o, part_ml, (float*)out, ldo, n_tokens, n_heads, head_dim, n_splits);
+        MU_CHECK_LAUNCH();
+    }
+    return MU_OK;
+}

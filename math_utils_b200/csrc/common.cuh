@@ -1,0 +1,79 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Every launcher is an extern "C" function that takes raw device pointers,
+// sizes and a stream, checks what it can on the host, and returns 0 or one of
+// the MU_ERR_* codes below (the Python side turns a code into an exception).
+// No launcher allocates, synchronises or reads device memory on the host.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MU_OK 0
+#define MU_ERR_BAD_ARGUMENT 1      // a size or pointer the kernel cannot take
+#define MU_ERR_UNSUPPORTED_SIZE 2  // a size outside what this kernel was written for
+#define MU_ERR_LAUNCH 3            // the CUDA runtime refused the launch
+#define MU_ERR_ALIGNMENT 4         // a pointer or stride that breaks an alignment rule
+
+#define MU_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define MU_CHECK_LAUNCH()                                   \
+    do {                                                    \
+        cudaError_t e__ = cudaGetLastError();               \
+        if (e__ != cudaSuccess) return MU_ERR_LAUNCH;       \
+    } while (0)
+
+namespace mu {
+
+constexpr int ACT_NONE = 0;
+constexpr int ACT_GELU_NEW = 1;   // tanh form
+constexpr int ACT_GELU_ERF = 2;   // exact form
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float gelu_new(float x) {
+    const float k = 0.7978845608028654f;  // sqrt(2/pi)
+    return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+    return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+}
+__device__ __forceinline__ float apply_act(float x, int act) {
+    if (act == ACT_GELU_NEW) return gelu_new(x);
+    if (act == ACT_GELU_ERF) return gelu_erf(x);
+    return x;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; every thread gets the result.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    r = warp_sum(r);
+    return r;
+}
+
+}  // namespace mu

@@ -1,0 +1,96 @@
+// Embedding gather and LayerNorm.
+//
+// embed:     x[t, :] = table[id[t], :] + (pos_table ? pos_table[pos[t], :] : 0)
+//            -> float32 residual stream (include/ai/LocalModel.hpp:3686-3697).
+// layernorm: y = (x - mean) * rsqrt(var + eps) * gamma + beta, biased variance,
+//            two passes over the row, all in float32
+//            (include/ai/LocalModel.hpp:1355-1367); output in the compute dtype.
+#include "common.cuh"
+
+namespace mu {
+
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
+                             const TW* __restrict__ table, const TW* __restrict__ pos_table,
+                             float* __restrict__ x, int hidden) {
+    const int t = blockIdx.x;
+    const long long row = ids[t];
+    const TW* src = table + row * hidden;
+    const TW* psrc = pos_table ? pos_table + (long long)pos[t] * hidden : nullptr;
+    float* dst = x + (long long)t * hidden;
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        float v = to_float(src[d]);
+        if (psrc) v += to_float(psrc[d]);
+        dst[d] = v;
+    }
+}
+
+// One block per output row.  The row is staged in shared memory so that the
+// mean, the variance and the output each read it once from there.
+template <typename TO>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                 TO* __restrict__ y, int hidden, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long src_row = rows ? rows[r] : r;
+    const float* src = x + src_row * hidden;
+    float s = 0.0f;
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        const float v = src[d];
+        row[d] = v;
+        s += v;
+    }
+    const float mean = block_sum(s, scratch) / (float)hidden;
+    float q = 0.0f;
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        const float c = row[d] - mean;
+        q += c * c;
+    }
+    const float var = block_sum(q, scratch) / (float)hidden;
+    const float inv = 1.0f / sqrtf(var + eps);
+    TO* dst = y + (long long)r * hidden;
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        const float v = (row[d] - mean) * inv * gamma[d] + (beta ? beta[d] : 0.0f);
+        dst[d] = from_float<TO>(v);
+    }
+}
+
+}  // namespace mu
+
+// table_bf16: 1 if the tables hold bfloat16, 0 for float32.
+MU_EXPORT int mu_embed(const int* ids, const int* pos, const void* table, const void* pos_table,
+                       float* x, int n_tokens, int hidden, int table_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (hidden <= 0 || !ids || !table || !x || (pos_table && !pos)) return MU_ERR_BAD_ARGUMENT;
+    const int threads = hidden >= 256 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_bf16)
+        mu::embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(
+            ids, pos, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
+    else
+        mu::embed_kernel<float><<<n_tokens, threads, 0, s>>>(
+            ids, pos, (const float*)table, (const float*)pos_table, x, hidden);
+    MU_CHECK_LAUNCH();
+    return MU_OK;
+}
+
+// rows: optional int32 row indices into x (n_rows of them); out_bf16 picks the output dtype.
+MU_EXPORT int mu_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
+                           void* y, int n_rows, int hidden, float eps, int out_bf16, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (hidden <= 0 || !x || !gamma || !y) return MU_ERR_BAD_ARGUMENT;
+    if (hidden > 12288) return MU_ERR_UNSUPPORTED_SIZE;   // the row must fit 48 KB of shared memory
+    const int threads = hidden >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_bf16)
+        mu::layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, s>>>(
+            x, rows, gamma, beta, (__nv_bfloat16*)y, hidden, eps);
+    else
+        mu::layernorm_kernel<float><<<n_rows, threads, smem, s>>>(
+            x, rows, gamma, beta, (float*)y, hidden, eps);
+    MU_CHECK_LAUNCH();
+    return MU_OK;
+}

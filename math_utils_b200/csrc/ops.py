@@ -1,0 +1,272 @@
+"""Python face of the CUDA kernels: torch tensors in, launches on the current stream.
+
+The kernels live in one shared object built from the ``.cu`` files beside this
+module (``build.py``) and are called through their ``extern "C"`` launchers.
+There is no other implementation behind these functions: if the library cannot
+be built or loaded, or a tensor is not on a CUDA device, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from . import build
+
+ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2}
+
+_ERRORS = {
+    1: "bad argument (a size, stride or pointer the kernel cannot take)",
+    2: "unsupported size for this kernel",
+    3: "the CUDA runtime refused the launch",
+    4: "a pointer or stride breaks an alignment rule of this kernel",
+    5: "the kernel library could not set itself up on this device",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_lock = threading.Lock()
+
+_c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
+
+_SIGNATURES = {
+    "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p],
+    "mu_layernorm": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p],
+    "mu_gemm_simt": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
+                     _c_int, _c_int, _c_int, _c_p],
+    "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+                     _c_int, _c_p, _c_int, _c_p],
+    "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
+                     _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p],
+    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p],
+    "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; builds it at the first call if needed."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = build.library_path()
+                try:
+                    lib = ctypes.CDLL(path)
+                except OSError as e:
+                    raise KernelError(f"cannot load the CUDA kernels of math_utils_b200 from {path}: {e}") from None
+                for name, argtypes in _SIGNATURES.items():
+                    try:
+                        fn = getattr(lib, name)
+                    except AttributeError:
+                        continue          # optional kernels are looked up where they are used
+                    fn.argtypes = argtypes
+                    fn.restype = _c_int
+                _lib = lib
+    return _lib
+
+
+def declare(name: str, argtypes) -> None:
+    """Registers the signature of one more launcher of the library."""
+    _SIGNATURES[name] = argtypes
+    if _lib is not None and hasattr(_lib, name):
+        fn = getattr(_lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _c_int
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("math_utils_b200 kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+
+
+def _is_bf16(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise KernelError(f"kernels take bfloat16 or float32, got {t.dtype}")
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> None:
+    if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Tensor,
+          pos_table: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] + pos_table[positions[t]] as float32 [T, hidden]."""
+    _need_cuda(ids, positions, table, pos_table)
+    _i32(ids, "ids"); _i32(positions, "positions")
+    n, hidden = ids.numel(), table.shape[1]
+    if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != hidden):
+        raise KernelError("the position table must match the token table in dtype and width")
+    if not table.is_contiguous() or (pos_table is not None and not pos_table.is_contiguous()):
+        raise KernelError("embedding tables must be contiguous")
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _check(library().mu_embed(_ptr(ids), _ptr(positions), _ptr(table), _ptr(pos_table), _ptr(out),
+                              n, hidden, _is_bf16(table), _stream()), "embed")
+    return out
+
+
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float,
+              out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm of float32 rows (optionally the rows that ``rows`` picks)."""
+    _need_cuda(x, gamma, beta, rows)
+    _i32(rows, "rows")
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("layernorm input must be contiguous float32")
+    if gamma.dtype != torch.float32 or (beta is not None and beta.dtype != torch.float32):
+        raise KernelError("layernorm parameters must be float32")
+    hidden = x.shape[-1]
+    n = rows.numel() if rows is not None else x.numel() // hidden
+    if out is None:
+        out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    _check(library().mu_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), n, hidden,
+                                  float(eps), _is_bf16(out), _stream()), f"layernorm(hidden={hidden})")
+    return out
+
+
+# ------------------------------------------------------------------------ GEMM
+def _gemm_args(a, w, bias, residual, out, out_dtype):
+    _need_cuda(a, w, bias, residual, out)
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
+        raise KernelError(f"gemm shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}")
+    if a.dtype != w.dtype:
+        raise KernelError(f"gemm operands differ in dtype: {a.dtype} and {w.dtype}")
+    if a.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm operands must have unit stride along k")
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if out.shape != (m, n) or out.stride(1) != 1:
+        raise KernelError("gemm output has the wrong shape or stride")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != n):
+        raise KernelError("gemm bias must be float32 of length n")
+    if residual is not None and (residual.dtype != torch.float32 or residual.shape != (m, n)
+                                 or residual.stride(1) != 1):
+        raise KernelError("gemm residual must be float32 [m, n]")
+    return m, n, k, out
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """out = act(a @ w^T + bias) + residual on CUDA cores, any shape, any of the
+    two dtypes; with float32 operands this is the true 32-bit product."""
+    m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
+    _check(library().mu_gemm_simt(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
+        out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
+        _is_bf16(a), _is_bf16(out), _stream()), f"gemm_simt({m}x{n}x{k})")
+    return out
+
+
+# ------------------------------------------------------------------- attention
+def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: torch.Tensor,
+              page_tokens: int, n_kv_heads: int, head_dim: int, kv_pages: torch.Tensor) -> None:
+    """Copies keys and values of this step's tokens ([T, n_kv_heads * head_dim]
+    views, unit inner stride) into their pages."""
+    _need_cuda(k, v, tok_pos, tok_seq, block_table, kv_pages)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    if k.dtype != kv_pages.dtype or v.dtype != kv_pages.dtype:
+        raise KernelError("keys, values and the cache must share a dtype")
+    if k.stride(1) != 1 or v.stride(1) != 1:
+        raise KernelError("keys and values must have unit inner stride")
+    _check(library().mu_kv_append(
+        _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(tok_pos), _ptr(tok_seq),
+        _ptr(block_table), block_table.shape[1], page_tokens, k.shape[0], n_kv_heads, head_dim,
+        _ptr(kv_pages), _is_bf16(kv_pages), _stream()), f"kv_append(head_dim={head_dim})")
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor,
+              page_tokens: int, tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int,
+              scale: float, window: int = 0, n_splits: int = 1, split_keys: int = 0,
+              part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of each query token ([T, n_heads * head_dim] view) over the
+    cached keys first..its position; writes ``out`` [T, n_heads * head_dim]."""
+    _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, part_o, part_ml)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    if q.dtype != kv_pages.dtype or out.dtype != kv_pages.dtype:
+        raise KernelError("queries, output and the cache must share a dtype")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("queries and output must have unit inner stride")
+    n_tokens = q.shape[0]
+    if n_splits > 1:
+        need_o, need_ml = n_tokens * n_heads * n_splits * head_dim, n_tokens * n_heads * n_splits * 2
+        if (part_o is None or part_ml is None or part_o.numel() < need_o or part_ml.numel() < need_ml
+                or part_o.dtype != torch.float32 or part_ml.dtype != torch.float32):
+            raise KernelError("split attention needs float32 scratch for its partial results")
+    _check(library().mu_attention(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv_pages), _ptr(block_table),
+        block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), int(split_keys),
+        _ptr(part_o), _ptr(part_ml), _is_bf16(kv_pages), _stream()),
+        f"attention(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+    return out
+
+
+# -------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(logits, out)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logits must be float32 [rows, vocab] with unit inner stride")
+    n, vocab = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(library().mu_argmax(_ptr(logits), logits.stride(0), n, vocab, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
+           request_ids: Optional[torch.Tensor], draw_index: torch.Tensor,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row by temperature / top-k; ``draw_index`` (int32 per row)
+    counts the draws of each request and is advanced by one."""
+    _need_cuda(logits, request_ids, draw_index, out)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logits must be float32 [rows, vocab] with unit inner stride")
+    if request_ids is not None and request_ids.dtype != torch.int64:
+        raise KernelError("request_ids must be int64")
+    _i32(draw_index, "draw_index")
+    n, vocab = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(library().mu_sample(_ptr(logits), logits.stride(0), n, vocab, float(temperature), int(top_k),
+                               int(seed) & ((1 << 64) - 1), _ptr(request_ids), _ptr(draw_index), _ptr(out),
+                               _stream()), "sample")
+    return out
+
+
+# -------------------------------------------------------------------- dispatch
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(x @ weight^T + bias) + residual through the kernel that fits the
+    dtype and the shape.  float32 operands always take the CUDA-core kernel."""
+    return gemm_simt(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

@@ -1,0 +1,298 @@
+// Sampling on the device: greedy, and temperature with an optional top-k.
+//
+// The rule is the reference's sampleTopK (include/ai/LocalModel.hpp:3809-3841):
+// greedy when temperature <= 0 or top_k == 1 (first maximum wins); otherwise
+// keep the top_k largest logits (0 keeps all), p_i = exp(l_i / T - best / T),
+// pick = u * sum p, and walk the kept tokens in descending order of logit
+// (ties: lower index first) until the running sum passes pick.
+//
+// No sort is needed for that walk.  Logits map to 32-bit keys that order like
+// the floats; an 8-bit radix descent over the keys (4 passes) finds the k-th
+// largest key, and a second descent, over histograms of probability mass
+// instead of counts, finds the key at which the running mass passes pick.
+// Masses are summed as 64-bit fixed point (2^-40 units) with integer atomics,
+// so the sums do not depend on the order threads arrive in and a (seed,
+// request, draw index) always gives the same token.
+//
+// u comes from a counter-based stream per request: key = splitmix64(seed ^
+// request * 0x9E3779B97F4A7C15), x = splitmix64(key + n * 0xD1B54A32D192ED03),
+// u = (x >> 11) * 2^-53 (splitmix64 and the 53-bit mantissa rule as in
+// include/math/Random.hpp:27,79-84), n = how many tokens the request has drawn.
+#include "common.cuh"
+
+namespace mu {
+
+constexpr int SAMPLE_THREADS = 1024;
+constexpr double FIXED_ONE = 1099511627776.0;  // 2^40
+
+__device__ __forceinline__ unsigned int float_key(float v) {
+    const unsigned int b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__host__ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+    unsigned long long z = x + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ double uniform_draw(unsigned long long seed, unsigned long long request,
+                                               unsigned long long n) {
+    const unsigned long long key = splitmix64(seed ^ (request * 0x9E3779B97F4A7C15ull));
+    const unsigned long long x = splitmix64(key + n * 0xD1B54A32D192ED03ull);
+    return (double)(x >> 11) * (1.0 / 9007199254740992.0);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out) {
+    __shared__ unsigned long long best_smem[32];
+    const float* row = logits + (long long)blockIdx.x * ld;
+    unsigned long long best = 0;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        // larger logit wins; among equals the lower index (larger ~index) wins
+        const unsigned long long cand =
+            ((unsigned long long)float_key(row[i]) << 32) | (unsigned int)(0xFFFFFFFFu - (unsigned)i);
+        best = cand > best ? cand : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) best_smem[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? best_smem[threadIdx.x] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(best & 0xFFFFFFFFull));
+    }
+}
+
+// Among 256 bins taken from the highest down, finds the first whose running
+// total exceeds `target`.  Called by warp 0; returns through shared memory
+// (sel[0] = bin, sel[1] = total of the bins above it).
+__device__ __forceinline__ void select_bin(const unsigned long long* hist, unsigned long long target,
+                                           unsigned long long* sel) {
+    const int lane = threadIdx.x & 31;
+    unsigned long long local = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) local += hist[255 - (lane * 8 + i)];
+    unsigned long long incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const unsigned long long before = incl - local;
+    if (before <= target && target < incl) {
+        unsigned long long run = before;
+        for (int i = 0; i < 8; ++i) {
+            const int bin = 255 - (lane * 8 + i);
+            const unsigned long long h = hist[bin];
+            if (target < run + h) {
+                sel[0] = (unsigned long long)bin;
+                sel[1] = run;
+                break;
+            }
+            run += h;
+        }
+    }
+}
+
+struct RowView {
+    const float* row;
+    int vocab;
+    float temperature, best;       // best = max logit / temperature
+    unsigned int thr_key;          // kept: key > thr_key, or key == thr_key and index <= idx_cut
+    int idx_cut;
+    __device__ __forceinline__ bool kept(unsigned int key, int i) const {
+        return key > thr_key || (key == thr_key && i <= idx_cut);
+    }
+    __device__ __forceinline__ unsigned long long mass(float logit) const {
+        return (unsigned long long)((double)expf(logit / temperature - best) * FIXED_ONE);
+    }
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature, int top_k,
+              unsigned long long seed, const long long* __restrict__ request_ids,
+              int* __restrict__ draw_index, int* __restrict__ out) {
+    __shared__ unsigned long long hist[256];
+    __shared__ unsigned long long sel[2];
+    __shared__ float red[32];
+    __shared__ unsigned long long total_smem;
+    __shared__ int found_idx;
+    const int tid = threadIdx.x, r = blockIdx.x;
+    RowView v;
+    v.row = logits + (long long)r * ld;
+    v.vocab = vocab;
+    v.temperature = temperature;
+    v.thr_key = 0;
+    v.idx_cut = vocab;
+
+    // maximum logit
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, v.row[i]);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < (blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+    v.best = mx / temperature;
+
+    // the k-th largest key, when top_k cuts anything
+    if (top_k > 0 && top_k < vocab) {
+        unsigned int prefix = 0, mask = 0;
+        unsigned long long need = (unsigned long long)top_k - 1;   // first bin whose running count exceeds this
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256) hist[tid] = 0;
+            __syncthreads();
+            {
+                // neighbouring tokens mostly share a bin: add up a run before touching shared memory
+                int cur = -1;
+                unsigned long long run = 0;
+                for (int i = tid; i < vocab; i += blockDim.x) {
+                    const unsigned int key = float_key(v.row[i]);
+                    if ((key & mask) != prefix) continue;
+                    const int bin = (int)((key >> shift) & 255u);
+                    if (bin == cur) { ++run; continue; }
+                    if (cur >= 0) atomicAdd(&hist[cur], run);
+                    cur = bin;
+                    run = 1;
+                }
+                if (cur >= 0) atomicAdd(&hist[cur], run);
+            }
+            __syncthreads();
+            if (tid < 32) select_bin(hist, need, sel);
+            __syncthreads();
+            prefix |= (unsigned int)sel[0] << shift;
+            mask |= 0xFFu << shift;
+            need -= sel[1];
+            __syncthreads();
+        }
+        v.thr_key = prefix;
+        // `need` + 1 of the tokens equal to the threshold are kept; cut by index if there are more
+        if (tid == 0) found_idx = vocab;
+        __syncthreads();
+        const unsigned long long equal_total = hist[prefix & 255u];
+        if (equal_total > need + 1) {
+            if (tid == 0) {
+                unsigned long long seen = 0;
+                for (int i = 0; i < vocab; ++i)
+                    if (float_key(v.row[i]) == prefix && ++seen == need + 1) { found_idx = i; break; }
+            }
+            __syncthreads();
+        }
+        v.idx_cut = found_idx;
+        __syncthreads();
+    }
+
+    // total mass of the kept tokens
+    if (tid == 0) total_smem = 0;
+    __syncthreads();
+    {
+        unsigned long long local = 0;
+        for (int i = tid; i < vocab; i += blockDim.x) {
+            const float l = v.row[i];
+            if (v.kept(float_key(l), i)) local += v.mass(l);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((tid & 31) == 0) atomicAdd(&total_smem, local);
+    }
+    __syncthreads();
+    const unsigned long long total = total_smem;
+    const long long request = request_ids ? request_ids[r] : r;
+    const double u = uniform_draw(seed, (unsigned long long)request, (unsigned long long)draw_index[r]);
+    unsigned long long target = (unsigned long long)(u * (double)total);
+    if (target >= total) target = total - 1;
+
+    // the key at which the running mass, taken from the largest logit down, passes target
+    unsigned int prefix = 0, mask = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        {
+            int cur = -1;
+            unsigned long long run = 0;
+            for (int i = tid; i < vocab; i += blockDim.x) {
+                const float l = v.row[i];
+                const unsigned int key = float_key(l);
+                if ((key & mask) != prefix || !v.kept(key, i)) continue;
+                const int bin = (int)((key >> shift) & 255u);
+                const unsigned long long w = v.mass(l);
+                if (bin == cur) { run += w; continue; }
+                if (cur >= 0) atomicAdd(&hist[cur], run);
+                cur = bin;
+                run = w;
+            }
+            if (cur >= 0) atomicAdd(&hist[cur], run);
+        }
+        __syncthreads();
+        if (tid < 32) select_bin(hist, target, sel);
+        __syncthreads();
+        prefix |= (unsigned int)sel[0] << shift;
+        mask |= 0xFFu << shift;
+        target -= sel[1];
+        __syncthreads();
+    }
+    // tokens with exactly this key share one mass; the (target / mass)-th of them by index
+    if (tid == 0) found_idx = vocab;
+    __syncthreads();
+    const unsigned long long group_mass = hist[prefix & 255u];
+    float group_logit = 0.0f;
+    {
+        // recover the logit from the key
+        const unsigned int b = (prefix & 0x80000000u) ? (prefix & 0x7FFFFFFFu) : ~prefix;
+        group_logit = __uint_as_float(b);
+    }
+    const unsigned long long one = v.mass(group_logit);
+    const unsigned long long nth = one ? target / one : 0;
+    if (nth == 0) {
+        for (int i = tid; i < vocab; i += blockDim.x)
+            if (float_key(v.row[i]) == prefix && v.kept(prefix, i)) atomicMin(&found_idx, i);
+    } else if (tid == 0) {
+        unsigned long long seen = 0;
+        for (int i = 0; i < vocab; ++i)
+            if (float_key(v.row[i]) == prefix && v.kept(prefix, i)) {
+                found_idx = i;                       // the last one stands if fewer than nth + 1 exist
+                if (seen++ == nth) break;
+            }
+    }
+    (void)group_mass;
+    __syncthreads();
+    if (tid == 0) {
+        out[r] = found_idx < vocab ? found_idx : 0;
+        draw_index[r] += 1;
+    }
+}
+
+}  // namespace mu
+
+// logits [n_rows, ld] float32 -> out[n_rows] token ids.
+MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (!logits || !out || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
+    mu::argmax_kernel<<<n_rows, mu::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+    MU_CHECK_LAUNCH();
+    return MU_OK;
+}
+
+// request_ids [n_rows] int64 (null: the row index), draw_index [n_rows] int32 is read and
+// then incremented.  temperature must be > 0; the caller routes greedy to mu_argmax.
+MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature,
+                        int top_k, unsigned long long seed, const long long* request_ids,
+                        int* draw_index, int* out, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (!logits || !out || !draw_index || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
+    if (!(temperature > 0.0f) || top_k < 0) return MU_ERR_BAD_ARGUMENT;
+    mu::sample_kernel<<<n_rows, mu::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+        logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out);
+    MU_CHECK_LAUNCH();
+    return MU_OK;
+}

@@ -1,0 +1,102 @@
+"""The decoder and its one step function.
+
+``DecoderModel.step(cache, entries)`` runs exactly the tokens it is given: for
+each sequence the next tokens after what its cache slot already holds (a whole
+prompt, a part of one, or a single token), all sequences of the call as one
+batch, and returns the logits at the wanted places.  Per sequence this is the
+reference's ``forward(ids, count, startPos, cache, logits)``
+(include/ai/LocalModel.hpp:3648-3802); the batch over slots is this library's.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache import SequenceCache
+from ..config import load_config
+from ..weights.loader import load_weights
+from .assemble import assemble, collect_tensor_specs
+from .batch import PinnedRing, StepEntry, build_context
+from .runtime import Runtime
+
+
+class DecoderModel:
+    def __init__(self, plan, tensors, runtime: Runtime, config=None):
+        self.plan = plan
+        self.config = config
+        self.runtime = runtime
+        self.assembly = assemble(plan)
+        for part in self.assembly.parts():
+            part.bind(tensors, runtime)
+        if hasattr(self.assembly.head, "attach_embedding"):
+            self.assembly.head.attach_embedding(self.assembly.embedding)
+        self.vocab_size = plan.vocab_size
+        self.max_positions = plan.max_positions
+        self.stop_ids = tuple(plan.stop_ids)
+        self._ring = PinnedRing()
+        self._workspace: dict = {}
+        self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
+
+    # ---------------------------------------------------------------- loading
+    @classmethod
+    def from_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0") -> "DecoderModel":
+        """Loads config.json and the weights of a model folder; the class of
+        model is chosen by config.json through the registry."""
+        runtime = Runtime.create(dtype, device)
+        if runtime.device.type != "cuda":
+            raise RuntimeError("math_utils_b200 runs on a CUDA device only; there is no CPU path")
+        runtime.ops.library()                       # fail now, loudly, if the kernels are missing
+        arch, config, plan = load_config(model_dir)
+        assembly = assemble(plan)
+        specs = collect_tensor_specs(plan, assembly)
+        tensors = load_weights(model_dir, specs, runtime.dtype, runtime.device,
+                               ignored=plan.ignored_tensors, prefixes=arch.name_prefixes)
+        return cls(plan, tensors, runtime, config)
+
+    # ------------------------------------------------------------------ cache
+    def cache_specs(self) -> List[Optional[object]]:
+        """Per schedule entry: the cache spec of its mixer if the entry owns a
+        cache, else None."""
+        out = []
+        for i, entry in enumerate(self.plan.schedule):
+            mixer = self.assembly.layers[entry.layer].mixer
+            out.append(mixer.cache_spec() if entry.cache_of == i else None)
+        return out
+
+    def new_cache(self, max_tokens: int, n_slots: Optional[int] = None) -> SequenceCache:
+        return SequenceCache(self.cache_specs(), max_tokens, self.max_positions, self.runtime.dtype,
+                             self.runtime.device, n_slots=n_slots)
+
+    # ------------------------------------------------------------------- step
+    def step(self, cache: SequenceCache, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the given tokens; returns float32 logits [wanted, vocab] in the
+        order of the entries and of their ``want`` lists, or None if nothing is
+        wanted."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        if len({e.slot for e in entries}) != len(entries):
+            raise ValueError("a slot appears twice in one step")
+        for e in entries:
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise ValueError(f"token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
+        starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
+        ctx = build_context(self.runtime, self.assembly.position, cache, entries, starts,
+                            self._ring, self._workspace)
+        logits = self.forward(ctx, cache)
+        for e in entries:
+            cache.commit(e.slot, len(e.tokens))
+        return logits
+
+    def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:
+        a = self.assembly
+        x = a.embedding.forward(ctx, a.position.embedding_table())
+        for i, entry in enumerate(self.plan.schedule):
+            layer = a.layers[entry.layer]
+            layer.arrangement.forward(x, layer, ctx, cache.entry(entry.cache_of), entry.cache_of == i)
+        if ctx.want_rows is None:
+            return None
+        h = a.final_norm.forward(x, rows=ctx.want_rows)
+        return a.head.forward(h)

@@ -1,0 +1,45 @@
+"""Dense two-matrix feed-forward: up projection, activation, down projection
+(include/ai/LocalModel.hpp:3767-3774).  The activation is a parameter:
+``gelu_new`` (tanh form, include/ai/LocalModel.hpp:1388-1391) or ``gelu``
+(erf form)."""
+from __future__ import annotations
+
+from ..config.base import ConfigError, PartSpec
+from .base import FeedForward, TensorSpec, register_part
+from .linear import Linear
+
+ACTIVATIONS = ("gelu_new", "gelu")
+
+
+class DenseFeedForward(FeedForward):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.hidden_size = int(self.param("hidden_size"))
+        self.inner_size = int(self.param("inner_size"))
+        self.activation = self.param("activation")
+        if self.activation not in ACTIVATIONS:
+            raise ConfigError(f"dense_ffn: activation '{self.activation}' is not one of {', '.join(ACTIVATIONS)}")
+        self.in_out = self.param("weight_layout", "out_in") == "in_out"
+
+    def _matrix(self, role, out_f, in_f, init):
+        shape = (in_f, out_f) if self.in_out else (out_f, in_f)
+        return TensorSpec(self.tensor_name(role), shape, role="matrix", transpose=self.in_out, init=init)
+
+    def tensor_specs(self):
+        d, i = self.hidden_size, self.inner_size
+        return (self._matrix("up_weight", i, d, "normal"),
+                TensorSpec(self.tensor_name("up_bias"), (i,), role="vector", init="bias"),
+                self._matrix("down_weight", d, i, "residual_projection"),
+                TensorSpec(self.tensor_name("down_bias"), (d,), role="vector", init="bias"))
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.up = Linear(tensors[self.tensor_name("up_weight")], tensors[self.tensor_name("up_bias")], runtime)
+        self.down = Linear(tensors[self.tensor_name("down_weight")], tensors[self.tensor_name("down_bias")], runtime)
+
+    def forward(self, h, residual, ctx) -> None:
+        u = self.up(h, act=self.activation)
+        self.down(u, residual=residual, out=residual)
+
+
+register_part("feed_forward", "dense_ffn", DenseFeedForward, replace=True)

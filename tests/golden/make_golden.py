@@ -1,0 +1,148 @@
+"""Makes the golden logits under tests/golden/ from the reference's own code.
+
+Run once, by hand, on a machine that has the reference checked out:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+Two statements of GPT-2 in the reference are run on tiny random models made by
+``make_weights`` below (plain NumPy, seeded):
+  * the NumPy oracle ``tools/gpt2_oracle.py`` (``forward``), imported;
+  * the C++ decoder ``ai::LocalModel`` (include/ai/LocalModel.hpp), compiled
+    with g++ against the reference's headers from the small driver
+    ``local_model_probe.cpp`` beside this script, whole prompt and token by token.
+The reference fixes the feed-forward width at four times the model width and
+the tanh GELU, so the golden configurations keep to those; the other options
+(``n_inner``, erf GELU, ``scale_attn_by_inverse_layer_idx``) rest on their
+formulas alone.  ``tests/test_plain_reference.py`` rebuilds the same weights and
+checks the plain implementation against the stored logits.
+"""
+import json
+import os
+import struct
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+GOLDEN_CONFIGS = {
+    "golden_a": {"model_type": "gpt2", "n_layer": 2, "n_embd": 64, "n_head": 4, "vocab_size": 512,
+                 "n_positions": 128, "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new"},
+    "golden_b": {"model_type": "gpt2", "n_layer": 3, "n_embd": 96, "n_head": 3, "vocab_size": 1031,
+                 "n_positions": 80, "layer_norm_epsilon": 1e-6, "activation_function": "gelu_new"},
+}
+GOLDEN_IDS = {
+    "golden_a": [5, 17, 3, 250, 511, 0, 42, 42, 99, 310, 7, 128, 64, 200, 1, 2, 3],
+    "golden_b": [1030, 0, 517, 33, 900, 12, 12, 640, 77, 1000, 5, 81, 300, 2, 45, 999, 731, 8, 64, 100,
+                 410, 29, 650, 3],
+}
+
+
+def LOCAL_MODEL_ROWS(n):
+    return [0, 1, n // 2, n - 2, n - 1]
+
+
+def make_weights(cfg, seed):
+    """name -> float32 array, GPT-2's tensor names and on-disk ([in, out]) shapes."""
+    rng = np.random.default_rng(seed)
+    d, v, p, n = cfg["n_embd"], cfg["vocab_size"], cfg["n_positions"], cfg["n_layer"]
+    inner = 4 * d
+
+    def normal(*shape, mean=0.0, std=0.08):
+        return (rng.standard_normal(shape) * std + mean).astype(np.float32)
+
+    w = {"wte.weight": normal(v, d), "wpe.weight": normal(p, d),
+         "ln_f.weight": normal(d, mean=1.0), "ln_f.bias": normal(d)}
+    for i in range(n):
+        h = f"h.{i}"
+        w[h + ".ln_1.weight"] = normal(d, mean=1.0)
+        w[h + ".ln_1.bias"] = normal(d)
+        w[h + ".attn.c_attn.weight"] = normal(d, 3 * d)
+        w[h + ".attn.c_attn.bias"] = normal(3 * d)
+        w[h + ".attn.c_proj.weight"] = normal(d, d)
+        w[h + ".attn.c_proj.bias"] = normal(d)
+        w[h + ".ln_2.weight"] = normal(d, mean=1.0)
+        w[h + ".ln_2.bias"] = normal(d)
+        w[h + ".mlp.c_fc.weight"] = normal(d, inner)
+        w[h + ".mlp.c_fc.bias"] = normal(inner)
+        w[h + ".mlp.c_proj.weight"] = normal(inner, d)
+        w[h + ".mlp.c_proj.bias"] = normal(d)
+    return w
+
+
+def write_f32_safetensors(path, weights):
+    header, offset = {}, 0
+    for name in sorted(weights):
+        n = weights[name].nbytes
+        header[name] = {"dtype": "F32", "shape": list(weights[name].shape), "data_offsets": [offset, offset + n]}
+        offset += n
+    blob = json.dumps(header).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for name in sorted(weights):
+            f.write(np.ascontiguousarray(weights[name]).tobytes())
+
+
+def write_model_dir(folder, cfg, weights):
+    """config.json, F32 weights and the dummy byte-level tokenizer files that
+    LocalModel::load insists on (include/ai/LocalModel.hpp:1724, 1800-1817)."""
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_f32_safetensors(os.path.join(folder, "model.safetensors"), weights)
+    sys.path.insert(0, os.path.join(REFERENCE, "tools"))
+    import gpt2_oracle
+    symbols = list(gpt2_oracle.bytes_to_unicode().values())
+    vocab = {s: i for i, s in enumerate(symbols)}
+    vocab[symbols[0] + symbols[1]] = len(vocab)
+    with open(os.path.join(folder, "vocab.json"), "w", encoding="utf-8") as f:
+        json.dump(vocab, f, ensure_ascii=False)
+    with open(os.path.join(folder, "merges.txt"), "w", encoding="utf-8") as f:
+        f.write("#version: 0.2\n" + symbols[0] + " " + symbols[1] + "\n")
+
+
+def run_oracle(cfg, weights, ids):
+    sys.path.insert(0, os.path.join(REFERENCE, "tools"))
+    import gpt2_oracle
+    return np.asarray(gpt2_oracle.forward(list(ids), weights, cfg, gpt2_oracle.Dumper(None)), dtype=np.float32)
+
+
+def run_local_model(folder, ids, vocab):
+    """Compiles the probe against the reference's headers and runs it: logits
+    of every position, once from whole-prompt calls and once token by token."""
+    exe = os.path.join(tempfile.gettempdir(), "local_model_probe")
+    if not os.path.exists(exe):
+        cmd = ["g++", "-std=c++2b", "-O2", "-w", "-I", os.path.join(REFERENCE, "include"),
+               os.path.join(HERE, "local_model_probe.cpp"), os.path.join(REFERENCE, "src", "gpu", "Stub.cpp"),
+               "-lpthread", "-o", exe]
+        subprocess.run(cmd, check=True)
+    out = os.path.join(folder, "probe_out.bin")
+    subprocess.run([exe, folder, out] + [str(i) for i in ids], check=True)
+    both = np.fromfile(out, dtype=np.float32).reshape(2, len(ids), vocab)
+    return both[0], both[1]
+
+
+if __name__ == "__main__":
+    REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    with_cpp = os.path.exists(os.path.join(HERE, "local_model_probe.cpp"))
+    for k, (name, cfg) in enumerate(GOLDEN_CONFIGS.items()):
+        weights = make_weights(cfg, seed=1234 + k)
+        ids = GOLDEN_IDS[name]
+        arrays = {"oracle": run_oracle(cfg, weights, ids)}
+        if with_cpp:
+            folder = tempfile.mkdtemp(prefix=name)
+            write_model_dir(folder, cfg, weights)
+            whole, stepwise = run_local_model(folder, ids, cfg["vocab_size"])
+            rows = LOCAL_MODEL_ROWS(len(ids))          # a few rows keep the files small
+            arrays["local_model_rows"] = np.asarray(rows)
+            arrays["local_model_whole"] = whole[rows]
+            arrays["local_model_stepwise"] = stepwise[rows]
+            print(name, "LocalModel vs oracle, all rows:", float(np.abs(whole - arrays["oracle"]).max()),
+                  float(np.abs(stepwise - arrays["oracle"]).max()))
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
+        print(name, {k2: v.shape for k2, v in arrays.items()})
+else:
+    REFERENCE = "/root/reference"

@@ -1,0 +1,113 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16:
+each request alone and whole, with its last tokens one by one, and in batches
+of unequal lengths one after another so that slots and pages are used again."""
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+from helpers import check_logits, run_batch, run_tail_one_by_one, run_whole
+from math_utils_b200 import DecoderModel
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def requests_for(cfg, seed, lengths):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lengths]
+
+
+@pytest.fixture(scope="module")
+def engines(model_dirs):
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            cache[(name, dtype)] = DecoderModel.from_dir(model_dirs[name], dtype=dtype)
+        return cache[(name, dtype)]
+    return get
+
+
+@pytest.fixture(scope="module")
+def plain_logits(plain_models):
+    memo = {}
+
+    def get(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in memo:
+            cfg, w = plain_models[name]
+            memo[key] = plain_gpt2.forward(list(tokens), cfg, w)
+        return memo[key]
+    return get
+
+
+LENGTHS = {"tiny_a": [5, 17, 32, 128, 70], "tiny_b": [1, 2, 9, 40, 63, 80]}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_whole_requests(name, dtype, engines, plain_models, plain_logits):
+    model = engines(name, dtype)
+    cfg = plain_models[name][0]
+    cache = model.new_cache(max_tokens=256)
+    for tokens in requests_for(cfg, 1, LENGTHS[name]):
+        got = run_whole(model, cache, tokens)
+        check_logits(got, plain_logits(name, tokens), dtype, f"{name} whole n={len(tokens)}")
+    assert cache.slots.n_free == cache.n_slots and cache.free_pages() == cache.n_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_last_tokens_one_by_one(name, dtype, engines, plain_models, plain_logits):
+    model = engines(name, dtype)
+    cfg = plain_models[name][0]
+    cache = model.new_cache(max_tokens=256)
+    for tokens in requests_for(cfg, 2, LENGTHS[name][2:]):
+        got = run_tail_one_by_one(model, cache, tokens, tail=32)
+        check_logits(got, plain_logits(name, tokens), dtype, f"{name} tail n={len(tokens)}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_unequal_batches_reuse_slots(name, dtype, engines, plain_models, plain_logits):
+    model = engines(name, dtype)
+    cfg = plain_models[name][0]
+    top = cfg["n_positions"]
+    # room for one batch only, so the second batch must take the first one's slots and pages
+    totals_a = [top, 40, 66, 7]
+    cache = model.new_cache(max_tokens=sum(-(-t // 64) * 64 for t in totals_a), n_slots=4)
+    for round_, totals in enumerate([totals_a, [33, top, 12, 64], [top - 1, 3, 65, 20]]):
+        reqs = requests_for(cfg, 10 + round_, totals)
+        prompts = [max(1, min(t - 1, p)) for t, p in zip(totals, [17, 5, 64, 2])]
+        got = run_batch(model, cache, reqs, prompts)
+        for i, (g, r) in enumerate(zip(got, reqs)):
+            check_logits(g, plain_logits(name, r), dtype, f"{name} batch {round_} request {i}")
+        assert cache.slots.n_free == 4 and cache.free_pages() == cache.n_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_split_prompt_equals_whole(dtype, engines, plain_models, plain_logits):
+    """A prompt fed in two parts (the second starts at a filled cache)."""
+    from math_utils_b200 import StepEntry
+    name = "tiny_b"
+    model = engines(name, dtype)
+    tokens = requests_for(plain_models[name][0], 5, [71])[0]
+    cache = model.new_cache(max_tokens=128)
+    slot = cache.acquire()
+    a = model.step(cache, [StepEntry(slot, tokens[:30], list(range(30)))]).cpu().numpy()
+    b = model.step(cache, [StepEntry(slot, tokens[30:], list(range(41)))]).cpu().numpy()
+    cache.release(slot)
+    check_logits(np.concatenate([a, b]), plain_logits(name, tokens), dtype, "split prompt")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_from_one_token(dtype, engines, plain_models, plain_logits):
+    """The first tokens of a sequence and a long run of single-token steps."""
+    name = "tiny_a"
+    model = engines(name, dtype)
+    tokens = requests_for(plain_models[name][0], 6, [128])[0]
+    cache = model.new_cache(max_tokens=128)
+    got = run_tail_one_by_one(model, cache, tokens, tail=127)
+    check_logits(got, plain_logits(name, tokens), dtype, "decode from the first token")

@@ -80,9 +80,14 @@ def declare(name: str, argtypes) -> None:
         fn.restype = _c_int
 
 
-def _check(code: int, what: str) -> None:
+launch_count = 0      # kernels of this library launched so far (a merge after a split counts too)
+
+
+def _check(code: int, what: str, launches: int = 1) -> None:
+    global launch_count
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+    launch_count += launches
 
 
 def _stream() -> int:
@@ -227,7 +232,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_
         block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
         n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), int(split_keys),
         _ptr(part_o), _ptr(part_ml), _is_bf16(kv_pages), _stream()),
-        f"attention(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+        f"attention(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})", launches=2 if n_splits > 1 else 1)
     return out
 
 

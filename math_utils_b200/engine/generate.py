@@ -1,0 +1,149 @@
+"""The generation loop above the step function.
+
+For one batch of requests that start together: a slot each, all prompts
+(unequal lengths) in one step, a token sampled for each from its last logits,
+then one token each per step.  A request ends when it samples a stop token
+(which is neither kept nor fed), when it has produced ``max_tokens``, or when
+its sequence fills the context; it then leaves the batch and its slot goes
+back.  More requests than fit in one batch run as batches one after another.
+The single-sequence shape is the reference's: prefill, then
+``sample -> stop? -> emit -> forward(one token)`` while ``i < maxTokens`` and
+``cache.length < context`` (src/LLM.cpp:688-707; include/ai/LLM.hpp:226-243).
+
+The decisions (how requests are cut into batches, what a sampled token does
+to its request) are plain functions of host values, so they are tested
+without a device.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling import Sampler, SamplingParams
+from .batch import StepEntry
+
+
+def round_up(n: int, unit: int) -> int:
+    return -(-n // unit) * unit
+
+
+def most_positions(prompt_len: int, max_tokens: int, context: int) -> int:
+    """Positions a request can come to hold in the cache: its prompt plus every
+    produced token that is fed back (the last one produced never is)."""
+    return min(context, prompt_len + max(max_tokens - 1, 0))
+
+
+def plan_batches(prompt_lens: Sequence[int], max_tokens: int, context: int, max_batch: int,
+                 cache_tokens: int, page_tokens: int) -> List[List[int]]:
+    """Cuts requests, in order, into batches that fit ``max_batch`` sequences
+    and ``cache_tokens`` cache positions (each request rounded up to whole
+    pages of its largest possible length)."""
+    batches: List[List[int]] = []
+    current: List[int] = []
+    used = 0
+    for i, n in enumerate(prompt_lens):
+        need = round_up(max(most_positions(n, max_tokens, context), 1), page_tokens)
+        if need > cache_tokens:
+            raise ValueError(f"request {i} needs {need} cache positions, the cache holds {cache_tokens}")
+        if current and (len(current) >= max_batch or used + need > cache_tokens):
+            batches.append(current)
+            current, used = [], 0
+        current.append(i)
+        used += need
+    if current:
+        batches.append(current)
+    return batches
+
+
+@dataclass
+class RequestState:
+    index: int                      # place in the caller's list; also keys the sampling stream
+    prompt: Sequence[int]
+    produced: List[int] = field(default_factory=list)
+    finished: bool = False
+    reason: str = ""
+
+
+def take_token(state: RequestState, token: int, stop_ids, max_tokens: int, context: int) -> bool:
+    """Applies one sampled token to its request; True if the token is to be
+    fed back for another step."""
+    if token in stop_ids:
+        state.finished, state.reason = True, "stop"
+        return False
+    state.produced.append(int(token))
+    if len(state.produced) >= max_tokens:
+        state.finished, state.reason = True, "max_tokens"
+        return False
+    if len(state.prompt) + len(state.produced) >= context:
+        # the reference samples only while cache.length < context (src/LLM.cpp:696)
+        state.finished, state.reason = True, "context"
+        return False
+    return True
+
+
+def run_batch(step: Callable, sample: Callable, acquire: Callable, release: Callable,
+              states: Sequence[RequestState], stop_ids, max_tokens: int, context: int) -> None:
+    """One batch from start to end.  ``step(entries) -> logits``,
+    ``sample(logits, rows) -> tokens`` (``rows``: indices into ``states``),
+    ``acquire() -> slot``, ``release(slot)``."""
+    slots = {}
+    try:
+        live = []
+        for k, st in enumerate(states):
+            if max_tokens <= 0 or len(st.prompt) >= context:
+                st.finished, st.reason = True, "max_tokens" if max_tokens <= 0 else "context"
+                continue
+            slots[k] = acquire()
+            live.append(k)
+        if not live:
+            return
+        entries = [StepEntry(slots[k], list(states[k].prompt), [len(states[k].prompt) - 1]) for k in live]
+        while live:
+            logits = step(entries)
+            tokens = sample(logits, live)
+            fed, entries = [], []
+            for k, tok in zip(live, tokens):
+                if take_token(states[k], int(tok), stop_ids, max_tokens, context):
+                    fed.append(k)
+                    entries.append(StepEntry(slots[k], [int(tok)], [0]))
+                else:
+                    release(slots.pop(k))
+            live = fed
+    finally:
+        for slot in slots.values():
+            release(slot)
+
+
+def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams,
+             stop_ids: Optional[Sequence[int]] = None, context: Optional[int] = None,
+             max_batch: int = 64, cache=None, request_offset: int = 0) -> List[List[int]]:
+    """Generates a continuation for every prompt (lists of token ids)."""
+    context = min(context or model.max_positions, model.max_positions)
+    stop = frozenset(model.stop_ids if stop_ids is None else stop_ids)
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise ValueError(f"prompt {i} is empty")
+        if len(p) > context:
+            raise ValueError(f"prompt {i} has {len(p)} tokens, the context holds {context}")
+    page = None
+    if cache is None:
+        from ..cache import PAGE_TOKENS
+        need = sorted((round_up(max(most_positions(len(p), max_tokens, context), 1), PAGE_TOKENS)
+                       for p in prompts), reverse=True)
+        cache = model.new_cache(max_tokens=max(sum(need[:max_batch]), PAGE_TOKENS), n_slots=max_batch)
+    page = cache.page_tokens
+    batches = plan_batches([len(p) for p in prompts], max_tokens, context, min(max_batch, cache.n_slots),
+                           cache.n_pages * page, page)
+    states = [RequestState(i + request_offset, p) for i, p in enumerate(prompts)]
+    ops = model.runtime.ops
+    for batch in batches:
+        members = [states[i] for i in batch]
+        sampler = Sampler(params, [s.index for s in members], model.runtime.device, ops)
+
+        def sample(logits, rows, sampler=sampler, n=len(members)):
+            toks = sampler.sample(logits, None if len(rows) == n else rows)
+            return toks.cpu().tolist()
+
+        run_batch(lambda entries: model.step(cache, entries), sample, cache.acquire, cache.release,
+                  members, stop, max_tokens, context)
+    return [s.produced for s in states]

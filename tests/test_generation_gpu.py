@@ -1,0 +1,159 @@
+"""Generation through the Python entry point and the command line, and trace replay
+as a program."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_gpt2
+from conftest import ROOT
+from helpers import check_logits
+
+pytestmark = pytest.mark.gpu
+
+
+def prompts_for(cfg, seed, lengths):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in lengths]
+
+
+def same_or_near_tie(model_cfg, weights, prompt, got, want, stop, context):
+    """Greedy tokens must agree; where they first differ the plain logits of the
+    two candidates must be within rounding of each other (a near tie that the
+    other precision may resolve the other way), and the comparison ends there."""
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            logits = plain_gpt2.forward(list(prompt) + want[:i], model_cfg, weights)[-1]
+            assert abs(logits[g] - logits[w]) < 2e-2 * logits.std(), (i, g, w)
+            return
+    assert len(got) == len(want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lengths,context", [("tiny_a", [5, 17, 32], None), ("tiny_b", [1, 2, 9, 40, 63], 80)])
+def test_greedy_generation_matches_plain(name, lengths, context, dtype, model_dirs, plain_models):
+    from math_utils_b200 import LLM, Options
+    cfg, w = plain_models[name]
+    llm = LLM(model_dirs[name], Options(dtype=dtype, temperature=0.0, max_batch=3))
+    prompts = prompts_for(cfg, 21, lengths)
+    n_new = 16 if name == "tiny_a" else 80
+    got = llm.generate(prompts, max_tokens=n_new, stop_ids=[])
+    for p, g in zip(prompts, got):
+        want = plain_gpt2.generate(p, cfg, w, n_new, context=context)
+        assert len(g) == min(n_new, cfg["n_positions"] - len(p))
+        if dtype == "float32":
+            assert g == want
+        else:
+            same_or_near_tie(cfg, w, p, g, want, (), context)
+
+
+def test_stop_tokens_end_requests_early(model_dirs, plain_models):
+    from math_utils_b200 import LLM, Options
+    cfg, w = plain_models["tiny_a"]
+    llm = LLM(model_dirs["tiny_a"], Options(dtype="float32", temperature=0.0))
+    prompts = prompts_for(cfg, 22, [4, 9, 30, 2])
+    free_run = llm.generate(prompts, max_tokens=24, stop_ids=[])
+    stop = {free_run[0][3], free_run[2][10]}                 # tokens that do come up
+    got = llm.generate(prompts, max_tokens=24, stop_ids=sorted(stop))
+    for p, g, f in zip(prompts, got, free_run):
+        cut = next((i for i, t in enumerate(f) if t in stop), len(f))
+        assert g == f[:cut] and g == plain_gpt2.generate(p, cfg, w, 24, stop_ids=stop)
+    assert len(got[0]) <= 3 and len(got[2]) <= 10
+    assert llm.model.stop_ids == (7,)                        # eos_token_id of config.json is the default
+
+
+def test_temperature_sampling_is_seeded_per_request(model_dirs, plain_models):
+    from math_utils_b200 import LLM, Options
+    cfg, w = plain_models["tiny_b"]
+    llm = LLM(model_dirs["tiny_b"], Options(dtype="float32", temperature=0.8, top_k=0, seed=3))
+    prompts = prompts_for(cfg, 23, [1, 2, 9, 40, 63])
+    a = llm.generate(prompts, max_tokens=12, stop_ids=[])
+    b = llm.generate(prompts, max_tokens=12, stop_ids=[], max_batch=2)      # other batches, same streams
+    c = llm.generate(prompts, max_tokens=12, stop_ids=[], seed=4)
+    assert a == b and a != c
+    for i, (p, g) in enumerate(zip(prompts, a)):
+        want = plain_gpt2.generate(p, cfg, w, 12, temperature=0.8, top_k=0, seed=3, request=i)
+        agree = next((k for k, (x, y) in enumerate(zip(g, want)) if x != y), len(g))
+        assert agree >= 4, (i, g, want)       # float32 logits near a boundary may part ways later, not at once
+
+
+def test_conversation_keeps_its_cache(model_dirs, plain_models):
+    from math_utils_b200 import LLM, Options
+    cfg, w = plain_models["tiny_a"]
+    llm = LLM(model_dirs["tiny_a"], Options(dtype="float32", temperature=0.0, max_tokens=5))
+    llm.model.stop_ids = ()
+    first = llm.prompt([3, 1, 4])
+    second = llm.prompt([1, 5])
+    # the second turn continues the first: prompt, answer (its last token was never fed), new ids
+    history = [3, 1, 4] + first[:-1] + [1, 5]
+    assert second == plain_gpt2.generate(history, cfg, w, 5)
+    assert llm.once([3, 1, 4]) == first
+    llm.reset()
+    assert llm.prompt([3, 1, 4]) == first
+
+
+def test_command_line(model_dirs, plain_models, tmp_path):
+    cfg, w = plain_models["tiny_a"]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llm"), model_dirs["tiny_a"], "--prompt",
+                          "5,17,3", "--tokens", "6", "--temp", "0", "--fp32", "--stop", ""],
+                         capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr
+    got = [int(t) for t in out.stdout.strip().splitlines()[-1].split()]
+    assert got == plain_gpt2.generate([5, 17, 3], cfg, w, 6)
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(cfg))
+    out = subprocess.run([sys.executable, "-m", "math_utils_b200", "--random", "--config", str(cfg_file),
+                          "--seed", "9", "--prompt", "1 2 3", "--tokens", "4", "--topk", "1"],
+                         capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert out.returncode == 0, out.stderr
+    assert len(out.stdout.strip().splitlines()[-1].split()) <= 4
+
+
+def replay(model_dir, dtype, steps, out_dir, max_tokens):
+    proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+                           "--out", out_dir, "--max-tokens", str(max_tokens)],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                          timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_program(dtype, model_dirs, plain_models, tmp_path):
+    """Unequal batch, requests that end early, a second batch in the freed room."""
+    name = "tiny_b"
+    cfg, w = plain_models[name]
+    vocab = cfg["vocab_size"]
+    reqs = {rid: r for rid, r in zip("abcdef", prompts_for(cfg, 31, [80, 20, 66, 41, 80, 9]))}
+    steps, wanted = [], {}
+
+    def batch(ids, prompt_lens, step0):
+        step = step0
+        pos = dict(zip(ids, prompt_lens))
+        entries = [{"id": i, "tokens": reqs[i][:pos[i]], "want": list(range(pos[i]))} for i in ids]
+        live = list(ids)
+        while live:
+            ends = [e["id"] for e in entries if pos[e["id"]] >= len(reqs[e["id"]])]
+            steps.append({"step": step, "entries": entries, "end": ends})
+            wanted[step] = [(e["id"], pos[e["id"]] - len(e["tokens"]) + k) for e in entries for k in e["want"]]
+            live = [i for i in live if i not in ends]
+            entries = [{"id": i, "tokens": [reqs[i][pos[i]]], "want": [0]} for i in live]
+            for i in live:
+                pos[i] += 1
+            step += 1
+        return step
+
+    nxt = batch(["a", "b", "c"], [50, 19, 64], 0)
+    batch(["d", "e", "f"], [1, 79, 9], nxt)
+    out_dir = str(tmp_path / f"out_{dtype}")
+    # a, b, c hold at most 128 + 64 + 128 positions; so do d, e, f
+    replay(model_dirs[name], dtype, steps, out_dir, max_tokens=320)
+    plain = {rid: plain_gpt2.forward(r, cfg, w) for rid, r in reqs.items()}
+    for s in steps:
+        got = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(-1, vocab)
+        want = np.stack([plain[rid][p] for rid, p in wanted[s["step"]]])
+        check_logits(got, want, dtype, f"replay step {s['step']}")

@@ -1,0 +1,257 @@
+"""Each kernel alone against a plain float64 statement of the same operation,
+at sizes other than the engine's (ragged, not powers of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a)).to("cuda", dtype)
+
+
+def assert_close(got, want, dtype, what=""):
+    """float32 results: max |diff| <= 1e-5 x rms of the expected values (the
+    reference's measure for kernels, src/gpu-testing.cpp:79-95).  bfloat16
+    results are rounded to 8 bits of mantissa on output, so each element may
+    be off by 2^-9 of its own size; allow 2^-7 of it plus 0.6 % of the rms for
+    the rounding of intermediate results."""
+    want = np.asarray(want, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    rms = max(np.sqrt((want ** 2).mean()), 1e-30)
+    diff = np.abs(got - want)
+    bound = 1e-5 * rms if dtype == "float32" else 2.0 ** -7 * np.abs(want) + 6e-3 * rms
+    worst = float((diff / bound).max()) if dtype != "float32" else float(diff.max() / bound)
+    assert worst <= 1.0, f"{what}: error is {worst:.2f} x the bound (rms {rms:.3g}, max |diff| {diff.max():.3g})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(0)
+    table = dev(rng.standard_normal((37, 72)), DT[dtype])
+    pos = dev(rng.standard_normal((19, 72)), DT[dtype])
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device="cuda")
+    p = torch.tensor([0, 18, 3, 4, 9], dtype=torch.int32, device="cuda")
+    got = ops.embed(ids, p, table, pos).cpu().numpy()
+    want = table.double().cpu().numpy()[ids.cpu()] + pos.double().cpu().numpy()[p.cpu()]
+    assert np.abs(got - want).max() < 1e-6
+    got = ops.embed(ids, None, table, None).cpu().numpy()
+    assert np.array_equal(got, table.float().cpu().numpy()[ids.cpu()])
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,eps", [(48, 1e-5), (1000, 1e-6), (1600, 1e-3)])
+def test_layernorm(hidden, eps, out_dtype):
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((11, hidden)) * 3 + 5).astype(np.float32)     # a mean far from zero
+    g = rng.standard_normal(hidden).astype(np.float32)
+    b = rng.standard_normal(hidden).astype(np.float32)
+    want = plain_gpt2.layer_norm(x.astype(np.float64), g.astype(np.float64), b.astype(np.float64), eps)
+    got = ops.layernorm(dev(x), dev(g), dev(b), eps, DT[out_dtype]).float().cpu().numpy()
+    assert_close(got, want, out_dtype, "layernorm")
+    rows = torch.tensor([10, 0, 3], dtype=torch.int32, device="cuda")
+    got = ops.layernorm(dev(x), dev(g), dev(b), eps, DT[out_dtype], rows=rows).float().cpu().numpy()
+    assert_close(got, want[[10, 0, 3]], out_dtype, "layernorm of picked rows")
+
+
+GEMM_SHAPES = [(1, 50, 24), (13, 77, 40), (64, 96, 320), (130, 257, 136), (5, 1031, 96), (200, 64, 8)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("act", [None, "gelu_new", "gelu"])
+def test_linear(m, n, k, act, dtype):
+    """Every product kernel behind ops.linear, with bias, activation and residual."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(m * 1000 + n)
+    a = dev(rng.standard_normal((m, k)), DT[dtype])
+    w = dev(rng.standard_normal((n, k)) / math.sqrt(k), DT[dtype])
+    bias = dev(rng.standard_normal(n))
+    res = dev(rng.standard_normal((m, n)))
+    z = a.double().cpu().numpy() @ w.double().cpu().numpy().T + bias.double().cpu().numpy()
+    if act:
+        z = plain_gpt2.ACTIVATIONS[act](z)
+    got = ops.linear(a, w, bias, act=act).float().cpu().numpy()
+    assert_close(got, z, dtype, "output in the compute dtype")
+    # float32 output of bfloat16 operands: only the accumulation differs from float64
+    got = ops.linear(a, w, bias, act=act, residual=res, out_dtype=torch.float32).cpu().numpy()
+    assert_close(got, z + res.double().cpu().numpy(), "float32", "with residual, float32 out")
+    x = res.clone()                                       # adding into the residual in place
+    ops.linear(a, w, bias, act=act, residual=x, out=x)
+    assert_close(x.cpu().numpy(), z + res.double().cpu().numpy(), "float32", "in place")
+    got = ops.linear(a, w, None, out_dtype=torch.float32).cpu().numpy()
+    assert_close(got, a.double().cpu().numpy() @ w.double().cpu().numpy().T, "float32", "no bias")
+
+
+def test_linear_rows_do_not_depend_on_the_batch():
+    """float32: a row's product is the same bits whatever else is in the batch."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(3)
+    a = dev(rng.standard_normal((70, 200)))
+    w = dev(rng.standard_normal((90, 200)))
+    full = ops.linear(a, w)
+    for rows in ([0], [69], list(range(5, 22))):
+        part = ops.linear(a[rows].contiguous(), w)
+        assert torch.equal(part, full[rows])
+
+
+def paged_setup(rng, seq_lens, n_kv_heads, head_dim, dtype, page=64, shuffle=True):
+    """Random keys/values laid into shuffled pages; returns them flat too."""
+    n_pages_seq = [-(-n // page) for n in seq_lens]
+    total = sum(n_pages_seq) + 3
+    order = rng.permutation(total) if shuffle else np.arange(total)
+    max_pages = max(n_pages_seq)
+    table = np.zeros((len(seq_lens), max_pages), dtype=np.int32)
+    kv = torch.zeros((total, 2, n_kv_heads, page, head_dim), dtype=DT[dtype], device="cuda")
+    ks, vs, nxt = [], [], 0
+    for s, n in enumerate(seq_lens):
+        k = dev(rng.standard_normal((n, n_kv_heads * head_dim)), DT[dtype])
+        v = dev(rng.standard_normal((n, n_kv_heads * head_dim)), DT[dtype])
+        ks.append(k); vs.append(v)
+        for i in range(n_pages_seq[s]):
+            table[s, i] = order[nxt]; nxt += 1
+    return kv, torch.as_tensor(table).cuda(), ks, vs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (4, 4, 16, 0), (6, 2, 48, 0), (3, 3, 80, 0), (8, 2, 128, 37), (5, 1, 256, 0), (2, 2, 64, 1), (4, 2, 32, 200)])
+def test_attention_over_pages(n_heads, n_kv_heads, head_dim, window, dtype):
+    """Whole prompts appended and attended in one call, then a single-token step
+    with the keys split over warps; any head count, grouping, size and window."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(head_dim + n_heads)
+    seq_lens = [1, 70, 129, 64]
+    kv, table, ks, vs = paged_setup(rng, seq_lens, n_kv_heads, head_dim, dtype)
+    tok_pos = torch.tensor([p for n in seq_lens for p in range(n)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([s for s, n in enumerate(seq_lens) for _ in range(n)], dtype=torch.int32, device="cuda")
+    k_all, v_all = torch.cat(ks), torch.cat(vs)
+    ops.kv_append(k_all, v_all, tok_pos, tok_seq, table, 64, n_kv_heads, head_dim, kv)
+    q_all = dev(rng.standard_normal((sum(seq_lens), n_heads * head_dim)), DT[dtype])
+    out = torch.empty_like(q_all)
+    scale = 0.37 / math.sqrt(head_dim)
+    ops.attention(q_all, out, kv, table, 64, tok_pos, tok_seq, n_heads, n_kv_heads, head_dim, scale, window)
+    o = 0
+    want_rows = []
+    for s, n in enumerate(seq_lens):
+        want = plain_gpt2.causal_attention(q_all[o:o + n].double().cpu().numpy(), ks[s].double().cpu().numpy(),
+                                           vs[s].double().cpu().numpy(), n_heads, n_kv_heads, scale, window)
+        assert_close(out[o:o + n].float().cpu().numpy(), want, dtype, f"sequence {s}")
+        want_rows.append(want[-1])
+        o += n
+    # single-token step for the last position of each sequence, keys split 5 ways
+    last = torch.tensor(np.cumsum(seq_lens) - 1, dtype=torch.int64, device="cuda")
+    q1 = q_all[last].contiguous()
+    pos1 = tok_pos[last].contiguous()
+    seq1 = torch.arange(len(seq_lens), dtype=torch.int32, device="cuda")
+    out1 = torch.empty_like(q1)
+    n_splits, split_keys = 5, 32
+    part_o = torch.full((len(seq_lens) * n_heads * n_splits * head_dim,), float("nan"), device="cuda")
+    part_ml = torch.full((len(seq_lens) * n_heads * n_splits * 2,), float("nan"), device="cuda")
+    ops.attention(q1, out1, kv, table, 64, pos1, seq1, n_heads, n_kv_heads, head_dim, scale, window,
+                  n_splits, split_keys, part_o, part_ml)
+    assert_close(out1.float().cpu().numpy(), np.stack(want_rows), dtype, "split keys")
+
+
+def test_attention_finds_a_far_key():
+    """One key among hundreds is made to dominate: the output must be its value.
+    Random scores would hide a wrong page or a dropped key."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(9)
+    n, heads, dh = 700, 2, 32
+    kv, table, ks, vs = paged_setup(rng, [n], heads, dh, "float32")
+    pos = torch.arange(n, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(n, dtype=torch.int32, device="cuda")
+    for target in (0, 63, 64, 383, 640, 699):
+        k = ks[0].clone()
+        q = dev(rng.standard_normal((1, heads * dh)))
+        k[target] = q[0] * 40.0                                # its score towers over the rest
+        ops.kv_append(k, vs[0], pos, seq, table, 64, heads, dh, kv)
+        out = torch.empty_like(q)
+        p1 = torch.tensor([n - 1], dtype=torch.int32, device="cuda")
+        s1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for n_splits in (1, 7):
+            part_o = torch.zeros(heads * n_splits * dh, device="cuda")
+            part_ml = torch.zeros(heads * n_splits * 2, device="cuda")
+            ops.attention(q, out, kv, table, 64, p1, s1, heads, heads, dh, 1.0, 0, n_splits, 128, part_o, part_ml)
+            assert torch.allclose(out[0], vs[0][target], atol=1e-4), (target, n_splits)
+
+
+def test_window_edge():
+    """The key just outside the window must not be seen, the one just inside must."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(4)
+    n, dh, window = 200, 16, 70
+    kv, table, ks, vs = paged_setup(rng, [n], 1, dh, "float32")
+    q = dev(rng.standard_normal((1, dh)))
+    pos = torch.arange(n, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(n, dtype=torch.int32, device="cuda")
+    p1 = torch.tensor([n - 1], dtype=torch.int32, device="cuda")
+    s1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    first_inside = n - window                      # position 130 is the oldest key the query sees
+    for target, seen in ((first_inside, True), (first_inside - 1, False)):
+        k = ks[0].clone()
+        k[target] = q[0] * 40.0
+        ops.kv_append(k, vs[0], pos, seq, table, 64, 1, dh, kv)
+        out = torch.empty_like(q)
+        ops.attention(q, out, kv, table, 64, p1, s1, 1, 1, dh, 1.0, window)
+        assert torch.allclose(out[0], vs[0][target], atol=1e-4) == seen
+
+
+def test_argmax_first_maximum_wins():
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((6, 50257)).astype(np.float32)
+    x[1, 777] = x[1, 40000] = 9.0
+    x[2, :] = -3.0                                  # all equal: index 0
+    x[3, 50256] = 11.0
+    got = ops.argmax(dev(x)).cpu().tolist()
+    assert got == [plain_gpt2.argmax(r) for r in x] and got[1] == 777 and got[2] == 0 and got[3] == 50256
+
+
+@pytest.mark.parametrize("vocab,top_k,temperature", [(1031, 0, 0.8), (1031, 20, 0.7), (50257, 40, 1.0),
+                                                      (513, 5, 1.5), (50257, 0, 1.0)])
+def test_sample_follows_the_plain_rule(vocab, top_k, temperature):
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(vocab + top_k)
+    rows = 24
+    x = (rng.standard_normal((rows, vocab)) * 2.5).astype(np.float32)
+    x[3, 5] = x[3, 9] = x[3].max() + 1.0           # tied leaders
+    x[4, :] = 0.25                                  # everything tied
+    req = torch.arange(100, 100 + rows, dtype=torch.int64, device="cuda")
+    draws = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    logits = dev(x)
+    for n in range(3):
+        got = ops.sample(logits, temperature, top_k, 42, req, draws).cpu().tolist()
+        for r in range(rows):
+            u = plain_gpt2.uniform_draw(42, 100 + r, n)
+            want, margin = plain_gpt2.sample_top_k(x[r], temperature, top_k, u)
+            # a disagreement is allowed only where u falls within rounding of a boundary
+            assert got[r] == want or margin < 1e-5, (r, n, got[r], want, margin)
+    assert draws.cpu().tolist() == [3] * rows
+
+
+def test_sample_distribution():
+    """Frequencies over many requests follow softmax(l / T) of the kept tokens."""
+    from math_utils_b200.csrc import ops
+    l = np.array([2.0, 1.0, 0.0, -1.0, 3.0, -5.0, 0.5], dtype=np.float32)
+    rows = 20000
+    logits = dev(np.tile(l, (rows, 1)))
+    req = torch.arange(rows, dtype=torch.int64, device="cuda")
+    draws = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    got = ops.sample(logits, 0.9, 4, 7, req, draws).cpu().numpy()
+    keep = np.argsort(-l)[:4]
+    p = np.exp(l[keep] / 0.9); p /= p.sum()
+    freq = np.array([(got == k).mean() for k in keep])
+    assert set(np.unique(got)) <= set(keep.tolist())
+    assert np.abs(freq - p).max() < 0.015

@@ -1,0 +1,174 @@
+"""Single-token steps of a fixed batch, replayed from one CUDA graph.
+
+Once a batch's prompts are in the cache, every further step has the same
+shape: one token per sequence.  A ``DecodeSession`` keeps that step's index
+arrays in fixed device buffers, captures the model's forward pass, the
+sampling and the hand-over of the sampled tokens to the next step in a CUDA
+graph once, and replays it: one launch per step instead of a hundred.  The
+kernels are the ones the eager step runs; only the launching differs.
+
+Two ways to drive it:
+  * ``feed(tokens, positions)`` then ``launch()`` then ``read_tokens()``: the
+    host supplies every step's inputs and reads every step's tokens (the
+    generation loop, which has to see stop tokens);
+  * ``launch()`` repeatedly: each step's samples are the next step's inputs on
+    the device (``advance``), with no host round trip between steps.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..sampling import SamplingParams
+from .batch import StepContext
+
+
+class DecodeSession:
+    def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
+                 request_ids: Sequence[int], kv_bound: Optional[int] = None):
+        self.model, self.cache = model, cache
+        self.slots = list(slots)
+        self.n = len(self.slots)
+        self.params = params
+        rt = model.runtime
+        dev = rt.device
+        n = self.n
+        self.kv_bound = int(kv_bound or model.max_positions)
+        self.tables_shape = [(n, g.max_pages) for g in cache.kv_groups]
+        sizes = [n, n, n, n, n] + [a * b for a, b in self.tables_shape]
+        offs = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])]).astype(int)
+        self._offs = offs
+        self.dev = torch.zeros(int(offs[-1]), dtype=torch.int32, device=dev)
+        self.host = torch.zeros(int(offs[-1]), dtype=torch.int32, pin_memory=True)
+        h = self.host.numpy()
+        h[offs[2]:offs[2] + n] = np.arange(n)            # tok_seq
+        h[offs[3]:offs[3] + n] = np.arange(n)            # want_rows: every token's logits
+        h[offs[4]:offs[4] + n] = np.asarray(self.slots)
+        self.dev.copy_(self.host)
+
+        def part(i, count):
+            return self.dev[int(offs[i]): int(offs[i]) + count]
+
+        self.token_ids, self.tok_pos = part(0, n), part(1, n)
+        self.block_tables = [part(5 + i, a * b).view(a, b) for i, (a, b) in enumerate(self.tables_shape)]
+        self.next_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.next_host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
+        self.request_ids = torch.tensor(list(request_ids), dtype=torch.int64, device=dev)
+        self.draws = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(
+            runtime=rt, position=model.assembly.position, n_tokens=n, n_seqs=n,
+            token_ids=self.token_ids, tok_pos=self.tok_pos, tok_seq=part(2, n), want_rows=part(3, n),
+            block_tables=self.block_tables, seq_slots=part(4, n), slots=self.slots, starts=[0] * n,
+            q_lens=[1] * n, max_q_len=1, max_kv_len=self.kv_bound, workspace={})
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+        self.logits: Optional[torch.Tensor] = None
+        self._tables_host = [None] * len(self.tables_shape)
+
+    def rebind(self, slots: Sequence[int], request_ids: Sequence[int], draws: Sequence[int]) -> None:
+        """Gives the session's places to another set of sequences of the same
+        number: their slots, their sampling streams and how far those have run."""
+        if len(slots) != self.n:
+            raise ValueError(f"this session steps {self.n} sequences, got {len(slots)}")
+        self.slots = list(slots)
+        self.ctx.slots = self.slots
+        h = self.host.numpy()
+        o = int(self._offs[4])
+        h[o:o + self.n] = np.asarray(self.slots, dtype=np.int32)
+        self.dev[o:o + self.n].copy_(self.host[o:o + self.n], non_blocking=True)
+        self.request_ids.copy_(torch.tensor(list(request_ids), dtype=torch.int64), non_blocking=False)
+        self.draws.copy_(torch.tensor(list(draws), dtype=torch.int32), non_blocking=False)
+        self._tables_host = [None] * len(self.tables_shape)
+        self._fed = False
+
+    # ------------------------------------------------------------------ inputs
+    def sync_block_tables(self) -> None:
+        """Sends the slots' page lists to the device where they changed."""
+        offs = self._offs
+        h = self.host.numpy()
+        for i, g in enumerate(self.cache.kv_groups):
+            rows = self.cache.block_table_rows(g.index, self.slots)
+            if self._tables_host[i] is None or not np.array_equal(rows, self._tables_host[i]):
+                self._tables_host[i] = rows.copy()
+                h[offs[5 + i]: offs[5 + i] + rows.size] = rows.reshape(-1)
+                self.dev[int(offs[5 + i]): int(offs[5 + i]) + rows.size].copy_(
+                    self.host[int(offs[5 + i]): int(offs[5 + i]) + rows.size], non_blocking=True)
+
+    def feed(self, tokens: Sequence[int], positions: Sequence[int]) -> int:
+        """This step's token and position of every sequence; returns the bytes
+        sent to the device."""
+        n = self.n
+        h = self.host.numpy()
+        h[0:n] = np.asarray(tokens, dtype=np.int32)
+        h[self._offs[1]: self._offs[1] + n] = np.asarray(positions, dtype=np.int32)
+        upto = int(self._offs[1]) + n
+        self.dev[:upto].copy_(self.host[:upto], non_blocking=True)
+        self._fed = True
+        return upto * 4
+
+    # ------------------------------------------------------------------- steps
+    def _run_once(self) -> None:
+        ops = self.model.runtime.ops
+        logits = self.model.forward(self.ctx, self.cache)
+        self.logits = logits
+        if self.params.greedy:
+            ops.argmax(logits, out=self.next_tokens)
+        else:
+            ops.sample(logits, self.params.temperature, self.params.top_k, self.params.seed,
+                       self.request_ids, self.draws, out=self.next_tokens)
+        ops.advance(self.token_ids, self.tok_pos, self.next_tokens, self.kv_bound - 1)
+
+    def capture(self) -> None:
+        """Runs the step once eagerly (first-use set-up must not happen inside a
+        capture), then records it.  The eager run writes keys and values at the
+        current positions and the capture runs nothing, so inputs and counters
+        are restored afterwards."""
+        if not getattr(self, "_fed", False):
+            raise RuntimeError("feed() the real tokens and positions before the first launch: the set-up run "
+                               "writes keys and values at the positions it is given")
+        ops = self.model.runtime.ops
+        saved = (self.token_ids.clone(), self.tok_pos.clone(), self.draws.clone())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._run_once()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._run_once()
+        self.launches_per_step = ops.launch_count - before
+        self.graph = graph
+        self.token_ids.copy_(saved[0]); self.tok_pos.copy_(saved[1]); self.draws.copy_(saved[2])
+
+    def launch(self) -> None:
+        if self.graph is None:
+            self.capture()
+        self.graph.replay()
+        self.model.runtime.ops.launch_count += self.launches_per_step
+
+    def read_tokens(self) -> List[int]:
+        """The tokens the last launched step sampled (waits for it)."""
+        self.next_host.copy_(self.next_tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.next_host.tolist()
+
+
+_SESSIONS_KEPT = 6
+
+
+def session_for(model, cache, params: SamplingParams, n: int) -> DecodeSession:
+    """A session of ``n`` sequences for this model, cache and sampling rule; the
+    last few are kept so that batch after batch replays the same graphs."""
+    kept = model.__dict__.setdefault("_decode_sessions", {})
+    key = (id(cache), n, params)
+    session = kept.pop(key, None)
+    if session is None or session.cache is not cache:
+        session = DecodeSession(model, cache, [0] * n, params, [0] * n, kv_bound=model.max_positions)
+    kept[key] = session                                  # most recently used last
+    while len(kept) > _SESSIONS_KEPT:
+        kept.pop(next(iter(kept)))
+    return session

@@ -114,9 +114,74 @@ def run_batch(step: Callable, sample: Callable, acquire: Callable, release: Call
             release(slot)
 
 
+def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[RequestState], stop_ids,
+                      max_tokens: int, context: int) -> None:
+    """The same batch as ``run_batch``, with the single-token steps replayed
+    from a CUDA graph (``DecodeSession``).  The prompts run as one eager step.
+    A finished request stays parked in the graph's batch (its last token at its
+    last position, so nothing of another sequence is touched) and keeps its slot
+    until the batch has halved, when the rest moves to a smaller graph."""
+    from .decode_session import session_for
+    ops = model.runtime.ops
+    slots = {}
+    try:
+        live = []
+        for k, st in enumerate(states):
+            if max_tokens <= 0 or len(st.prompt) >= context:
+                st.finished, st.reason = True, "max_tokens" if max_tokens <= 0 else "context"
+                continue
+            slots[k] = cache.acquire()
+            live.append(k)
+        if not live:
+            return
+        sampler = Sampler(params, [states[k].index for k in live], model.runtime.device, ops)
+        logits = model.step(cache, [StepEntry(slots[k], list(states[k].prompt), [len(states[k].prompt) - 1])
+                                    for k in live])
+        tokens = sampler.sample(logits).cpu().tolist()
+        draws = {k: 1 for k in live}
+        feed = {}
+        for k, tok in zip(list(live), tokens):
+            if take_token(states[k], int(tok), stop_ids, max_tokens, context):
+                feed[k] = int(tok)
+            else:
+                live.remove(k)
+                cache.release(slots.pop(k))
+        while live:
+            members = list(live)                         # the graph's batch; some may park later
+            session = session_for(model, cache, params, len(members))
+            session.rebind([slots[k] for k in members], [states[k].index for k in members],
+                           [draws[k] for k in members])
+            parked = set()
+            last = {k: (feed[k], cache.length(slots[k])) for k in members}
+            while live and (len(live) * 2 > len(members) or len(members) == 1):
+                for k in live:
+                    cache.reserve(slots[k], 1)
+                    last[k] = (feed[k], cache.length(slots[k]))
+                session.sync_block_tables()
+                session.feed([last[k][0] for k in members], [last[k][1] for k in members])
+                session.launch()
+                tokens = session.read_tokens()
+                for k in live:
+                    cache.commit(slots[k], 1)
+                    draws[k] += 1
+                for k, tok in zip(members, tokens):
+                    if k in parked:
+                        continue
+                    if take_token(states[k], int(tok), stop_ids, max_tokens, context):
+                        feed[k] = int(tok)
+                    else:
+                        parked.add(k)
+                        live.remove(k)
+            for k in parked:
+                cache.release(slots.pop(k))
+    finally:
+        for slot in slots.values():
+            cache.release(slot)
+
+
 def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams,
              stop_ids: Optional[Sequence[int]] = None, context: Optional[int] = None,
-             max_batch: int = 64, cache=None, request_offset: int = 0) -> List[List[int]]:
+             max_batch: int = 64, cache=None, request_offset: int = 0, use_graph: bool = True) -> List[List[int]]:
     """Generates a continuation for every prompt (lists of token ids)."""
     context = min(context or model.max_positions, model.max_positions)
     stop = frozenset(model.stop_ids if stop_ids is None else stop_ids)
@@ -125,7 +190,6 @@ def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: S
             raise ValueError(f"prompt {i} is empty")
         if len(p) > context:
             raise ValueError(f"prompt {i} has {len(p)} tokens, the context holds {context}")
-    page = None
     if cache is None:
         from ..cache import PAGE_TOKENS
         need = sorted((round_up(max(most_positions(len(p), max_tokens, context), 1), PAGE_TOKENS)
@@ -138,6 +202,9 @@ def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: S
     ops = model.runtime.ops
     for batch in batches:
         members = [states[i] for i in batch]
+        if use_graph and getattr(model, "graph_safe", True):
+            run_batch_graphed(model, cache, params, members, stop, max_tokens, context)
+            continue
         sampler = Sampler(params, [s.index for s in members], model.runtime.device, ops)
 
         def sample(logits, rows, sampler=sampler, n=len(members)):

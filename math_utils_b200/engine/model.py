@@ -37,6 +37,7 @@ class DecoderModel:
         self._ring = PinnedRing()
         self._workspace: dict = {}
         self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
+        self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.assembly.parts())
 
     # ---------------------------------------------------------------- loading
     @classmethod

@@ -70,6 +70,11 @@ class Part:
     """Base of all parts.  ``spec.params`` holds sizes and constants,
     ``spec.tensors`` the file names of the part's tensors."""
 
+    # False for a part whose forward pass reads host-side values of the step
+    # (``ctx.slots``, ``ctx.q_lens``): such a pass cannot be replayed from a CUDA
+    # graph, and generation then launches every step eagerly.
+    graph_safe = True
+
     def __init__(self, spec: PartSpec):
         self.spec = spec
 

@@ -151,6 +151,7 @@ def test_embedding_position_and_head_parts():
 class RunningMeanMixer(Mixer):
     """Output at a token = gain * mean of the inputs of all tokens so far.
     Keeps a fixed-size state per sequence: the running sum and the count."""
+    graph_safe = False          # walks the step's sequences on the host
 
     def __init__(self, spec):
         super().__init__(spec)

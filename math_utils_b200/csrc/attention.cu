@@ -265,3 +265,56 @@ MU_EXPORT int mu_attention(const void* q, long long ldq, void* out, long long ld
     }
     return MU_OK;
 }
+
+// ---------------------------------------------------------------------------
+// The variant for callers that cannot allocate: see attention_static_scratch.h.
+#include "attention_static_scratch.h"
+
+#include <mutex>
+
+// Scratch of the split attention, part of the loaded library on every device.
+static __device__ __align__(256) float mu_static_scratch[MU_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MU_MAX_DEVICES = 64;
+std::mutex static_scratch_mutex;
+float* static_scratch_address[MU_MAX_DEVICES] = {};
+
+// In host code `mu_static_scratch` is only a handle for the runtime, not an
+// address a kernel could use: the device address is asked for once per device.
+int static_scratch_for_current_device(float** ptr) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MU_MAX_DEVICES) return MU_ERR_SETUP;
+    std::lock_guard<std::mutex> lock(static_scratch_mutex);
+    if (!static_scratch_address[device]) {
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, mu_static_scratch) != cudaSuccess || !address) return MU_ERR_SETUP;
+        static_scratch_address[device] = (float*)address;
+    }
+    *ptr = static_scratch_address[device];
+    return MU_OK;
+}
+}  // namespace
+
+MU_EXPORT int mu_attention_static_scratch(const void* q, long long ldq, void* out, long long ldo,
+                                          const void* kv, const int* block_table, int max_pages,
+                                          int page_tokens, const int* tok_pos, const int* tok_seq,
+                                          int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                          float scale, int window, int n_splits, int split_keys,
+                                          int is_bf16, void* stream) {
+    if (n_tokens <= 0) return MU_OK;
+    if (n_heads <= 0 || head_dim <= 0 || n_splits < 1) return MU_ERR_BAD_ARGUMENT;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (n_splits > 1) {
+        const long long units = (long long)n_tokens * n_heads * n_splits;
+        if (units * (head_dim + 2) > (long long)MU_STATIC_SCRATCH_FLOATS) return MU_ERR_STATIC_SCRATCH;
+        float* base = nullptr;
+        if (int e = static_scratch_for_current_device(&base)) return e;
+        part_o = base;
+        part_ml = base + units * head_dim;
+    }
+    return mu_attention(q, ldq, out, ldo, kv, block_table, max_pages, page_tokens, tok_pos, tok_seq,
+                        n_tokens, n_heads, n_kv_heads, head_dim, scale, window, n_splits, split_keys,
+                        part_o, part_ml, is_bf16, stream);
+}

@@ -254,6 +254,47 @@ def run_ours(args):
     return 0
 
 
+def run_part(args):
+    """One part of the measurement on its own, optionally with fewer layers: a
+    small case for a profiler.  Prints a short JSON line; not a bench record."""
+    import numpy as np
+    import torch
+    from math_utils_b200 import LLM, Options, StepEntry, write_random_model
+    from math_utils_b200.sampling import SamplingParams
+    cfg = baseline_config()
+    if args.layers:
+        cfg["n_layer"] = args.layers
+    rng = np.random.default_rng(0)
+    with tempfile.TemporaryDirectory(prefix="mu_b200_bench_") as folder:
+        write_random_model(folder, cfg, seed=0)
+        llm = LLM(folder, Options(dtype="bfloat16", temperature=0.0, context=CONTEXT))
+    model = llm.model
+    model.stop_ids = ()
+    if args.only == "decode":
+        prompts = [rng.integers(0, cfg["vocab_size"], size=PROMPT_LEN).tolist() for _ in range(args.batch)]
+        seconds, launches, _ = time_decode(model, prompts, args.steps, args.warmup, SamplingParams(temperature=0.0))
+        print(json.dumps({"part": "decode", "batch": args.batch, "layers": cfg["n_layer"], "steps": args.steps,
+                          "ms_per_step": round(seconds / args.steps * 1e3, 4), "launches": launches}))
+    else:
+        pre = [rng.integers(0, cfg["vocab_size"], size=CONTEXT).tolist() for _ in range(PREFILL_SEQS)]
+        cache = model.new_cache(max_tokens=PREFILL_SEQS * CONTEXT, n_slots=PREFILL_SEQS)
+        times = []
+        for it in range(args.warmup + args.steps):
+            slots = [cache.acquire() for _ in pre]
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            model.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, pre)])
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+            for s in slots:
+                cache.release(s)
+        print(json.dumps({"part": "prefill", "tokens": PREFILL_SEQS * CONTEXT, "layers": cfg["n_layer"],
+                          "ms": round(statistics.median(times[args.warmup:]), 4)}))
+    return 0
+
+
 def run_reference(args):
     # The reference is a header-only C++ project with a makefile and no Python packaging, so the
     # offline `pip install --target baseline/_ref /root/reference` has nothing to install.
@@ -271,6 +312,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only and print a short line (for profiling a small case)")
+    ap.add_argument("--layers", type=int, default=0, help="with --only: fewer layers than the model has")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -278,6 +322,8 @@ def main():
         print(f"bench.py measures one GPU only: this library has no multi-GPU path (asked for {args.gpus})",
               flush=True)
         return 2
+    if args.only != "all":
+        return run_part(args)
     return run_ours(args)
 
 

@@ -1,0 +1,172 @@
+// C[M, N] = act(A[M, K] . W[N, K]^T + bias) (+ residual) for few rows (M <= 64), bfloat16.
+//
+// With a handful of rows the product is bound by reading W once from HBM, so
+// the kernel is built around streaming W: the weight rows are the 16-row
+// operand of mma.sync.m16n8k16 (bf16 in, fp32 accumulate) and the activations
+// the 8-column operand, so a warp turns 16 weight rows x 32 k into tensor-core
+// work for up to 64 activation rows without any shuffle or shared-memory
+// staging: each thread loads 16 contiguous bytes of a weight row and of an
+// activation row and feeds both to the same k slots of the instruction (the
+// sum over k does not care which k sits in which slot as long as both operands
+// agree).  A block is 8 warps laid out as WN groups of 16 weight rows x WK
+// slices of K; the slices are summed through shared memory in a fixed order,
+// then bias, activation and residual are applied and the result written with
+// consecutive threads on consecutive columns.
+//
+// This is the path of single-token steps (the reference runs them through
+// matmulNTBias, one dot product per output: include/ai/Kernels.hpp:433-447).
+#include "common.cuh"
+
+namespace mu {
+
+constexpr int SK_WARPS = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_stream(const __nv_bfloat16* p) {
+    // weights are read once per step: keep them out of L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int MT, int WN, int WK, typename TC>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                   const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
+                   long long lda, long long ldw, long long ldc, long long ldr, int act) {
+    static_assert(WN * WK == SK_WARPS, "a block is 8 warps");
+    constexpr int ROWS = 16 * WN;          // weight rows (output columns) per block
+    constexpr int MP = 8 * MT;             // activation rows, padded
+    __shared__ float red[WK][ROWS][MP + 1];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wn = warp % WN, wk = warp / WN;
+    const int g = lane >> 2, t = lane & 3;
+    const int n_base = blockIdx.x * ROWS + wn * 16;
+
+    // K is cut into WK slices on 32-element boundaries
+    const int k_blocks = (K + 31) / 32;
+    const int per = (k_blocks + WK - 1) / WK;
+    const int kb0 = wk * per, kb1 = min(k_blocks, kb0 + per);
+
+    // rows past the end are clamped for loading and dropped when writing
+    const int r0 = min(n_base + g, N - 1), r1 = min(n_base + g + 8, N - 1);
+    const __nv_bfloat16* w0 = W + (long long)r0 * ldw + 8 * t;
+    const __nv_bfloat16* w1 = W + (long long)r1 * ldw + 8 * t;
+    const __nv_bfloat16* xrow[MT];
+    bool xvalid[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        const int m = 8 * j + g;
+        xvalid[j] = m < M;
+        xrow[j] = A + (long long)min(m, M - 1) * lda + 8 * t;
+    }
+
+    float acc[MT][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+
+    constexpr int UNROLL = 4;
+    for (int kb = kb0; kb < kb1; kb += UNROLL) {
+        uint4 wa[UNROLL], wb[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (kb + u) * 32;
+            const bool in = (kb + u) < kb1 && (k + 8 * t) < K;      // K is a multiple of 8
+            wa[u] = in ? load_stream(w0 + k) : make_uint4(0, 0, 0, 0);
+            wb[u] = in ? load_stream(w1 + k) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (kb + u) * 32;
+            const bool in = (kb + u) < kb1 && (k + 8 * t) < K;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                uint4 xb = make_uint4(0, 0, 0, 0);
+                if (in && xvalid[j]) xb = *reinterpret_cast<const uint4*>(xrow[j] + k);
+                mma_bf16_16816(acc[j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
+                mma_bf16_16816(acc[j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
+            }
+        }
+    }
+
+    // accumulator layout: c0,c1 = (weight row g, activation rows 8j+2t, +1); c2,c3 = weight row g+8
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        red[wk][wn * 16 + g][8 * j + 2 * t] = acc[j][0];
+        red[wk][wn * 16 + g][8 * j + 2 * t + 1] = acc[j][1];
+        red[wk][wn * 16 + g + 8][8 * j + 2 * t] = acc[j][2];
+        red[wk][wn * 16 + g + 8][8 * j + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();
+    const int col0 = blockIdx.x * ROWS;
+    for (int idx = threadIdx.x; idx < ROWS * M; idx += SK_WARPS * 32) {
+        const int m = idx / ROWS, r = idx % ROWS;
+        const int n = col0 + r;
+        if (n >= N) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int s = 0; s < WK; ++s) v += red[s][r][m];
+        if (bias) v += bias[n];
+        v = apply_act(v, act);
+        if (residual) v += residual[(long long)m * ldr + n];
+        C[(long long)m * ldc + n] = from_float<TC>(v);
+    }
+}
+
+template <int MT, typename TC>
+static int launch_skinny(const __nv_bfloat16* A, const __nv_bfloat16* W, const float* bias,
+                         const float* residual, TC* C, int M, int N, int K, long long lda, long long ldw,
+                         long long ldc, long long ldr, int act, cudaStream_t s) {
+    // few output columns: cut K over the warps so that enough blocks exist; many: whole K per warp
+#define MU_SK(WN, WK)                                                                              \
+    gemm_skinny_kernel<MT, WN, WK, TC><<<(N + 16 * WN - 1) / (16 * WN), SK_WARPS * 32, 0, s>>>(     \
+        A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act)
+    if (N >= 16 * 8 * 296 && K <= 2048) MU_SK(8, 1);
+    else if (N >= 16 * 4 * 296) MU_SK(4, 2);
+    else if (N >= 16 * 2 * 296) MU_SK(2, 4);
+    else MU_SK(1, 8);
+#undef MU_SK
+    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+}
+
+}  // namespace mu
+
+// bfloat16 A [M, K] and W [N, K] with K, lda and ldw multiples of 8 and 16-byte aligned bases;
+// M <= 64.  C is bfloat16 or float32; residual float32 (may be C itself).
+MU_EXPORT int mu_gemm_skinny(const void* A, const void* W, const float* bias, const float* residual,
+                             void* C, int M, int N, int K, long long lda, long long ldw, long long ldc,
+                             long long ldr, int act, int out_bf16, void* stream) {
+    if (M <= 0 || N <= 0) return MU_OK;
+    if (K <= 0 || !A || !W || !C) return MU_ERR_BAD_ARGUMENT;
+    if (M > 64) return MU_ERR_UNSUPPORTED_SIZE;
+    if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return MU_ERR_ALIGNMENT;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return MU_ERR_ALIGNMENT;
+    if (lda < K || ldw < K || ldc < N || (residual && ldr < N)) return MU_ERR_BAD_ARGUMENT;
+    const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)W;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int mt = (M + 7) / 8;
+#define MU_MT(MT)                                                                                      \
+    (out_bf16 ? mu::launch_skinny<MT, __nv_bfloat16>(a, w, bias, residual, (__nv_bfloat16*)C, M, N, K, \
+                                                     lda, ldw, ldc, ldr, act, s)                       \
+              : mu::launch_skinny<MT, float>(a, w, bias, residual, (float*)C, M, N, K, lda, ldw, ldc,  \
+                                             ldr, act, s))
+    if (mt <= 1) return MU_MT(1);
+    if (mt <= 2) return MU_MT(2);
+    if (mt <= 4) return MU_MT(4);
+    return MU_MT(8);
+#undef MU_MT
+}

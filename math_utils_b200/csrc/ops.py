@@ -40,6 +40,8 @@ _SIGNATURES = {
     "mu_layernorm": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p],
     "mu_gemm_simt": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                      _c_int, _c_int, _c_int, _c_p],
+    "mu_gemm_skinny": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
+                       _c_int, _c_int, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_p, _c_int, _c_p],
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
@@ -200,6 +202,27 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     return out
 
 
+def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether gemm_skinny takes this product: bfloat16, at most 64 rows, k and
+    both row strides multiples of 8 elements, 16-byte aligned bases."""
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= 64 and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The product for a few rows (single-token steps): streams the weights once
+    through mma.sync with the weight rows as the wide operand."""
+    m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
+    _check(library().mu_gemm_skinny(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
+        out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
+        _is_bf16(out), _stream()), f"gemm_skinny({m}x{n}x{k})")
+    return out
+
+
 # ------------------------------------------------------------------- attention
 def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: torch.Tensor,
               page_tokens: int, n_kv_heads: int, head_dim: int, kv_pages: torch.Tensor) -> None:
@@ -284,4 +307,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """act(x @ weight^T + bias) + residual through the kernel that fits the
     dtype and the shape.  float32 operands always take the CUDA-core kernel."""
+    if skinny_ok(x, weight):
+        return gemm_skinny(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
     return gemm_simt(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

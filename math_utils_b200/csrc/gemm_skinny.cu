@@ -39,15 +39,51 @@ __device__ __forceinline__ uint4 load_stream(const __nv_bfloat16* p) {
     return v;
 }
 
-template <int MT, int WN, int WK, typename TC>
+// With LN the activations are not given but made: row m of A is the LayerNorm
+// of row ln_rows[m] (or m) of the float32 matrix ln_x, computed by the block
+// into shared memory as bfloat16 (mean and biased variance in float32, as
+// mu_layernorm does), so that the norm costs no launch of its own.
+struct SkinnyNorm {
+    const float* x;
+    const int* rows;
+    const float* gamma;
+    const float* beta;
+    long long ldx;
+    float eps;
+};
+
+template <int MT, int WN, int WK, typename TC, bool LN>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
-                   long long lda, long long ldw, long long ldc, long long ldr, int act) {
+                   long long lda, long long ldw, long long ldc, long long ldr, int act, SkinnyNorm norm) {
     static_assert(WN * WK == SK_WARPS, "a block is 8 warps");
     constexpr int ROWS = 16 * WN;          // weight rows (output columns) per block
     constexpr int MP = 8 * MT;             // activation rows, padded
     __shared__ float red[WK][ROWS][MP + 1];
+    extern __shared__ __align__(16) unsigned char skinny_dyn[];
+    __nv_bfloat16* act_smem = reinterpret_cast<__nv_bfloat16*>(skinny_dyn);   // [MP][K + 8] with LN
+    const int act_ld = K + 8;              // rows 16 bytes apart modulo 128: no bank conflicts
+    if (LN) {
+        const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+        for (int m = w; m < MP; m += SK_WARPS) {
+            __nv_bfloat16* dst = act_smem + (long long)m * act_ld;
+            if (m >= M) {
+                for (int k = ln; k < K; k += 32) dst[k] = __float2bfloat16_rn(0.0f);
+                continue;
+            }
+            const float* src = norm.x + (long long)(norm.rows ? norm.rows[m] : m) * norm.ldx;
+            float sum = 0.0f;
+            for (int k = ln; k < K; k += 32) sum += src[k];
+            const float mean = warp_sum(sum) / (float)K;
+            float sq = 0.0f;
+            for (int k = ln; k < K; k += 32) { const float c = src[k] - mean; sq += c * c; }
+            const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+            for (int k = ln; k < K; k += 32)
+                dst[k] = __float2bfloat16_rn((src[k] - mean) * inv * norm.gamma[k] + (norm.beta ? norm.beta[k] : 0.0f));
+        }
+        __syncthreads();
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wn = warp % WN, wk = warp / WN;
@@ -68,8 +104,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
         const int m = 8 * j + g;
-        xvalid[j] = m < M;
-        xrow[j] = A + (long long)min(m, M - 1) * lda + 8 * t;
+        xvalid[j] = LN || m < M;           // padded rows of the shared copy hold zeros
+        xrow[j] = LN ? act_smem + (long long)m * act_ld + 8 * t : A + (long long)min(m, M - 1) * lda + 8 * t;
     }
 
     float acc[MT][4];
@@ -126,23 +162,70 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     }
 }
 
-template <int MT, typename TC>
+template <int MT, int WN, int WK, typename TC, bool LN>
+static int launch_skinny_as(const __nv_bfloat16* A, const __nv_bfloat16* W, const float* bias,
+                            const float* residual, TC* C, int M, int N, int K, long long lda, long long ldw,
+                            long long ldc, long long ldr, int act, const SkinnyNorm& norm, cudaStream_t s) {
+    auto kernel = gemm_skinny_kernel<MT, WN, WK, TC, LN>;
+    size_t dyn = 0;
+    if (LN) {
+        dyn = (size_t)8 * MT * (K + 8) * sizeof(__nv_bfloat16);
+        if (dyn > 160 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+        if (dyn > 40 * 1024) {
+            // more than the default limit allows next to the static part; asked for once per variant
+            static bool raised = false;
+            if (!raised) {
+                if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) !=
+                    cudaSuccess)
+                    return MU_ERR_LAUNCH;
+                raised = true;
+            }
+        }
+    }
+    kernel<<<(N + 16 * WN - 1) / (16 * WN), SK_WARPS * 32, dyn, s>>>(A, W, bias, residual, C, M, N, K, lda,
+                                                                     ldw, ldc, ldr, act, norm);
+    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+}
+
+template <int MT, typename TC, bool LN>
 static int launch_skinny(const __nv_bfloat16* A, const __nv_bfloat16* W, const float* bias,
                          const float* residual, TC* C, int M, int N, int K, long long lda, long long ldw,
-                         long long ldc, long long ldr, int act, cudaStream_t s) {
+                         long long ldc, long long ldr, int act, const SkinnyNorm& norm, cudaStream_t s) {
     // few output columns: cut K over the warps so that enough blocks exist; many: whole K per warp
-#define MU_SK(WN, WK)                                                                              \
-    gemm_skinny_kernel<MT, WN, WK, TC><<<(N + 16 * WN - 1) / (16 * WN), SK_WARPS * 32, 0, s>>>(     \
-        A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act)
+#define MU_SK(WN, WK) \
+    return launch_skinny_as<MT, WN, WK, TC, LN>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act, norm, s)
     if (N >= 16 * 8 * 296 && K <= 2048) MU_SK(8, 1);
     else if (N >= 16 * 4 * 296) MU_SK(4, 2);
     else if (N >= 16 * 2 * 296) MU_SK(2, 4);
     else MU_SK(1, 8);
 #undef MU_SK
-    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
 }
 
 }  // namespace mu
+
+static int skinny_dispatch(const __nv_bfloat16* a, const __nv_bfloat16* w, const float* bias,
+                           const float* residual, void* C, int M, int N, int K, long long lda, long long ldw,
+                           long long ldc, long long ldr, int act, int out_bf16, const mu::SkinnyNorm* norm,
+                           cudaStream_t s) {
+    const int mt = (M + 7) / 8;
+    const mu::SkinnyNorm none = {};
+#define MU_MT(MT, LN)                                                                                         \
+    (out_bf16 ? mu::launch_skinny<MT, __nv_bfloat16, LN>(a, w, bias, residual, (__nv_bfloat16*)C, M, N, K,   \
+                                                         lda, ldw, ldc, ldr, act, norm ? *norm : none, s)     \
+              : mu::launch_skinny<MT, float, LN>(a, w, bias, residual, (float*)C, M, N, K, lda, ldw, ldc,     \
+                                                 ldr, act, norm ? *norm : none, s))
+    if (norm) {
+        if (mt <= 1) return MU_MT(1, true);
+        if (mt <= 2) return MU_MT(2, true);
+        if (mt <= 4) return MU_MT(4, true);
+        return MU_MT(8, true);
+    }
+    if (mt <= 1) return MU_MT(1, false);
+    if (mt <= 2) return MU_MT(2, false);
+    if (mt <= 4) return MU_MT(4, false);
+    return MU_MT(8, false);
+#undef MU_MT
+}
 
 // bfloat16 A [M, K] and W [N, K] with K, lda and ldw multiples of 8 and 16-byte aligned bases;
 // M <= 64.  C is bfloat16 or float32; residual float32 (may be C itself).
@@ -155,18 +238,23 @@ MU_EXPORT int mu_gemm_skinny(const void* A, const void* W, const float* bias, co
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return MU_ERR_ALIGNMENT;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return MU_ERR_ALIGNMENT;
     if (lda < K || ldw < K || ldc < N || (residual && ldr < N)) return MU_ERR_BAD_ARGUMENT;
-    const __nv_bfloat16* a = (const __nv_bfloat16*)A;
-    const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-    cudaStream_t s = (cudaStream_t)stream;
-    const int mt = (M + 7) / 8;
-#define MU_MT(MT)                                                                                      \
-    (out_bf16 ? mu::launch_skinny<MT, __nv_bfloat16>(a, w, bias, residual, (__nv_bfloat16*)C, M, N, K, \
-                                                     lda, ldw, ldc, ldr, act, s)                       \
-              : mu::launch_skinny<MT, float>(a, w, bias, residual, (float*)C, M, N, K, lda, ldw, ldc,  \
-                                             ldr, act, s))
-    if (mt <= 1) return MU_MT(1);
-    if (mt <= 2) return MU_MT(2);
-    if (mt <= 4) return MU_MT(4);
-    return MU_MT(8);
-#undef MU_MT
+    return skinny_dispatch((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, residual, C, M, N, K, lda,
+                           ldw, ldc, ldr, act, out_bf16, nullptr, (cudaStream_t)stream);
+}
+
+// The same product with A = LayerNorm(x[rows]) made inside the kernel: x float32 [*, K] with leading
+// dimension ldx, rows optional int32 [M], gamma and beta (optional) float32 [K].
+MU_EXPORT int mu_gemm_skinny_ln(const float* x, long long ldx, const int* rows, const float* gamma,
+                                const float* beta, float eps, const void* W, const float* bias,
+                                const float* residual, void* C, int M, int N, int K, long long ldw,
+                                long long ldc, long long ldr, int act, int out_bf16, void* stream) {
+    if (M <= 0 || N <= 0) return MU_OK;
+    if (K <= 0 || !x || !gamma || !W || !C) return MU_ERR_BAD_ARGUMENT;
+    if (M > 64) return MU_ERR_UNSUPPORTED_SIZE;
+    if (K % 8 != 0 || ldw % 8 != 0) return MU_ERR_ALIGNMENT;
+    if ((uintptr_t)W & 15) return MU_ERR_ALIGNMENT;
+    if (ldx < K || ldw < K || ldc < N || (residual && ldr < N)) return MU_ERR_BAD_ARGUMENT;
+    const mu::SkinnyNorm norm = {x, rows, gamma, beta, ldx, eps};
+    return skinny_dispatch(nullptr, (const __nv_bfloat16*)W, bias, residual, C, M, N, K, 0, ldw, ldc, ldr,
+                           act, out_bf16, &norm, (cudaStream_t)stream);
 }

@@ -47,7 +47,12 @@ _SIGNATURES = {
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
                      _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p],
     "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
-    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p],
+    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p],
+    "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
+                          _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
+    "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
+                            _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p,
+                            _c_int, _c_p],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p],
 }
 
@@ -118,6 +123,25 @@ def _is_bf16(t: torch.Tensor) -> int:
 def _i32(t: Optional[torch.Tensor], name: str) -> None:
     if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
         raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+_workspaces = {}
+_retired = []
+
+
+def zeroed_workspace(name: str, device, n_bytes: int) -> torch.Tensor:
+    """A device buffer that kernels with tickets use and leave zero again.  It
+    is kept per purpose and device and only ever grows, so its address stays put
+    for launches recorded in a CUDA graph as long as no larger size is asked for
+    later."""
+    key = (name, str(device))
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < n_bytes:
+        if buf is not None:
+            _retired.append(buf)        # a recorded graph may still point at it
+        buf = torch.zeros(max(n_bytes, 65536), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
 
 
 # ------------------------------------------------------------------ elementwise
@@ -277,7 +301,8 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     n, vocab = logits.shape
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
-    _check(library().mu_argmax(_ptr(logits), logits.stride(0), n, vocab, _ptr(out), _stream()), "argmax")
+    ws = zeroed_workspace("argmax", logits.device, 2 * n * 8)
+    _check(library().mu_argmax(_ptr(logits), logits.stride(0), n, vocab, _ptr(out), _ptr(ws), _stream()), "argmax")
     return out
 
 
@@ -301,12 +326,84 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
     return out
 
 
+class NormedInput:
+    """The LayerNorm of (rows of) a float32 matrix that has not been computed
+    yet: a product kernel that can make it on the fly takes this instead of a
+    tensor; anything else calls ``materialize``."""
+
+    def __init__(self, x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float,
+                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
+        self.x, self.gamma, self.beta, self.eps, self.out_dtype, self.rows = x, gamma, beta, eps, out_dtype, rows
+        self._value = None
+
+    @property
+    def n_rows(self) -> int:
+        return self.rows.numel() if self.rows is not None else self.x.shape[0]
+
+    def materialize(self) -> torch.Tensor:
+        if self._value is None:
+            self._value = layernorm(self.x, self.gamma, self.beta, self.eps, self.out_dtype, rows=self.rows)
+        return self._value
+
+
+def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, out_dtype) -> torch.Tensor:
+    """act(LayerNorm(x) @ w^T + bias) + residual with the norm made inside the product kernel."""
+    _need_cuda(x.x, w, bias, residual, out, x.rows)
+    m, k, n = x.n_rows, x.x.shape[1], w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or w.dtype, device=w.device)
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != n):
+        raise KernelError("gemm bias must be float32 of length n")
+    if residual is not None and (residual.dtype != torch.float32 or residual.shape != (m, n)):
+        raise KernelError("gemm residual must be float32 [m, n]")
+    _check(library().mu_gemm_skinny_ln(
+        _ptr(x.x), x.x.stride(0), _ptr(x.rows), _ptr(x.gamma), _ptr(x.beta), float(x.eps), _ptr(w), _ptr(bias),
+        _ptr(residual), _ptr(out), m, n, k, w.stride(0), out.stride(0),
+        residual.stride(0) if residual is not None else 0, ACT_CODES[act], _is_bf16(out), _stream()),
+        f"gemm_skinny_ln({m}x{n}x{k})")
+    return out
+
+
+def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
+                     out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, page_tokens: int,
+                     tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                     window: int, n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor) -> torch.Tensor:
+    """Single-token attention, one launch: appends ``k_new`` / ``v_new`` (if
+    given), attends page by page, merges.  ``n_splits``: pages per sequence to
+    cover (the longest sequence's page count at least)."""
+    _need_cuda(q, k_new, v_new, out, kv_pages, block_table, tok_pos, tok_seq, part_o, part_ml)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    n_tokens = q.shape[0]
+    tickets = zeroed_workspace("attention_tickets", q.device, n_tokens * n_heads * 4)
+    need_o = n_tokens * n_heads * n_splits * head_dim
+    if n_splits > 1 and (part_o is None or part_ml is None or part_o.numel() < need_o
+                         or part_ml.numel() < n_tokens * n_heads * n_splits * 2):
+        raise KernelError("split attention needs float32 scratch for its partial results")
+    _check(library().mu_attention_decode(
+        _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
+        v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
+        _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml),
+        _ptr(tickets), _is_bf16(kv_pages), _stream()),
+        f"attention_decode(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+    return out
+
+
 # -------------------------------------------------------------------- dispatch
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """act(x @ weight^T + bias) + residual through the kernel that fits the
-    dtype and the shape.  float32 operands always take the CUDA-core kernel."""
+    dtype and the shape.  float32 operands always take the CUDA-core kernel.
+    ``x`` may be a ``NormedInput``: with few rows and bfloat16 weights the norm is
+    made inside the product kernel, otherwise it is computed first."""
+    if isinstance(x, NormedInput):
+        if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 16
+                and x.x.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
+                and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
+            return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
+        x = x.materialize()
     if skinny_ok(x, weight):
         return gemm_skinny(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
     return gemm_simt(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

@@ -44,12 +44,22 @@ __device__ __forceinline__ double uniform_draw(unsigned long long seed, unsigned
     return (double)(x >> 11) * (1.0 / 9007199254740992.0);
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out) {
-    __shared__ unsigned long long best_smem[32];
-    const float* row = logits + (long long)blockIdx.x * ld;
+// The vocabulary of a row is cut over ARGMAX_PARTS blocks.  Each folds (key, ~index) pairs into one
+// 64-bit maximum in global memory; the block that takes the row's last ticket writes the token and
+// puts the workspace back to zero for the next launch.
+constexpr int ARGMAX_THREADS = 256;
+constexpr int ARGMAX_PARTS = 16;
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out,
+              unsigned long long* __restrict__ best_ws, unsigned int* __restrict__ ticket_ws) {
+    __shared__ unsigned long long best_smem[ARGMAX_THREADS / 32];
+    const int r = blockIdx.x;
+    const float* row = logits + (long long)r * ld;
+    const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+    const int begin = blockIdx.y * per, end = min(vocab, begin + per);
     unsigned long long best = 0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         // larger logit wins; among equals the lower index (larger ~index) wins
         const unsigned long long cand =
             ((unsigned long long)float_key(row[i]) << 32) | (unsigned int)(0xFFFFFFFFu - (unsigned)i);
@@ -62,14 +72,17 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __
     }
     if ((threadIdx.x & 31) == 0) best_smem[threadIdx.x >> 5] = best;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        best = threadIdx.x < (blockDim.x >> 5) ? best_smem[threadIdx.x] : 0ull;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-            best = other > best ? other : best;
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < ARGMAX_THREADS / 32; ++w) best = best_smem[w] > best ? best_smem[w] : best;
+        atomicMax(&best_ws[r], best);
+        __threadfence();
+        const unsigned int ticket = atomicAdd(&ticket_ws[r], 1u);
+        if (ticket == ARGMAX_PARTS - 1) {
+            __threadfence();
+            const unsigned long long all = atomicExch(&best_ws[r], 0ull);
+            ticket_ws[r] = 0;
+            out[r] = (int)(0xFFFFFFFFu - (unsigned int)(all & 0xFFFFFFFFull));
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(best & 0xFFFFFFFFull));
     }
 }
 
@@ -274,11 +287,15 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
 
 }  // namespace mu
 
-// logits [n_rows, ld] float32 -> out[n_rows] token ids.
-MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, void* stream) {
+// logits [n_rows, ld] float32 -> out[n_rows] token ids.  workspace: 2 * n_rows 64-bit words that are
+// zero before the first launch (each launch leaves them zero).
+MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out,
+                        unsigned long long* workspace, void* stream) {
     if (n_rows <= 0) return MU_OK;
-    if (!logits || !out || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
-    mu::argmax_kernel<<<n_rows, mu::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+    if (!logits || !out || !workspace || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
+    dim3 grid(n_rows, mu::ARGMAX_PARTS);
+    mu::argmax_kernel<<<grid, mu::ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(
+        logits, ld, vocab, out, workspace, reinterpret_cast<unsigned int*>(workspace + n_rows));
     MU_CHECK_LAUNCH();
     return MU_OK;
 }

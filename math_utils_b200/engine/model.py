@@ -99,5 +99,6 @@ class DecoderModel:
             layer.arrangement.forward(x, layer, ctx, cache.entry(entry.cache_of), entry.cache_of == i)
         if ctx.want_rows is None:
             return None
-        h = a.final_norm.forward(x, rows=ctx.want_rows)
+        lazy = getattr(a.head, "takes_lazy_norm", False)
+        h = a.final_norm.lazy(x, rows=ctx.want_rows) if lazy else a.final_norm.forward(x, rows=ctx.want_rows)
         return a.head.forward(h)

@@ -18,6 +18,8 @@ from .linear import Linear
 
 
 class CausalSelfAttention(Mixer):
+    takes_lazy_norm = True
+
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.hidden_size = int(self.param("hidden_size"))
@@ -61,14 +63,22 @@ class CausalSelfAttention(Mixer):
         v = qkv[:, self.q_width + self.kv_width:]
         ctx.position.rotate(q, k, ctx)
         table = ctx.block_tables[cache.group]
-        if owns_cache:
-            ops.kv_append(k, v, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens,
-                          self.n_kv_heads, self.head_dim, cache.pages)
         attn = torch.empty((ctx.n_tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
-        n_splits, split_keys, part_o, part_ml = ctx.attention_splits(self.n_heads, self.head_dim)
-        ops.attention(q, attn, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq,
-                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window,
-                      n_splits, split_keys, part_o, part_ml)
+        if ctx.is_decode and cache.page_tokens == 64:
+            # one launch: append this token's key and value, attend page by page, merge
+            n_pages, part_o, part_ml = ctx.decode_scratch(self.n_heads, self.head_dim, cache.page_tokens)
+            ops.attention_decode(q, k if owns_cache else None, v if owns_cache else None, attn, cache.pages,
+                                 table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, self.n_heads,
+                                 self.n_kv_heads, self.head_dim, self.scale, self.window, n_pages,
+                                 part_o, part_ml)
+        else:
+            if owns_cache:
+                ops.kv_append(k, v, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens,
+                              self.n_kv_heads, self.head_dim, cache.pages)
+            n_splits, split_keys, part_o, part_ml = ctx.attention_splits(self.n_heads, self.head_dim)
+            ops.attention(q, attn, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq,
+                          self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window,
+                          n_splits, split_keys, part_o, part_ml)
         self.out(attn, residual=residual, out=residual)
 
 

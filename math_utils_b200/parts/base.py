@@ -112,6 +112,8 @@ class Mixer(Part):
     belongs to an earlier layer and is only read.
     """
 
+    takes_lazy_norm = False          # see FeedForward
+
     def cache_spec(self):
         return None
 
@@ -120,7 +122,12 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """``forward(h, residual, ctx)``: adds its result into ``residual``."""
+    """``forward(h, residual, ctx)``: adds its result into ``residual``.  A
+    feed-forward (or mixer) that sets ``takes_lazy_norm`` may be handed a
+    ``NormedInput`` (a norm not computed yet) instead of a tensor as ``h`` and
+    passes it to its first ``Linear``, which folds the norm into the product
+    where it can."""
+    takes_lazy_norm = False
 
     def forward(self, h, residual, ctx) -> None:
         raise NotImplementedError
@@ -132,6 +139,11 @@ class Norm(Part):
 
     def forward(self, x, rows=None):
         raise NotImplementedError
+
+    def lazy(self, x, rows=None):
+        """The norm as a ``NormedInput`` for a consumer that may fold it into
+        its product; a norm that cannot be folded returns the computed tensor."""
+        return self.forward(x, rows)
 
 
 class PositionEncoding(Part):

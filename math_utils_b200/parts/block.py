@@ -11,9 +11,9 @@ from .base import Arrangement, register_part
 
 class PreNormBlock(Arrangement):
     def forward(self, x, layer, ctx, cache, owns_cache: bool) -> None:
-        h = layer.norm1.forward(x)
+        h = layer.norm1.lazy(x) if layer.mixer.takes_lazy_norm else layer.norm1.forward(x)
         layer.mixer.forward(h, x, ctx, cache, owns_cache)
-        h = layer.norm2.forward(x)
+        h = layer.norm2.lazy(x) if layer.feed_forward.takes_lazy_norm else layer.norm2.forward(x)
         layer.feed_forward.forward(h, x, ctx)
 
 

@@ -44,6 +44,8 @@ class TiedHead(Head):
             raise ValueError("the tied head and the token table disagree on their sizes")
         self.linear = Linear(table, None, self.runtime)
 
+    takes_lazy_norm = True
+
     def forward(self, h):
         import torch
         return self.linear(h, out_dtype=torch.float32)

@@ -12,6 +12,8 @@ ACTIVATIONS = ("gelu_new", "gelu")
 
 
 class DenseFeedForward(FeedForward):
+    takes_lazy_norm = True
+
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.hidden_size = int(self.param("hidden_size"))

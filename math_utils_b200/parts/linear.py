@@ -25,5 +25,5 @@ class Linear:
                  out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         ops = self.runtime.ops
         if out is None and out_dtype is None:
-            out_dtype = torch.float32 if residual is not None else x.dtype
+            out_dtype = torch.float32 if residual is not None else getattr(x, "out_dtype", None) or x.dtype
         return ops.linear(x, self.weight, self.bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

@@ -26,3 +26,10 @@ class LayerNorm(Norm):
 
 
 register_part("norm", "layer_norm", LayerNorm, replace=True)
+
+
+def _lazy(self, x, rows=None):
+    return self.runtime.ops.NormedInput(x, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)
+
+
+LayerNorm.lazy = _lazy

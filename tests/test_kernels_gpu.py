@@ -255,3 +255,68 @@ def test_sample_distribution():
     freq = np.array([(got == k).mean() for k in keep])
     assert set(np.unique(got)) <= set(keep.tolist())
     assert np.abs(freq - p).max() < 0.015
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (4, 4, 16, 0), (6, 2, 48, 0), (3, 3, 80, 0), (8, 2, 128, 70), (5, 1, 256, 0), (12, 12, 64, 0), (4, 2, 32, 1)])
+def test_single_token_attention_kernel(n_heads, n_kv_heads, head_dim, window, dtype):
+    """The one-launch kernel of single-token steps: the new key and value come
+    from the step's projections and are appended by the kernel itself."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(7 * head_dim + n_heads)
+    seq_lens = [1, 64, 65, 200, 129, 448]
+    kv, table, ks, vs = paged_setup(rng, seq_lens, n_kv_heads, head_dim, dtype)
+    # the cache holds all but the last token of every sequence
+    tok_pos = torch.tensor([p for n in seq_lens for p in range(n - 1)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([s for s, n in enumerate(seq_lens) for _ in range(n - 1)], dtype=torch.int32, device="cuda")
+    ops.kv_append(torch.cat([k[:-1] for k in ks]), torch.cat([v[:-1] for v in vs]), tok_pos, tok_seq, table, 64,
+                  n_kv_heads, head_dim, kv)
+    scale = 0.41 / math.sqrt(head_dim)
+    q = dev(rng.standard_normal((len(seq_lens), n_heads * head_dim)), DT[dtype])
+    k_new = torch.stack([k[-1] for k in ks]).contiguous()
+    v_new = torch.stack([v[-1] for v in vs]).contiguous()
+    pos1 = torch.tensor([n - 1 for n in seq_lens], dtype=torch.int32, device="cuda")
+    seq1 = torch.arange(len(seq_lens), dtype=torch.int32, device="cuda")
+    n_pages = table.shape[1]
+    units = len(seq_lens) * n_heads * n_pages
+    part_o = torch.full((units * head_dim,), float("nan"), device="cuda")
+    part_ml = torch.full((units * 2,), float("nan"), device="cuda")
+    want = np.stack([plain_gpt2.causal_attention(
+        np.repeat(q[s:s + 1].double().cpu().numpy(), n, axis=0), ks[s].double().cpu().numpy(),
+        vs[s].double().cpu().numpy(), n_heads, n_kv_heads, scale, window)[-1] for s, n in enumerate(seq_lens)])
+    for round_ in range(2):                   # the second launch finds the tickets back at zero
+        out = torch.full_like(q, float("nan"))
+        ops.attention_decode(q, k_new if round_ == 0 else None, v_new if round_ == 0 else None, out, kv, table, 64,
+                             pos1, seq1, n_heads, n_kv_heads, head_dim, scale, window, n_pages, part_o, part_ml)
+        assert_close(out.float().cpu().numpy(), want, dtype, f"launch {round_}")
+    # the appended keys are where the general kernel looks for them
+    out2 = torch.empty_like(q)
+    ops.attention(q, out2, kv, table, 64, pos1, seq1, n_heads, n_kv_heads, head_dim, scale, window)
+    assert_close(out2.float().cpu().numpy(), want, dtype, "after the append")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 50, 24), (8, 2304, 768), (13, 77, 40), (16, 1031, 96), (3, 130, 1600)])
+@pytest.mark.parametrize("act", [None, "gelu_new"])
+def test_product_with_the_norm_inside(m, n, k, act):
+    """LayerNorm folded into the few-rows product against norm-then-product."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(m + n + k)
+    x = (rng.standard_normal((m + 3, k)) * 2 + 0.5).astype(np.float32)
+    g, b = rng.standard_normal(k).astype(np.float32), rng.standard_normal(k).astype(np.float32)
+    w = dev(rng.standard_normal((n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.standard_normal(n))
+    rows = torch.tensor(rng.permutation(m + 3)[:m].astype(np.int32), device="cuda")
+    for r in (None, rows):
+        lazy = ops.NormedInput(dev(x if r is not None else x[:m]), dev(g), dev(b), 1e-5, torch.bfloat16, rows=r)
+        got = ops.linear(lazy, w, bias, act=act, out_dtype=torch.float32).cpu().numpy()
+        src = x[:m] if r is None else x[r.cpu().numpy()]
+        h = plain_gpt2.layer_norm(src.astype(np.float64), g.astype(np.float64), b.astype(np.float64), 1e-5)
+        h = dev(h, torch.bfloat16).double().cpu().numpy()           # the kernel rounds the norm to bfloat16
+        z = h[:m] @ w.double().cpu().numpy().T + bias.double().cpu().numpy()
+        if act:
+            z = plain_gpt2.ACTIVATIONS[act](z)
+        # a normed value that lands on a rounding boundary may round the other way: allow for one such
+        # flip per row on top of the float32 bound (2^-9 of one term among k)
+        rms = np.sqrt((z ** 2).mean())
+        assert np.abs(got - z).max() < 1e-5 * rms + 2.0 ** -8 * 4.0 / math.sqrt(k) * 3, (m, n, k)

@@ -1,0 +1,341 @@
+// C[M, N] = act(A[M, K] . W[N, K]^T + bias) (+ residual) on the 5th-generation tensor cores.
+//
+// The product kernel of whole prompts (bfloat16 in, float32 accumulate).  One
+// block computes one 128 x BN tile of C:
+//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//            of 128 x 64 tiles of A and BN x 64 tiles of W into a ring of
+//            shared-memory stages and arms each stage's "full" mbarrier;
+//   warp 1   allocates BN columns of tensor memory; one lane issues
+//            tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per
+//            stage with shared-memory descriptors, the accumulator staying in
+//            tensor memory, and commits each stage back to the producer
+//            ("empty" mbarrier) and at the end the accumulator to the epilogue;
+//   warps 2-5  read the accumulator with tcgen05.ld (each warp its 32 lanes =
+//            32 rows of the tile), add bias, apply the activation, add the
+//            float32 residual and store bfloat16 or float32.
+// Rows of A and W beyond M, N and K are zero-filled by TMA; the epilogue
+// predicates its stores.  Every wait on an mbarrier is bounded: if it runs out
+// the block records a code in `status`, lets its copies land, frees its tensor
+// memory and returns, so a wrong phase shows up as an error and not as a hang.
+//
+// The reference's counterpart is matmulTiled (include/ai/Kernels.hpp:315-430).
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace mu {
+
+constexpr int TC_BM = 128, TC_BK = 64, TC_THREADS = 192;
+constexpr unsigned long long TC_WAIT_NS = 2000000000ull;      // a wait gives up after two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false if it never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long start = 0;
+    for (unsigned int spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 255u) == 255u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > TC_WAIT_NS) return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile with rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart (bits: address >> 4 at 0, leading offset at 16, stride offset at 32,
+// descriptor version 1 at 46, swizzle mode 2 = 128 B at 61).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator (bit 4), bfloat16 A and B (bits 7, 10),
+// both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN, int STAGES>
+struct TcSmem {
+    __nv_bfloat16 a[STAGES][TC_BM * TC_BK];      // each tile 1024-byte aligned: 128 x 128 B
+    __nv_bfloat16 b[STAGES][BN * TC_BK];
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t accum;
+    uint32_t tmem_base;
+};
+
+template <int BN, int STAGES, typename TC>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
+               long long ldc, long long ldr, int act, int* status) {
+    extern __shared__ unsigned char tc_raw[];
+    TcSmem<BN, STAGES>& sm =
+        *reinterpret_cast<TcSmem<BN, STAGES>*>(((uintptr_t)tc_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    constexpr uint32_t STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16);
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    bool ok = true;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES) ok = mbar_wait(&sm.empty[s], ((kb / STAGES) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+                tma_load_2d(sm.a[s], &map_a, kb * TC_BK, m0, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_w, kb * TC_BK, n0, &sm.full[s]);
+                issued = kb + 1;
+            }
+            if (!ok) {
+                atomicExch(status, 1);
+                // let the copies already under way land before the block goes away
+                for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+                    mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&sm.full[s], (kb / STAGES) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
+                    umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&sm.empty[s]);            // the stage is free once these have read it
+            }
+            if (ok) umma_commit(&sm.accum);           // the accumulator is complete
+            else atomicExch(status, 2);
+        }
+    } else {
+        // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+        const int quad = warp & 3;
+        ok = mbar_wait(&sm.accum, 0);
+        if (!ok) {
+            if (lane == 0) atomicExch(status, 3);
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quad * 32 + lane;
+            const bool vec_ok = ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) &&
+                                (!residual || ((ldr % 4 == 0) && (((uintptr_t)residual) % 16 == 0)));
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+                const int nb = n0 + c0;
+                if (row >= M || nb >= N) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int n = nb + i;
+                    float x = __uint_as_float(r[i]);
+                    if (bias && n < N) x += bias[n];
+                    v[i] = apply_act(x, act);
+                }
+                TC* crow = C + (long long)row * ldc + nb;
+                const float* rrow = residual ? residual + (long long)row * ldr + nb : nullptr;
+                if (vec_ok && nb + 32 <= N) {
+                    if (rrow) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 q = *reinterpret_cast<const float4*>(rrow + i);
+                            v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+                        }
+                    }
+                    if (sizeof(TC) == 4) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(crow) + i) =
+                                make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 packed;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                            packed.x = *reinterpret_cast<uint32_t*>(&h0);
+                            packed.y = *reinterpret_cast<uint32_t*>(&h1);
+                            packed.z = *reinterpret_cast<uint32_t*>(&h2);
+                            packed.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(crow) + i) = packed;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (nb + i < N) {
+                            float x = v[i];
+                            if (rrow) x += rrow[i];
+                            crow[i] = from_float<TC>(x);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows, cut into boxes of box_rows x 64.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(__nv_bfloat16)};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, typename TC>
+static int launch_tc(const void* A, const void* W, const float* bias, const float* residual, TC* C, int M, int N,
+                     int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int* status,
+                     cudaStream_t s) {
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, A, M, K, lda, TC_BM) || !make_map(&map_w, W, N, K, ldw, BN)) return MU_ERR_LAUNCH;
+    auto kernel = gemm_tc_kernel<BN, STAGES, TC>;
+    const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return MU_ERR_LAUNCH;
+        raised = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    kernel<<<grid, TC_THREADS, smem, s>>>(map_a, map_w, bias, residual, C, M, N, K, ldc, ldr, act, status);
+    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+}
+
+}  // namespace mu
+
+// bfloat16 A [M, K] (lda) and W [N, K] (ldw): K, lda, ldw multiples of 8, bases 16-byte aligned.
+// C bfloat16 or float32 (ldc); residual float32 (ldr), may be C itself.  `status` is a device word
+// that stays 0 unless a wait inside the kernel ran out (1 producer, 2 tensor-core issuer, 3 epilogue).
+MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const float* residual, void* C,
+                         int M, int N, int K, long long lda, long long ldw, long long ldc, long long ldr,
+                         int act, int out_bf16, int* status, void* stream) {
+    if (M <= 0 || N <= 0) return MU_OK;
+    if (K <= 0 || !A || !W || !C || !status) return MU_ERR_BAD_ARGUMENT;
+    if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return MU_ERR_ALIGNMENT;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return MU_ERR_ALIGNMENT;
+    if (lda < K || ldw < K || ldc < N || (residual && ldr < N)) return MU_ERR_BAD_ARGUMENT;
+    if ((M + mu::TC_BM - 1) / mu::TC_BM > 65535) return MU_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    // narrow tiles when wide ones would leave most of the 148 SMs without a tile
+    const long long tiles128 = (long long)((N + 127) / 128) * ((M + 127) / 128);
+    const bool narrow = N <= 64 || tiles128 < 148;
+#define MU_TC(BN, ST)                                                                                           \
+    (out_bf16 ? mu::launch_tc<BN, ST, __nv_bfloat16>(A, W, bias, residual, (__nv_bfloat16*)C, M, N, K, lda, ldw, \
+                                                     ldc, ldr, act, status, s)                                  \
+              : mu::launch_tc<BN, ST, float>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc, ldr, act,  \
+                                             status, s))
+    if (narrow) return MU_TC(64, 4);
+    return MU_TC(128, 3);
+#undef MU_TC
+}

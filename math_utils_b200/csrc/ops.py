@@ -42,6 +42,8 @@ _SIGNATURES = {
                      _c_int, _c_int, _c_int, _c_p],
     "mu_gemm_skinny": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                        _c_int, _c_int, _c_p],
+    "mu_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
+                   _c_int, _c_int, _c_p, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_p, _c_int, _c_p],
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
@@ -226,6 +228,48 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     return out
 
 
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """A device word that kernels with bounded waits write to when a wait runs
+    out (it stays 0 otherwise); ``check_status`` reads it."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device="cuda:0") -> None:
+    """Raises if a kernel gave up a bounded wait since the last check (this
+    synchronises with the device)."""
+    word = _status.get(str(torch.device(device)))
+    if word is not None:
+        code = int(word.item())
+        if code != 0:
+            word.zero_()
+            raise KernelError(f"a tensor-core product kernel gave up waiting (role {code}: 1 loads, 2 tensor "
+                              "cores, 3 epilogue); its results are not valid")
+
+
+def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether gemm_tc takes this product (alignment rules of its TMA loads)."""
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The product on the tcgen05 tensor cores (TMA loads, accumulator in tensor memory)."""
+    m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
+    _check(library().mu_gemm_tc(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
+        out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
+        _is_bf16(out), _ptr(status_word(a.device)), _stream()), f"gemm_tc({m}x{n}x{k})")
+    return out
+
+
 def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether gemm_skinny takes this product: bfloat16, at most 64 rows, k and
     both row strides multiples of 8 elements, 16-byte aligned bases."""
@@ -406,4 +450,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         x = x.materialize()
     if skinny_ok(x, weight):
         return gemm_skinny(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
+    if tc_ok(x, weight):
+        return gemm_tc(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
     return gemm_simt(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

@@ -17,9 +17,11 @@ def dev(a, dtype=torch.float32):
     return torch.as_tensor(np.asarray(a)).to("cuda", dtype)
 
 
-def assert_close(got, want, dtype, what=""):
+def assert_close(got, want, dtype, what="", k=1):
     """float32 results: max |diff| <= 1e-5 x rms of the expected values (the
-    reference's measure for kernels, src/gpu-testing.cpp:79-95).  bfloat16
+    reference's measure for kernels, src/gpu-testing.cpp:79-95); for a sum of
+    k float32 terms the rounding of the running sum grows like sqrt(k), so the
+    bound is scaled by sqrt(k / 512) beyond 512 terms.  bfloat16
     results are rounded to 8 bits of mantissa on output, so each element may
     be off by 2^-9 of its own size; allow 2^-7 of it plus 0.6 % of the rms for
     the rounding of intermediate results."""
@@ -28,7 +30,8 @@ def assert_close(got, want, dtype, what=""):
     assert got.shape == want.shape, (what, got.shape, want.shape)
     rms = max(np.sqrt((want ** 2).mean()), 1e-30)
     diff = np.abs(got - want)
-    bound = 1e-5 * rms if dtype == "float32" else 2.0 ** -7 * np.abs(want) + 6e-3 * rms
+    bound = (1e-5 * max(1.0, math.sqrt(k / 512.0)) * rms if dtype == "float32"
+             else 2.0 ** -7 * np.abs(want) + 6e-3 * rms)
     worst = float((diff / bound).max()) if dtype != "float32" else float(diff.max() / bound)
     assert worst <= 1.0, f"{what}: error is {worst:.2f} x the bound (rms {rms:.3g}, max |diff| {diff.max():.3g})"
 
@@ -320,3 +323,28 @@ def test_product_with_the_norm_inside(m, n, k, act):
         # flip per row on top of the float32 bound (2^-9 of one term among k)
         rms = np.sqrt((z ** 2).mean())
         assert np.abs(got - z).max() < 1e-5 * rms + 2.0 ** -8 * 4.0 / math.sqrt(k) * 3, (m, n, k)
+
+
+@pytest.mark.parametrize("m,n,k", [(65, 64, 64), (128, 128, 64), (129, 130, 72), (257, 200, 328), (1000, 520, 768),
+                                   (2048, 2304, 768), (2048, 768, 3072), (300, 1031, 96), (70, 50257, 64)])
+def test_tensor_core_product(m, n, k):
+    """The tcgen05 / TMA kernel at ragged sizes: more than one k-block ring turn,
+    edges in m, n and k, both tile widths, every epilogue."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(m + n + k)
+    a = dev(rng.standard_normal((m, k)), torch.bfloat16)
+    w = dev(rng.standard_normal((n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.standard_normal(n))
+    res = dev(rng.standard_normal((m, n)))
+    assert ops.tc_ok(a, w)
+    z = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    got = ops.gemm_tc(a, w, None, out_dtype=torch.float32).cpu().numpy()
+    ops.check_status()
+    assert_close(got, z, "float32", "plain product", k=k)
+    zb = z + bias.double().cpu().numpy()
+    got = ops.gemm_tc(a, w, bias, act="gelu_new").float().cpu().numpy()
+    assert_close(got, plain_gpt2.gelu_new(zb), "bfloat16", "bias, gelu, bfloat16 out")
+    x = res.clone()
+    ops.gemm_tc(a, w, bias, residual=x, out=x)
+    assert_close(x.cpu().numpy(), zb + res.double().cpu().numpy(), "float32", "residual in place", k=k)
+    ops.check_status()

@@ -49,6 +49,8 @@ _SIGNATURES = {
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
                      _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p],
     "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
+    "mu_attention_prefill": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int,
+                             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p],
     "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
@@ -431,6 +433,27 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml),
         _ptr(tickets), _is_bf16(kv_pages), _stream()),
         f"attention_decode(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+    return out
+
+
+def prefill_ok(q: torch.Tensor, head_dim: int, page_tokens: int) -> bool:
+    """Whether the tensor-core prompt attention takes this case."""
+    return (q.dtype == torch.bfloat16 and page_tokens == 64 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor,
+                      page_tokens: int, tok_pos, tok_seq, tiles: torch.Tensor, n_heads: int, n_kv_heads: int,
+                      head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Flash-style causal attention of prompt tokens on tensor cores.  ``tiles``
+    int32 [n, 2]: first flat query index and query count (<= 64) of each tile."""
+    _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, tiles)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table"), (tiles, "tiles")):
+        _i32(t, name)
+    _check(library().mu_attention_prefill(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv_pages), _ptr(block_table), block_table.shape[1],
+        page_tokens, _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles), tiles.shape[0], n_heads, n_kv_heads, head_dim,
+        float(scale), int(window), _stream()), f"attention_prefill(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
     return out
 
 

@@ -17,6 +17,9 @@ import numpy as np
 import torch
 
 
+TILE_QUERIES = 64
+
+
 @dataclass
 class StepEntry:
     """``tokens``: the next tokens of the sequence in ``slot``; ``want``:
@@ -73,6 +76,7 @@ class StepContext:
     max_kv_len: int                       # longest sequence after this step
     workspace: dict = field(default_factory=dict)
     split_target_warps: int = 148 * 8
+    q_tiles: Optional[torch.Tensor] = None  # [n, 2] int32: (first flat token, count <= 64) of each query tile
 
     @property
     def is_decode(self) -> bool:
@@ -120,7 +124,13 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     n_tokens, n_seqs = sum(q_lens), len(entries)
     n_want = sum(len(e.want) for e in entries)
     tables = [cache.block_table_rows(g.index, [e.slot for e in entries]) for g in cache.kv_groups]
-    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs] + [t.size for t in tables]
+    tiles = []                            # query tiles of 64 for the prompt attention kernel
+    if max(q_lens) > 1:
+        flat = 0
+        for n in q_lens:
+            tiles.extend((flat + o, min(TILE_QUERIES, n - o)) for o in range(0, n, TILE_QUERIES))
+            flat += n
+    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * len(tiles)] + [t.size for t in tables]
     offsets = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])])   # 16-byte aligned parts
     total = int(offsets[-1])
     host = ring.next(total)
@@ -139,8 +149,10 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
             o += 1
         flat += n
     h[offsets[4]: offsets[4] + n_seqs] = np.asarray([e.slot for e in entries], dtype=np.int32)
+    if tiles:
+        h[offsets[5]: offsets[5] + 2 * len(tiles)] = np.asarray(tiles, dtype=np.int32).reshape(-1)
     for i, t in enumerate(tables):
-        h[offsets[5 + i]: offsets[5 + i] + t.size] = t.reshape(-1)
+        h[offsets[6 + i]: offsets[6 + i] + t.size] = t.reshape(-1)
     dev = torch.empty(total, dtype=torch.int32, device=runtime.device)
     dev.copy_(host[:total], non_blocking=True)
     ring.mark()
@@ -152,8 +164,9 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
         runtime=runtime, position=position, n_tokens=n_tokens, n_seqs=n_seqs,
         token_ids=part(0, n_tokens), tok_pos=part(1, n_tokens), tok_seq=part(2, n_tokens),
         want_rows=part(3, n_want) if n_want else None,
-        block_tables=[part(5 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
+        block_tables=[part(6 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
         seq_slots=part(4, n_seqs),
+        q_tiles=part(5, 2 * len(tiles)).view(len(tiles), 2) if tiles else None,
         slots=[e.slot for e in entries], starts=list(starts), q_lens=q_lens,
         max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
         workspace=workspace)

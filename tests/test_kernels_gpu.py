@@ -17,7 +17,7 @@ def dev(a, dtype=torch.float32):
     return torch.as_tensor(np.asarray(a)).to("cuda", dtype)
 
 
-def assert_close(got, want, dtype, what="", k=1):
+def assert_close(got, want, dtype, what="", k=1, extra_abs=0.0):
     """float32 results: max |diff| <= 1e-5 x rms of the expected values (the
     reference's measure for kernels, src/gpu-testing.cpp:79-95); for a sum of
     k float32 terms the rounding of the running sum grows like sqrt(k), so the
@@ -31,7 +31,7 @@ def assert_close(got, want, dtype, what="", k=1):
     rms = max(np.sqrt((want ** 2).mean()), 1e-30)
     diff = np.abs(got - want)
     bound = (1e-5 * max(1.0, math.sqrt(k / 512.0)) * rms if dtype == "float32"
-             else 2.0 ** -7 * np.abs(want) + 6e-3 * rms)
+             else 2.0 ** -7 * np.abs(want) + 6e-3 * rms + extra_abs)
     worst = float((diff / bound).max()) if dtype != "float32" else float(diff.max() / bound)
     assert worst <= 1.0, f"{what}: error is {worst:.2f} x the bound (rms {rms:.3g}, max |diff| {diff.max():.3g})"
 
@@ -348,3 +348,43 @@ def test_tensor_core_product(m, n, k):
     ops.gemm_tc(a, w, bias, residual=x, out=x)
     assert_close(x.cpu().numpy(), zb + res.double().cpu().numpy(), "float32", "residual in place", k=k)
     ops.check_status()
+
+
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (4, 4, 16, 0), (6, 2, 48, 0), (3, 3, 80, 0), (8, 2, 128, 70), (12, 12, 64, 0), (4, 2, 32, 1), (2, 1, 112, 130)])
+def test_prompt_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window):
+    """Whole prompts and a prompt continued from a filled cache, tiles that end
+    inside a page, several sequences in one launch."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(11 * head_dim + n_heads)
+    totals = [1, 64, 65, 200, 333]
+    starts = [0, 0, 0, 70, 128]                    # tokens the cache already holds
+    kv, table, ks, vs = paged_setup(rng, totals, n_kv_heads, head_dim, "bfloat16")
+    all_pos = torch.tensor([p for n in totals for p in range(n)], dtype=torch.int32, device="cuda")
+    all_seq = torch.tensor([s for s, n in enumerate(totals) for _ in range(n)], dtype=torch.int32, device="cuda")
+    ops.kv_append(torch.cat(ks), torch.cat(vs), all_pos, all_seq, table, 64, n_kv_heads, head_dim, kv)
+    tok_pos = torch.tensor([p for n, s in zip(totals, starts) for p in range(s, n)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([i for i, (n, s) in enumerate(zip(totals, starts)) for _ in range(s, n)],
+                           dtype=torch.int32, device="cuda")
+    tiles, flat = [], 0
+    for n, s in zip(totals, starts):
+        for o in range(0, n - s, 64):
+            tiles.append((flat + o, min(64, n - s - o)))
+        flat += n - s
+    tiles_t = torch.tensor(tiles, dtype=torch.int32, device="cuda")
+    q_all = dev(rng.standard_normal((flat, n_heads * head_dim + 8)), torch.bfloat16)[:, :n_heads * head_dim]
+    out = torch.full((flat, n_heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scale = 0.6 / math.sqrt(head_dim)
+    assert ops.prefill_ok(q_all, head_dim, 64)
+    ops.attention_prefill(q_all, out, kv, table, 64, tok_pos, tok_seq, tiles_t, n_heads, n_kv_heads, head_dim,
+                          scale, window)
+    o = 0
+    for i, (n, s) in enumerate(zip(totals, starts)):
+        want = plain_gpt2.causal_attention(q_all[o:o + n - s].double().cpu().numpy(), ks[i].double().cpu().numpy(),
+                                           vs[i].double().cpu().numpy(), n_heads, n_kv_heads, scale, window, start=s)
+        # probabilities are rounded to bfloat16 before they meet the values: where one key carries
+        # most of the weight that is up to 2^-9 of the largest value, whatever the size of the output
+        vmax = float(vs[i].abs().max())
+        assert_close(out[o:o + n - s].float().cpu().numpy(), want, "bfloat16", f"sequence {i}",
+                     extra_abs=2.0 ** -8 * vmax)
+        o += n - s

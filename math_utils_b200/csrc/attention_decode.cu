@@ -30,6 +30,7 @@ constexpr int AD_PAGE = 64;
 
 __device__ __forceinline__ float dot_head(const float* qs, const float* krow, int head_dim) {
     float s = 0.0f;
+#pragma unroll 8
     for (int d = 0; d < head_dim; d += 4) {
         const float4 kk = *reinterpret_cast<const float4*>(krow + d);
         s = fmaf(qs[d], kk.x, s);
@@ -41,6 +42,7 @@ __device__ __forceinline__ float dot_head(const float* qs, const float* krow, in
 }
 __device__ __forceinline__ float dot_head(const float* qs, const __nv_bfloat16* krow, int head_dim) {
     float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll 8
     for (int d = 0; d < head_dim; d += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
         const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -58,6 +60,21 @@ __device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_ca
 __device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
     return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
 }
+
+// Two neighbouring elements as they lie in memory, widened only when used.
+template <typename TE> struct RawPair;
+template <> struct RawPair<float> {
+    float2 v;
+    __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float2*>(p); }
+    __device__ __forceinline__ void zero() { v = make_float2(0.0f, 0.0f); }
+    __device__ __forceinline__ float2 get() const { return v; }
+};
+template <> struct RawPair<__nv_bfloat16> {
+    __nv_bfloat162 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const __nv_bfloat162*>(p); }
+    __device__ __forceinline__ void zero() { v = __floats2bfloat162_rn(0.0f, 0.0f); }
+    __device__ __forceinline__ float2 get() const { return __bfloat1622float2(v); }
+};
 
 // DP: pairs of head dimensions per lane (lane owns dims 2*lane + 64*i, +1).
 template <typename TE, int DP>
@@ -93,6 +110,29 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     const TE* kn = has_new ? k_new + (long long)t * ldk + kvh * head_dim : nullptr;
     const TE* vn = has_new ? v_new + (long long)t * ldv + kvh * head_dim : nullptr;
 
+    // The values are asked for first, so that they travel while the scores are computed: VC keys
+    // at a time (as many as fit 64 registers), each lane its own dimensions of every key.  These
+    // rows were written by earlier steps, so they may be read before the kernels ahead have finished.
+    pdl_trigger();
+    constexpr int VC = 64 / (DP * (int)(sizeof(TE) / 2));
+    RawPair<TE> vreg[VC][DP];
+    auto fetch_values = [&](int j0) {
+#pragma unroll
+        for (int jj = 0; jj < VC; ++jj) {
+            const int j = j0 + jj;
+            const TE* vrow = vpage + (long long)j * head_dim;
+#pragma unroll
+            for (int i = 0; i < DP; ++i) {
+                const int d = 2 * lane + 64 * i;
+                if (j >= lo && j < hi_cache && d < head_dim) vreg[jj][i].load(vrow + d);
+                else vreg[jj][i].zero();
+            }
+        }
+    };
+    const int v_first = (lo / VC) * VC;                     // chunk that holds the first visible key
+    fetch_values(v_first);
+    pdl_wait();                                             // this step's query, key and value from here on
+
     float* qs = q_smem[warp];
     for (int d = lane; d < head_dim; d += 32) qs[d] = to_float(q[(long long)t * ldq + h * head_dim + d]);
     if (has_new && h % group == 0) {
@@ -107,10 +147,12 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     float s0 = -INFINITY, s1 = -INFINITY;
     {
         const int j0 = lane, j1 = lane + 32;
-        if (j0 >= lo && j0 < hi_cache) s0 = dot_head(qs, kpage + (long long)j0 * head_dim, head_dim) * scale;
-        else if (has_new && j0 == hi - 1) s0 = dot_head(qs, kn, head_dim) * scale;
-        if (j1 >= lo && j1 < hi_cache) s1 = dot_head(qs, kpage + (long long)j1 * head_dim, head_dim) * scale;
-        else if (has_new && j1 == hi - 1) s1 = dot_head(qs, kn, head_dim) * scale;
+        const bool in0 = j0 >= lo && j0 < hi_cache, in1 = j1 >= lo && j1 < hi_cache;
+        const bool new0 = has_new && j0 == hi - 1, new1 = has_new && j1 == hi - 1;
+        const TE* k0 = in0 ? kpage + (long long)j0 * head_dim : kn;
+        const TE* k1 = in1 ? kpage + (long long)j1 * head_dim : kn;
+        if (in0 || new0) s0 = dot_head(qs, k0, head_dim) * scale;
+        if (in1 || new1) s1 = dot_head(qs, k1, head_dim) * scale;
     }
     const float m = warp_max(fmaxf(s0, s1));
     const float p0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - m);
@@ -120,30 +162,15 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     float2 acc[DP];
 #pragma unroll
     for (int i = 0; i < DP; ++i) acc[i] = make_float2(0.0f, 0.0f);
-    const int end0 = min(hi_cache, 32);
-#pragma unroll 8
-    for (int j = lo; j < end0; ++j) {
-        const float pj = __shfl_sync(0xffffffffu, p0, j);
-        const TE* vrow = vpage + (long long)j * head_dim;
+    for (int c0 = v_first; c0 < hi_cache; c0 += VC) {
+        if (c0 != v_first) fetch_values(c0);
 #pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            const int d = 2 * lane + 64 * i;
-            if (d < head_dim) {
-                const float2 v = load2(vrow + d);
-                acc[i].x = fmaf(pj, v.x, acc[i].x);
-                acc[i].y = fmaf(pj, v.y, acc[i].y);
-            }
-        }
-    }
-#pragma unroll 8
-    for (int j = max(lo, 32); j < hi_cache; ++j) {
-        const float pj = __shfl_sync(0xffffffffu, p1, j - 32);
-        const TE* vrow = vpage + (long long)j * head_dim;
+        for (int jj = 0; jj < VC; ++jj) {
+            const int j = c0 + jj;                           // keys outside [lo, hi_cache) carry p = 0 or v = 0
+            const float pj = __shfl_sync(0xffffffffu, (j < 32) ? p0 : p1, j & 31);
 #pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            const int d = 2 * lane + 64 * i;
-            if (d < head_dim) {
-                const float2 v = load2(vrow + d);
+            for (int i = 0; i < DP; ++i) {
+                const float2 v = vreg[jj][i].get();
                 acc[i].x = fmaf(pj, v.x, acc[i].x);
                 acc[i].y = fmaf(pj, v.y, acc[i].y);
             }
@@ -257,7 +284,7 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
     cudaStream_t s = (cudaStream_t)stream;
     const int dp = (head_dim + 63) / 64;
 #define MU_AD(TE, DP)                                                                                  \
-    mu::attention_decode_kernel<TE, DP><<<grid, mu::AD_WARPS * 32, 0, s>>>(                             \
+    rc = mu::launch_pdl(mu::attention_decode_kernel<TE, DP>, grid, dim3(mu::AD_WARPS * 32), 0, s, 1,    \
         (const TE*)q, ldq, (const TE*)k_new, ldk, (const TE*)v_new, ldv, (TE*)out, ldo, (TE*)kv,       \
         block_table, max_pages, tok_pos, tok_seq, n_tokens, n_heads, n_kv_heads, head_dim, scale,      \
         window, n_splits, part_o, part_ml, tickets)
@@ -267,10 +294,10 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
         else if (dp <= 2) MU_AD(TE, 2);  \
         else MU_AD(TE, 4);               \
     } while (0)
+    int rc = MU_OK;
     if (is_bf16) MU_AD_T(__nv_bfloat16);
     else MU_AD_T(float);
 #undef MU_AD_T
 #undef MU_AD
-    MU_CHECK_LAUNCH();
-    return MU_OK;
+    return rc;
 }

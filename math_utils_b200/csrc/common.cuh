@@ -76,4 +76,47 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return r;
 }
 
+// --- programmatic dependent launch -------------------------------------------------------
+// Kernels of the single-token step are launched so that the next one may start while the
+// previous one drains: it runs its prologue (index arithmetic, prefetch of weights, which
+// no kernel ever writes) and then waits, at pdl_wait(), until every kernel before it has
+// finished and its results are visible.  Nothing that another kernel produces is read, and
+// nothing at all is written, before that wait.  pdl_trigger() lets the next kernel in.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& pdl_enabled() {
+    static int enabled = 1;
+    return enabled;
+}
+
+// Launches with the programmatic-serialization attribute (if enabled) and, when cluster_y > 1,
+// as thread-block clusters of (1, cluster_y, 1).
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      int cluster_y, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = (unsigned)cluster_y;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+}
+
 }  // namespace mu

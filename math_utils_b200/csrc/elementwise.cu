@@ -13,6 +13,8 @@ template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ table, const TW* __restrict__ pos_table,
                              float* __restrict__ x, int hidden) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const long long row = ids[t];
     const TW* src = table + row * hidden;
@@ -67,13 +69,10 @@ MU_EXPORT int mu_embed(const int* ids, const int* pos, const void* table, const 
     const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_bf16)
-        mu::embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(
-            ids, pos, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
-    else
-        mu::embed_kernel<float><<<n_tokens, threads, 0, s>>>(
-            ids, pos, (const float*)table, (const float*)pos_table, x, hidden);
-    MU_CHECK_LAUNCH();
-    return MU_OK;
+        return mu::launch_pdl(mu::embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
+                              (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
+    return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
+                          (const float*)table, (const float*)pos_table, x, hidden);
 }
 
 // rows: optional int32 row indices into x (n_rows of them); out_bf16 picks the output dtype.
@@ -98,6 +97,8 @@ MU_EXPORT int mu_layernorm(const float* x, const int* rows, const float* gamma, 
 namespace mu {
 __global__ void advance_kernel(int* __restrict__ token_ids, int* __restrict__ tok_pos,
                                const int* __restrict__ next_tokens, int n, int last_pos) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     token_ids[i] = next_tokens[i];
@@ -112,8 +113,12 @@ MU_EXPORT int mu_advance(int* token_ids, int* tok_pos, const int* next_tokens, i
                          void* stream) {
     if (n <= 0) return MU_OK;
     if (!token_ids || !tok_pos || !next_tokens) return MU_ERR_BAD_ARGUMENT;
-    mu::advance_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(token_ids, tok_pos, next_tokens, n,
-                                                                         last_pos);
-    MU_CHECK_LAUNCH();
+    return mu::launch_pdl(mu::advance_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, 1,
+                          token_ids, tok_pos, next_tokens, n, last_pos);
+}
+
+// Turns programmatic dependent launch of the single-token kernels on (1, the default) or off (0).
+MU_EXPORT int mu_set_pdl(int enabled) {
+    mu::pdl_enabled() = enabled ? 1 : 0;
     return MU_OK;
 }

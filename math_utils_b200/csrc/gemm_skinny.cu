@@ -11,11 +11,19 @@
 // agree).  A block is 8 warps laid out as WN groups of 16 weight rows x WK
 // slices of K; the slices are summed through shared memory in a fixed order,
 // then bias, activation and residual are applied and the result written with
-// consecutive threads on consecutive columns.
+// consecutive threads on consecutive columns.  When the output is narrow (few
+// blocks) and K long, CK blocks of a thread-block cluster share one output
+// tile, each taking a part of K; the others hand their partial tile to the
+// first block through distributed shared memory, which adds them in rank
+// order, so the sum does not depend on timing.
 //
 // This is the path of single-token steps (the reference runs them through
 // matmulNTBias, one dot product per output: include/ai/Kernels.hpp:433-447).
 #include "common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace mu {
 
@@ -52,7 +60,7 @@ struct SkinnyNorm {
     float eps;
 };
 
-template <int MT, int WN, int WK, typename TC, bool LN>
+template <int MT, int WN, int WK, int CK, typename TC, bool LN>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
@@ -61,9 +69,43 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     constexpr int ROWS = 16 * WN;          // weight rows (output columns) per block
     constexpr int MP = 8 * MT;             // activation rows, padded
     __shared__ float red[WK][ROWS][MP + 1];
+    __shared__ float peer[CK > 1 ? CK - 1 : 1][CK > 1 ? ROWS : 1][CK > 1 ? MP + 1 : 1];   // partial tiles of the other blocks
     extern __shared__ __align__(16) unsigned char skinny_dyn[];
     __nv_bfloat16* act_smem = reinterpret_cast<__nv_bfloat16*>(skinny_dyn);   // [MP][K + 8] with LN
     const int act_ld = K + 8;              // rows 16 bytes apart modulo 128: no bank conflicts
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wn = warp % WN, wk = warp / WN;
+    const int g = lane >> 2, t = lane & 3;
+    const int n_base = blockIdx.x * ROWS + wn * 16;
+    const int rank = CK > 1 ? (int)blockIdx.y : 0;         // the cluster spans grid.y
+
+    // K is cut into CK * WK slices on 32-element boundaries
+    const int k_blocks = (K + 31) / 32;
+    const int per = (k_blocks + CK * WK - 1) / (CK * WK);
+    const int kb0 = (rank * WK + wk) * per, kb1 = min(k_blocks, kb0 + per);
+
+    // rows past the end are clamped for loading and dropped when writing
+    const int r0 = min(n_base + g, N - 1), r1 = min(n_base + g + 8, N - 1);
+    const __nv_bfloat16* w0 = W + (long long)r0 * ldw + 8 * t;
+    const __nv_bfloat16* w1 = W + (long long)r1 * ldw + 8 * t;
+
+    // the first weights are asked for before anything else: they do not depend on the activations
+    constexpr int UNROLL = 4;
+    uint4 wa[UNROLL], wb[UNROLL];
+    auto load_weights = [&](int kb) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (kb + u) * 32;
+            const bool in = (kb + u) < kb1 && (k + 8 * t) < K;      // K is a multiple of 8
+            wa[u] = in ? load_stream(w0 + k) : make_uint4(0, 0, 0, 0);
+            wb[u] = in ? load_stream(w1 + k) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    pdl_trigger();
+    load_weights(kb0);
+    pdl_wait();                                            // activations, bias and residual from here on
+
     if (LN) {
         const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
         for (int m = w; m < MP; m += SK_WARPS) {
@@ -85,20 +127,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         __syncthreads();
     }
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wn = warp % WN, wk = warp / WN;
-    const int g = lane >> 2, t = lane & 3;
-    const int n_base = blockIdx.x * ROWS + wn * 16;
-
-    // K is cut into WK slices on 32-element boundaries
-    const int k_blocks = (K + 31) / 32;
-    const int per = (k_blocks + WK - 1) / WK;
-    const int kb0 = wk * per, kb1 = min(k_blocks, kb0 + per);
-
-    // rows past the end are clamped for loading and dropped when writing
-    const int r0 = min(n_base + g, N - 1), r1 = min(n_base + g + 8, N - 1);
-    const __nv_bfloat16* w0 = W + (long long)r0 * ldw + 8 * t;
-    const __nv_bfloat16* w1 = W + (long long)r1 * ldw + 8 * t;
     const __nv_bfloat16* xrow[MT];
     bool xvalid[MT];
 #pragma unroll
@@ -114,16 +142,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-    constexpr int UNROLL = 4;
     for (int kb = kb0; kb < kb1; kb += UNROLL) {
-        uint4 wa[UNROLL], wb[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k = (kb + u) * 32;
-            const bool in = (kb + u) < kb1 && (k + 8 * t) < K;      // K is a multiple of 8
-            wa[u] = in ? load_stream(w0 + k) : make_uint4(0, 0, 0, 0);
-            wb[u] = in ? load_stream(w1 + k) : make_uint4(0, 0, 0, 0);
-        }
+        if (kb != kb0) load_weights(kb);
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (kb + u) * 32;
@@ -147,6 +167,21 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         red[wk][wn * 16 + g + 8][8 * j + 2 * t + 1] = acc[j][3];
     }
     __syncthreads();
+    if (CK > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (rank != 0) {
+            float* dst = cluster.map_shared_rank(&peer[0][0][0], 0) + (long long)(rank - 1) * ROWS * (MP + 1);
+            for (int idx = threadIdx.x; idx < ROWS * MP; idx += SK_WARPS * 32) {
+                const int r = idx / MP, m = idx % MP;
+                float v = 0.0f;
+#pragma unroll
+                for (int s = 0; s < WK; ++s) v += red[s][r][m];
+                dst[r * (MP + 1) + m] = v;
+            }
+        }
+        cluster.sync();
+        if (rank != 0) return;
+    }
     const int col0 = blockIdx.x * ROWS;
     for (int idx = threadIdx.x; idx < ROWS * M; idx += SK_WARPS * 32) {
         const int m = idx / ROWS, r = idx % ROWS;
@@ -155,6 +190,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         float v = 0.0f;
 #pragma unroll
         for (int s = 0; s < WK; ++s) v += red[s][r][m];
+        if (CK > 1) {
+#pragma unroll
+            for (int c = 0; c < CK - 1; ++c) v += peer[c][r][m];
+        }
         if (bias) v += bias[n];
         v = apply_act(v, act);
         if (residual) v += residual[(long long)m * ldr + n];
@@ -162,16 +201,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     }
 }
 
-template <int MT, int WN, int WK, typename TC, bool LN>
+template <int MT, int WN, int WK, int CK, typename TC, bool LN>
 static int launch_skinny_as(const __nv_bfloat16* A, const __nv_bfloat16* W, const float* bias,
                             const float* residual, TC* C, int M, int N, int K, long long lda, long long ldw,
                             long long ldc, long long ldr, int act, const SkinnyNorm& norm, cudaStream_t s) {
-    auto kernel = gemm_skinny_kernel<MT, WN, WK, TC, LN>;
+    auto kernel = gemm_skinny_kernel<MT, WN, WK, CK, TC, LN>;
     size_t dyn = 0;
     if (LN) {
         dyn = (size_t)8 * MT * (K + 8) * sizeof(__nv_bfloat16);
         if (dyn > 160 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
-        if (dyn > 40 * 1024) {
+        if (dyn > 24 * 1024) {
             // more than the default limit allows next to the static part; asked for once per variant
             static bool raised = false;
             if (!raised) {
@@ -182,22 +221,25 @@ static int launch_skinny_as(const __nv_bfloat16* A, const __nv_bfloat16* W, cons
             }
         }
     }
-    kernel<<<(N + 16 * WN - 1) / (16 * WN), SK_WARPS * 32, dyn, s>>>(A, W, bias, residual, C, M, N, K, lda,
-                                                                     ldw, ldc, ldr, act, norm);
-    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+    return launch_pdl(kernel, dim3((N + 16 * WN - 1) / (16 * WN), CK, 1), dim3(SK_WARPS * 32), dyn, s, CK, A, W, bias,
+                      residual, C, M, N, K, lda, ldw, ldc, ldr, act, norm);
 }
 
 template <int MT, typename TC, bool LN>
 static int launch_skinny(const __nv_bfloat16* A, const __nv_bfloat16* W, const float* bias,
                          const float* residual, TC* C, int M, int N, int K, long long lda, long long ldw,
                          long long ldc, long long ldr, int act, const SkinnyNorm& norm, cudaStream_t s) {
-    // few output columns: cut K over the warps so that enough blocks exist; many: whole K per warp
-#define MU_SK(WN, WK) \
-    return launch_skinny_as<MT, WN, WK, TC, LN>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act, norm, s)
-    if (N >= 16 * 8 * 296 && K <= 2048) MU_SK(8, 1);
-    else if (N >= 16 * 4 * 296) MU_SK(4, 2);
-    else if (N >= 16 * 2 * 296) MU_SK(2, 4);
-    else MU_SK(1, 8);
+    // many output columns: whole K per warp; few: K cut over the warps of a block, and over the
+    // blocks of a cluster when even that leaves most SMs idle
+#define MU_SK(WN, WK, CK) \
+    return launch_skinny_as<MT, WN, WK, CK, TC, LN>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act, norm, s)
+    const int tiles = (N + 15) / 16, k_blocks = (K + 31) / 32;
+    if (N >= 16 * 8 * 296 && K <= 2048) MU_SK(8, 1, 1);
+    else if (N >= 16 * 4 * 296) MU_SK(4, 2, 1);
+    else if (N >= 16 * 2 * 296) MU_SK(2, 4, 1);
+    else if (tiles < 74 && k_blocks >= 64) MU_SK(1, 8, 4);
+    else if (tiles < 148 && k_blocks >= 16) MU_SK(1, 8, 2);
+    else MU_SK(1, 8, 1);
 #undef MU_SK
 }
 

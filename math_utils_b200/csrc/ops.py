@@ -8,6 +8,7 @@ be built or loaded, or a tensor is not on a CUDA device, they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional
 
@@ -79,6 +80,8 @@ def library() -> ctypes.CDLL:
                         continue          # optional kernels are looked up where they are used
                     fn.argtypes = argtypes
                     fn.restype = _c_int
+                if os.environ.get("MU_B200_PDL", "1") == "0":
+                    lib.mu_set_pdl(0)         # plain stream order between the single-token kernels
                 _lib = lib
     return _lib
 

@@ -54,6 +54,8 @@ __global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out,
               unsigned long long* __restrict__ best_ws, unsigned int* __restrict__ ticket_ws) {
     __shared__ unsigned long long best_smem[ARGMAX_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (long long)r * ld;
     const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
@@ -140,6 +142,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     __shared__ float red[32];
     __shared__ unsigned long long total_smem;
     __shared__ int found_idx;
+    pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x, r = blockIdx.x;
     RowView v;
     v.row = logits + (long long)r * ld;
@@ -294,10 +298,8 @@ MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab
     if (n_rows <= 0) return MU_OK;
     if (!logits || !out || !workspace || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
     dim3 grid(n_rows, mu::ARGMAX_PARTS);
-    mu::argmax_kernel<<<grid, mu::ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(
-        logits, ld, vocab, out, workspace, reinterpret_cast<unsigned int*>(workspace + n_rows));
-    MU_CHECK_LAUNCH();
-    return MU_OK;
+    return mu::launch_pdl(mu::argmax_kernel, grid, dim3(mu::ARGMAX_THREADS), 0, (cudaStream_t)stream, 1, logits, ld,
+                          vocab, out, workspace, reinterpret_cast<unsigned int*>(workspace + n_rows));
 }
 
 // request_ids [n_rows] int64 (null: the row index), draw_index [n_rows] int32 is read and
@@ -308,8 +310,6 @@ MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab
     if (n_rows <= 0) return MU_OK;
     if (!logits || !out || !draw_index || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
     if (!(temperature > 0.0f) || top_k < 0) return MU_ERR_BAD_ARGUMENT;
-    mu::sample_kernel<<<n_rows, mu::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
-        logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out);
-    MU_CHECK_LAUNCH();
-    return MU_OK;
+    return mu::launch_pdl(mu::sample_kernel, dim3(n_rows), dim3(mu::SAMPLE_THREADS), 0, (cudaStream_t)stream, 1,
+                          logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out);
 }

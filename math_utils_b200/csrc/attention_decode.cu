@@ -1,21 +1,23 @@
 // Single-token attention over the paged cache, one launch per layer.
 //
-// Each sequence brings one query token.  One warp takes one (sequence, head,
-// cache page): the page's 64 keys of that head are one contiguous block, so a
-// lane computes two scores (16-byte loads along the head), the warp does the
-// max-subtracted softmax of the page in float32, and the lanes, now spread over
-// the head's dimensions, add up the weighted values with the loads of a whole
-// unrolled group in flight together.  The warp parks its partial (max, sum,
-// unnormalised values) in scratch and takes a ticket; the warp that takes the
-// last ticket of a (sequence, head) merges the pages in page order, so the
-// result does not depend on which warp came last, and puts the ticket counter
-// back to zero for the next launch.
+// Each sequence brings one query token.  One block takes one (sequence, head);
+// its warps share out the sequence's cache pages.  A page's 64 keys of that head
+// are one contiguous block, so a lane computes two scores (16-byte loads along
+// the head), the warp does the max-subtracted softmax of the page in float32,
+// and the lanes, now spread over the head's dimensions, add up the weighted
+// values, which were asked for before anything else so that they travel while
+// the scores are computed.  A warp that has several pages folds them into one
+// running (max, sum, values); the warps' results meet in shared memory and are
+// merged in warp order, so the result does not depend on timing, and nothing
+// goes through global scratch.
 //
 // The new token's own key and value need not be in the cache yet: given
 // `k_new` / `v_new` (this step's projections) the kernel reads them from there,
 // and the first query head of each kv head copies them into the page.  That
 // folds the cache append and the merge of the split into the attention launch
-// (3 launches -> 1).
+// (3 launches -> 1).  Every load of a lane that does not depend on another is
+// issued before the first use of any of them: the kernel is a short chain of
+// round trips to memory, and each one saved shows.
 //
 // Formulas: include/ai/Kernels.hpp:132-161.  Split and merge after the idea of
 // src/gpu/Kernels.metal:284-345 (128-key partitions there, 64-key pages here).
@@ -76,228 +78,222 @@ template <> struct RawPair<__nv_bfloat16> {
     __device__ __forceinline__ float2 get() const { return __bfloat1622float2(v); }
 };
 
-// DP: pairs of head dimensions per lane (lane owns dims 2*lane + 64*i, +1).
-template <typename TE, int DP>
-__global__ void __launch_bounds__(AD_WARPS * 32)
+// DP: pairs of head dimensions per lane (lane owns dims 2*lane + 64*i, +1).  NW: warps per block.
+template <typename TE, int DP, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restrict__ k_new, long long ldk,
                         const TE* __restrict__ v_new, long long ldv, TE* __restrict__ out, long long ldo,
                         TE* kv, const int* __restrict__ block_table, int max_pages,
-                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_tokens,
-                        int n_heads, int n_kv_heads, int head_dim, float scale, int window, int n_splits,
-                        float* part_o, float* part_ml, int* tickets) {
-    __shared__ float q_smem[AD_WARPS][DP * 64];
+                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
+                        int n_kv_heads, int head_dim, float scale, int window) {
+    __shared__ float q_smem[DP * 64];
+    __shared__ float part_o[NW][DP * 64];
+    __shared__ float part_m[NW], part_l[NW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * AD_WARPS + warp;
-    if (item >= (long long)n_tokens * n_heads) return;
-    const int page_idx = blockIdx.y;
-    const int t = (int)(item / n_heads), h = (int)(item % n_heads);
+    const int t = blockIdx.x / n_heads, h = blockIdx.x % n_heads;
     const int group = n_heads / n_kv_heads;
     const int kvh = h / group;
+    pdl_trigger();
+    // positions and page lists were set before this step began: they may be read at once
     const int pos = tok_pos[t];
+    const int* pages = block_table + (long long)(tok_seq ? tok_seq[t] : t) * max_pages;
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = first / AD_PAGE, last_page = pos / AD_PAGE;
-    if (page_idx < first_page || page_idx > last_page) return;      // no key of this page is visible
-
-    const int* pages = block_table + (long long)tok_seq[t] * max_pages;
     const long long head_stride = (long long)AD_PAGE * head_dim;
-    TE* kpage = kv + ((long long)pages[page_idx] * 2 * n_kv_heads + kvh) * head_stride;
-    TE* vpage = kpage + (long long)n_kv_heads * head_stride;
-    const int base = page_idx * AD_PAGE;
-    const int lo = max(first - base, 0);                       // first visible key inside the page
-    const int hi = min(pos + 1 - base, AD_PAGE);               // one past the last visible key
-    const bool has_new = (k_new != nullptr) && page_idx == last_page;   // the query's own key lives here
-    const int hi_cache = has_new ? hi - 1 : hi;                // keys to be read from the cache
-    const TE* kn = has_new ? k_new + (long long)t * ldk + kvh * head_dim : nullptr;
-    const TE* vn = has_new ? v_new + (long long)t * ldv + kvh * head_dim : nullptr;
+    constexpr int VC = 64 / (DP * (int)(sizeof(TE) / 2));      // keys whose values fit 64 registers
 
-    // The values are asked for first, so that they travel while the scores are computed: VC keys
-    // at a time (as many as fit 64 registers), each lane its own dimensions of every key.  These
-    // rows were written by earlier steps, so they may be read before the kernels ahead have finished.
-    pdl_trigger();
-    constexpr int VC = 64 / (DP * (int)(sizeof(TE) / 2));
+    float m_run = -INFINITY, l_run = 0.0f;
+    float2 acc[DP];
+#pragma unroll
+    for (int i = 0; i < DP; ++i) acc[i] = make_float2(0.0f, 0.0f);
+
+    // What a page needs: where it lies, which of its keys are visible, whether the new key is in it.
+    struct PageView {
+        TE* kpage; TE* vpage;
+        int lo, hi, hi_cache;
+        bool has_new;
+    };
+    auto view_of = [&](int page_idx) {
+        PageView pv;
+        pv.kpage = kv + ((long long)pages[page_idx] * 2 * n_kv_heads + kvh) * head_stride;
+        pv.vpage = pv.kpage + (long long)n_kv_heads * head_stride;
+        const int base = page_idx * AD_PAGE;
+        pv.lo = max(first - base, 0);                          // first visible key inside the page
+        pv.hi = min(pos + 1 - base, AD_PAGE);                  // one past the last visible key
+        pv.has_new = (k_new != nullptr) && page_idx == last_page;   // the query's own key lives here
+        pv.hi_cache = pv.has_new ? pv.hi - 1 : pv.hi;          // keys to be read from the cache
+        return pv;
+    };
     RawPair<TE> vreg[VC][DP];
-    auto fetch_values = [&](int j0) {
+    auto fetch_values = [&](const PageView& pv, int j0) {
 #pragma unroll
         for (int jj = 0; jj < VC; ++jj) {
             const int j = j0 + jj;
-            const TE* vrow = vpage + (long long)j * head_dim;
+            const TE* vrow = pv.vpage + (long long)j * head_dim;
 #pragma unroll
             for (int i = 0; i < DP; ++i) {
                 const int d = 2 * lane + 64 * i;
-                if (j >= lo && j < hi_cache && d < head_dim) vreg[jj][i].load(vrow + d);
+                if (j >= pv.lo && j < pv.hi_cache && d < head_dim) vreg[jj][i].load(vrow + d);
                 else vreg[jj][i].zero();
             }
         }
     };
-    const int v_first = (lo / VC) * VC;                     // chunk that holds the first visible key
-    fetch_values(v_first);
-    pdl_wait();                                             // this step's query, key and value from here on
 
-    float* qs = q_smem[warp];
-    for (int d = lane; d < head_dim; d += 32) qs[d] = to_float(q[(long long)t * ldq + h * head_dim + d]);
-    if (has_new && h % group == 0) {
-        // append: this step's key and value of the kv head go to their place in the page
-        TE* kd = kpage + (long long)(hi - 1) * head_dim;
-        TE* vd = vpage + (long long)(hi - 1) * head_dim;
-        for (int d = lane; d < head_dim; d += 32) { kd[d] = kn[d]; vd[d] = vn[d]; }
+    // The warp's first page: its values are asked for before anything else (rows written by earlier
+    // steps, untouched by the kernels ahead of this one), so that they travel during the wait.
+    const int my_first = first_page + warp;
+    PageView pv = {};
+    if (my_first <= last_page) {
+        pv = view_of(my_first);
+        fetch_values(pv, (pv.lo / VC) * VC);
     }
-    __syncwarp();
+    pdl_wait();                                                 // this step's query, key and value from here on
+    for (int d = threadIdx.x; d < head_dim; d += NW * 32) q_smem[d] = to_float(q[(long long)t * ldq + h * head_dim + d]);
+    __syncthreads();
 
-    // scores: lane -> keys lane and lane + 32 of the page
-    float s0 = -INFINITY, s1 = -INFINITY;
-    {
-        const int j0 = lane, j1 = lane + 32;
-        const bool in0 = j0 >= lo && j0 < hi_cache, in1 = j1 >= lo && j1 < hi_cache;
-        const bool new0 = has_new && j0 == hi - 1, new1 = has_new && j1 == hi - 1;
-        const TE* k0 = in0 ? kpage + (long long)j0 * head_dim : kn;
-        const TE* k1 = in1 ? kpage + (long long)j1 * head_dim : kn;
-        if (in0 || new0) s0 = dot_head(qs, k0, head_dim) * scale;
-        if (in1 || new1) s1 = dot_head(qs, k1, head_dim) * scale;
-    }
-    const float m = warp_max(fmaxf(s0, s1));
-    const float p0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - m);
-    const float p1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - m);
-    const float l = warp_sum(p0 + p1);
+    for (int page_idx = my_first; page_idx <= last_page; page_idx += NW) {
+        if (page_idx != my_first) {
+            pv = view_of(page_idx);
+            fetch_values(pv, (pv.lo / VC) * VC);
+        }
+        TE* kpage = pv.kpage;
+        TE* vpage = pv.vpage;
+        const int lo = pv.lo, hi = pv.hi, hi_cache = pv.hi_cache;
+        const bool has_new = pv.has_new;
+        const int v_first = (lo / VC) * VC;                     // chunk that holds the first visible key
+        const TE* kn = has_new ? k_new + (long long)t * ldk + kvh * head_dim : nullptr;
+        const TE* vn = has_new ? v_new + (long long)t * ldv + kvh * head_dim : nullptr;
+        if (has_new && h % group == 0) {
+            // append: this step's key and value of the kv head go to their place in the page
+            TE* kd = kpage + (long long)(hi - 1) * head_dim;
+            TE* vd = vpage + (long long)(hi - 1) * head_dim;
+            for (int d = lane; d < head_dim; d += 32) { kd[d] = kn[d]; vd[d] = vn[d]; }
+        }
 
-    float2 acc[DP];
+        // scores: lane -> keys lane and lane + 32 of the page
+        float s0 = -INFINITY, s1 = -INFINITY;
+        {
+            const int j0 = lane, j1 = lane + 32;
+            const bool in0 = j0 >= lo && j0 < hi_cache, in1 = j1 >= lo && j1 < hi_cache;
+            const bool new0 = has_new && j0 == hi - 1, new1 = has_new && j1 == hi - 1;
+            const TE* k0 = in0 ? kpage + (long long)j0 * head_dim : kn;
+            const TE* k1 = in1 ? kpage + (long long)j1 * head_dim : kn;
+            if (in0 || new0) s0 = dot_head(q_smem, k0, head_dim) * scale;
+            if (in1 || new1) s1 = dot_head(q_smem, k1, head_dim) * scale;
+        }
+        const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));        // finite: the page has a visible key
+        const float p0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - m_new);
+        const float p1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - m_new);
+        const float corr = expf(m_run - m_new);                          // 0 for the warp's first page
+        l_run = l_run * corr + warp_sum(p0 + p1);
+        m_run = m_new;
 #pragma unroll
-    for (int i = 0; i < DP; ++i) acc[i] = make_float2(0.0f, 0.0f);
-    for (int c0 = v_first; c0 < hi_cache; c0 += VC) {
-        if (c0 != v_first) fetch_values(c0);
+        for (int i = 0; i < DP; ++i) { acc[i].x *= corr; acc[i].y *= corr; }
+
+        for (int c0 = v_first; c0 < hi_cache; c0 += VC) {
+            if (c0 != v_first) fetch_values(pv, c0);
 #pragma unroll
-        for (int jj = 0; jj < VC; ++jj) {
-            const int j = c0 + jj;                           // keys outside [lo, hi_cache) carry p = 0 or v = 0
-            const float pj = __shfl_sync(0xffffffffu, (j < 32) ? p0 : p1, j & 31);
+            for (int jj = 0; jj < VC; ++jj) {
+                const int j = c0 + jj;                           // keys outside [lo, hi_cache) carry p = 0 or v = 0
+                const float pj = __shfl_sync(0xffffffffu, (j < 32) ? p0 : p1, j & 31);
+#pragma unroll
+                for (int i = 0; i < DP; ++i) {
+                    const float2 v = vreg[jj][i].get();
+                    acc[i].x = fmaf(pj, v.x, acc[i].x);
+                    acc[i].y = fmaf(pj, v.y, acc[i].y);
+                }
+            }
+        }
+        if (has_new) {
+            const int j = hi - 1;
+            const float pj = (j < 32) ? __shfl_sync(0xffffffffu, p0, j) : __shfl_sync(0xffffffffu, p1, j - 32);
 #pragma unroll
             for (int i = 0; i < DP; ++i) {
-                const float2 v = vreg[jj][i].get();
-                acc[i].x = fmaf(pj, v.x, acc[i].x);
-                acc[i].y = fmaf(pj, v.y, acc[i].y);
+                const int d = 2 * lane + 64 * i;
+                if (d < head_dim) {
+                    const float2 v = load2(vn + d);
+                    acc[i].x = fmaf(pj, v.x, acc[i].x);
+                    acc[i].y = fmaf(pj, v.y, acc[i].y);
+                }
             }
         }
     }
-    if (has_new) {
-        const int j = hi - 1;
-        const float pj = (j < 32) ? __shfl_sync(0xffffffffu, p0, j) : __shfl_sync(0xffffffffu, p1, j - 32);
-#pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            const int d = 2 * lane + 64 * i;
-            if (d < head_dim) {
-                const float2 v = load2(vn + d);
-                acc[i].x = fmaf(pj, v.x, acc[i].x);
-                acc[i].y = fmaf(pj, v.y, acc[i].y);
-            }
-        }
-    }
-
-    const int n_visible = last_page - first_page + 1;
-    if (n_visible == 1) {                                   // nothing to merge
-        const float inv = 1.0f / l;
-#pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            const int d = 2 * lane + 64 * i;
-            if (d < head_dim) {
-                TE* o = out + (long long)t * ldo + h * head_dim + d;
-                o[0] = from_float<TE>(acc[i].x * inv);
-                o[1] = from_float<TE>(acc[i].y * inv);
-            }
-        }
-        return;
-    }
-
-    const long long unit = item * n_splits + page_idx;
 #pragma unroll
     for (int i = 0; i < DP; ++i) {
         const int d = 2 * lane + 64 * i;
-        if (d < head_dim) *reinterpret_cast<float2*>(part_o + unit * head_dim + d) = acc[i];
+        if (d < head_dim) { part_o[warp][d] = acc[i].x; part_o[warp][d + 1] = acc[i].y; }
     }
-    if (lane == 0) {
-        part_ml[unit * 2] = m;
-        part_ml[unit * 2 + 1] = l;
-    }
-    __threadfence();                                        // the partial is out before the ticket is taken
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(&tickets[item], 1);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != n_visible - 1) return;
-    __threadfence();                                        // the others' partials are visible from here on
-    if (lane == 0) tickets[item] = 0;                       // ready for the next launch
+    if (lane == 0) { part_m[warp] = m_run; part_l[warp] = l_run; }
+    __syncthreads();
 
-    const float* ml = part_ml + item * n_splits * 2;
+    // merge in warp order; warps without a page carry max = -inf and are skipped
     float big = -INFINITY;
-    for (int s = first_page; s <= last_page; ++s) big = fmaxf(big, __ldcg(ml + 2 * s));
+#pragma unroll
+    for (int w = 0; w < NW; ++w) big = fmaxf(big, part_m[w]);
     float total = 0.0f;
-    float2 o[DP];
 #pragma unroll
-    for (int i = 0; i < DP; ++i) o[i] = make_float2(0.0f, 0.0f);
-#pragma unroll 4
-    for (int s = first_page; s <= last_page; ++s) {
-        const float w = expf(__ldcg(ml + 2 * s) - big);
-        total = fmaf(__ldcg(ml + 2 * s + 1), w, total);
-        const float* po = part_o + (item * n_splits + s) * head_dim;
-#pragma unroll
-        for (int i = 0; i < DP; ++i) {
-            const int d = 2 * lane + 64 * i;
-            if (d < head_dim) {
-                const float2 v = __ldcg(reinterpret_cast<const float2*>(po + d));
-                o[i].x = fmaf(v.x, w, o[i].x);
-                o[i].y = fmaf(v.y, w, o[i].y);
-            }
-        }
-    }
+    for (int w = 0; w < NW; ++w) total += part_m[w] == -INFINITY ? 0.0f : part_l[w] * expf(part_m[w] - big);
     const float inv = 1.0f / total;
+    for (int d = threadIdx.x; d < head_dim; d += NW * 32) {
+        float o = 0.0f;
 #pragma unroll
-    for (int i = 0; i < DP; ++i) {
-        const int d = 2 * lane + 64 * i;
-        if (d < head_dim) {
-            TE* dst = out + (long long)t * ldo + h * head_dim + d;
-            dst[0] = from_float<TE>(o[i].x * inv);
-            dst[1] = from_float<TE>(o[i].y * inv);
-        }
+        for (int w = 0; w < NW; ++w)
+            if (part_m[w] != -INFINITY) o = fmaf(part_o[w][d], expf(part_m[w] - big), o);
+        out[(long long)t * ldo + h * head_dim + d] = from_float<TE>(o * inv);
     }
 }
 
 }  // namespace mu
 
-// One query token per sequence.  n_splits = pages per sequence that the launch covers (at least
-// max position / 64 + 1).  Scratch: part_o [n_tokens * n_heads * n_splits * head_dim] floats,
-// part_ml [n_tokens * n_heads * n_splits * 2] floats, tickets [n_tokens * n_heads] ints that are
-// zero before the first launch (each launch leaves them zero).  k_new / v_new: this step's keys
-// and values ([n_tokens, n_kv_heads * head_dim] views) to be appended, or null if the cache holds
-// them already.  The cache must have pages of 64 positions.
+// One query token per sequence.  n_splits: warps per block, each taking every n_splits-th page of
+// its sequence (1, 2, 4, 8 or 16; more pages than warps are folded by the warps in turn).
+// part_o, part_ml and tickets are not used (the merge happens in shared memory) and may be null.
+// tok_seq may be null when token t belongs to sequence t.  k_new / v_new: this step's keys and
+// values ([n_tokens, n_kv_heads * head_dim] views) to be appended, or null if the cache holds them
+// already.  The cache must have pages of 64 positions.
 MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_new, long long ldk,
                                   const void* v_new, long long ldv, void* out, long long ldo, void* kv,
                                   const int* block_table, int max_pages, int page_tokens,
                                   const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads,
                                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                                   float* part_o, float* part_ml, int* tickets, int is_bf16, void* stream) {
+    (void)part_o; (void)part_ml; (void)tickets;
     if (n_tokens <= 0) return MU_OK;
     if (page_tokens != mu::AD_PAGE) return MU_ERR_UNSUPPORTED_SIZE;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0) return MU_ERR_BAD_ARGUMENT;
-    if (!q || !out || !kv || !block_table || !tok_pos || !tok_seq) return MU_ERR_BAD_ARGUMENT;
+    if (!q || !out || !kv || !block_table || !tok_pos) return MU_ERR_BAD_ARGUMENT;
     if ((k_new == nullptr) != (v_new == nullptr)) return MU_ERR_BAD_ARGUMENT;
-    if (n_splits < 1 || n_splits > max_pages || n_splits > 65535) return MU_ERR_BAD_ARGUMENT;
-    if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return MU_ERR_BAD_ARGUMENT;
+    if (n_splits < 1) return MU_ERR_BAD_ARGUMENT;
     const long long items = (long long)n_tokens * n_heads;
-    dim3 grid((unsigned)((items + mu::AD_WARPS - 1) / mu::AD_WARPS), n_splits);
+    if (items > 2147483647ll) return MU_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((unsigned)items);
     cudaStream_t s = (cudaStream_t)stream;
     const int dp = (head_dim + 63) / 64;
-#define MU_AD(TE, DP)                                                                                  \
-    rc = mu::launch_pdl(mu::attention_decode_kernel<TE, DP>, grid, dim3(mu::AD_WARPS * 32), 0, s, 1,    \
-        (const TE*)q, ldq, (const TE*)k_new, ldk, (const TE*)v_new, ldv, (TE*)out, ldo, (TE*)kv,       \
-        block_table, max_pages, tok_pos, tok_seq, n_tokens, n_heads, n_kv_heads, head_dim, scale,      \
-        window, n_splits, part_o, part_ml, tickets)
-#define MU_AD_T(TE)                      \
-    do {                                 \
-        if (dp <= 1) MU_AD(TE, 1);       \
-        else if (dp <= 2) MU_AD(TE, 2);  \
-        else MU_AD(TE, 4);               \
-    } while (0)
+    const int nw = n_splits >= 16 ? 16 : n_splits >= 8 ? 8 : n_splits >= 4 ? 4 : n_splits >= 2 ? 2 : 1;
     int rc = MU_OK;
+#define MU_AD(TE, DP, NW)                                                                               \
+    rc = mu::launch_pdl(mu::attention_decode_kernel<TE, DP, NW>, grid, dim3(NW * 32), 0, s, 1,          \
+        (const TE*)q, ldq, (const TE*)k_new, ldk, (const TE*)v_new, ldv, (TE*)out, ldo, (TE*)kv,       \
+        block_table, max_pages, tok_pos, tok_seq, n_heads, n_kv_heads, head_dim, scale, window)
+#define MU_AD_W(TE, DP)                        \
+    do {                                       \
+        if (nw == 16) MU_AD(TE, DP, 16);       \
+        else if (nw == 8) MU_AD(TE, DP, 8);    \
+        else if (nw == 4) MU_AD(TE, DP, 4);    \
+        else if (nw == 2) MU_AD(TE, DP, 2);    \
+        else MU_AD(TE, DP, 1);                 \
+    } while (0)
+#define MU_AD_T(TE)                        \
+    do {                                   \
+        if (dp <= 1) MU_AD_W(TE, 1);       \
+        else if (dp <= 2) MU_AD_W(TE, 2);  \
+        else MU_AD_W(TE, 4);               \
+    } while (0)
     if (is_bf16) MU_AD_T(__nv_bfloat16);
     else MU_AD_T(float);
 #undef MU_AD_T
+#undef MU_AD_W
 #undef MU_AD
     return rc;
 }

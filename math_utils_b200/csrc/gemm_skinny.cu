@@ -107,22 +107,71 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     pdl_wait();                                            // activations, bias and residual from here on
 
     if (LN) {
+        // One warp per row.  The row is read once, as float4, into registers (all loads of a lane
+        // issued back to back: one round trip to L2 instead of one per element); rows too long for
+        // that are read three times with the same arithmetic.
+        constexpr int LNV = 16;                               // float4 per lane kept in registers
         const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+        const int n4 = K / 4;
         for (int m = w; m < MP; m += SK_WARPS) {
             __nv_bfloat16* dst = act_smem + (long long)m * act_ld;
             if (m >= M) {
-                for (int k = ln; k < K; k += 32) dst[k] = __float2bfloat16_rn(0.0f);
+                for (int k = ln * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
                 continue;
             }
             const float* src = norm.x + (long long)(norm.rows ? norm.rows[m] : m) * norm.ldx;
-            float sum = 0.0f;
-            for (int k = ln; k < K; k += 32) sum += src[k];
-            const float mean = warp_sum(sum) / (float)K;
-            float sq = 0.0f;
-            for (int k = ln; k < K; k += 32) { const float c = src[k] - mean; sq += c * c; }
-            const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
-            for (int k = ln; k < K; k += 32)
-                dst[k] = __float2bfloat16_rn((src[k] - mean) * inv * norm.gamma[k] + (norm.beta ? norm.beta[k] : 0.0f));
+            if (n4 <= 32 * LNV && (norm.ldx % 4 == 0) && (((uintptr_t)norm.x & 15) == 0)) {
+                const float4* src4 = reinterpret_cast<const float4*>(src);
+                float4 v[LNV];
+#pragma unroll
+                for (int i = 0; i < LNV; ++i) {
+                    const int idx = ln + 32 * i;
+                    v[i] = idx < n4 ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+                float sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < LNV; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+                const float mean = warp_sum(sum) / (float)K;
+                float sq = 0.0f;
+#pragma unroll
+                for (int i = 0; i < LNV; ++i) {
+                    if (ln + 32 * i < n4) {
+                        const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+                        sq += (a * a + b * b) + (c * c + d * d);
+                    }
+                }
+                const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+                const float4* g4 = reinterpret_cast<const float4*>(norm.gamma);
+                const float4* b4 = reinterpret_cast<const float4*>(norm.beta);
+#pragma unroll
+                for (int i = 0; i < LNV; ++i) {
+                    const int idx = ln + 32 * i;
+                    if (idx < n4) {
+                        const float4 gg = g4[idx];
+                        const float4 bb = norm.beta ? b4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        __nv_bfloat162 lo = __floats2bfloat162_rn((v[i].x - mean) * inv * gg.x + bb.x,
+                                                                  (v[i].y - mean) * inv * gg.y + bb.y);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn((v[i].z - mean) * inv * gg.z + bb.z,
+                                                                  (v[i].w - mean) * inv * gg.w + bb.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(dst + 4 * idx) = packed;
+                    }
+                }
+            } else {
+                float sum = 0.0f;
+#pragma unroll 8
+                for (int k = ln; k < K; k += 32) sum += src[k];
+                const float mean = warp_sum(sum) / (float)K;
+                float sq = 0.0f;
+#pragma unroll 8
+                for (int k = ln; k < K; k += 32) { const float c = src[k] - mean; sq += c * c; }
+                const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+#pragma unroll 8
+                for (int k = ln; k < K; k += 32)
+                    dst[k] = __float2bfloat16_rn((src[k] - mean) * inv * norm.gamma[k] + (norm.beta ? norm.beta[k] : 0.0f));
+            }
         }
         __syncthreads();
     }
@@ -238,7 +287,7 @@ static int launch_skinny(const __nv_bfloat16* A, const __nv_bfloat16* W, const f
     else if (N >= 16 * 4 * 296) MU_SK(4, 2, 1);
     else if (N >= 16 * 2 * 296) MU_SK(2, 4, 1);
     else if (tiles < 74 && k_blocks >= 64) MU_SK(1, 8, 4);
-    else if (tiles < 148 && k_blocks >= 16) MU_SK(1, 8, 2);
+    else if (tiles < 148 && k_blocks >= 48) MU_SK(1, 8, 2);
     else MU_SK(1, 8, 1);
 #undef MU_SK
 }

@@ -416,25 +416,23 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
 def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
                      out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, page_tokens: int,
                      tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                     window: int, n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor) -> torch.Tensor:
+                     window: int, n_splits: int, part_o: Optional[torch.Tensor] = None,
+                     part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-token attention, one launch: appends ``k_new`` / ``v_new`` (if
-    given), attends page by page, merges.  ``n_splits``: pages per sequence to
-    cover (the longest sequence's page count at least)."""
-    _need_cuda(q, k_new, v_new, out, kv_pages, block_table, tok_pos, tok_seq, part_o, part_ml)
+    given), attends page by page, merges in shared memory.  ``n_splits``: how
+    many warps share a sequence's pages (its page count is a good choice; at most
+    16 are used).  ``tok_seq`` None: token t is sequence t.  The scratch
+    arguments are accepted for older callers and ignored."""
+    _need_cuda(q, k_new, v_new, out, kv_pages, block_table, tok_pos, tok_seq)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     n_tokens = q.shape[0]
-    tickets = zeroed_workspace("attention_tickets", q.device, n_tokens * n_heads * 4)
-    need_o = n_tokens * n_heads * n_splits * head_dim
-    if n_splits > 1 and (part_o is None or part_ml is None or part_o.numel() < need_o
-                         or part_ml.numel() < n_tokens * n_heads * n_splits * 2):
-        raise KernelError("split attention needs float32 scratch for its partial results")
     _check(library().mu_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
         v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
         _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
-        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml),
-        _ptr(tickets), _is_bf16(kv_pages), _stream()),
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), None, None, None,
+        _is_bf16(kv_pages), _stream()),
         f"attention_decode(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
     return out
 

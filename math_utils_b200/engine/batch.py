@@ -91,12 +91,9 @@ class StepContext:
             self.workspace[key] = buf
         return buf
 
-    def decode_scratch(self, n_heads: int, head_dim: int, page_tokens: int):
-        """(pages per sequence to cover, partial values, partial max/sum) for
-        the single-token attention kernel."""
-        n_pages = max(1, -(-self.max_kv_len // page_tokens))
-        units = self.n_tokens * n_heads * n_pages
-        return n_pages, self.scratch("attn_part_o", units * head_dim), self.scratch("attn_part_ml", units * 2)
+    def decode_pages(self, page_tokens: int) -> int:
+        """Pages per sequence that a single-token step has to cover at most."""
+        return max(1, -(-self.max_kv_len // page_tokens))
 
     def attention_splits(self, n_heads: int, head_dim: int):
         """How single-token steps split each head's keys over warps: enough

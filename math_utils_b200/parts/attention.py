@@ -66,11 +66,10 @@ class CausalSelfAttention(Mixer):
         attn = torch.empty((ctx.n_tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
         if ctx.is_decode and cache.page_tokens == 64:
             # one launch: append this token's key and value, attend page by page, merge
-            n_pages, part_o, part_ml = ctx.decode_scratch(self.n_heads, self.head_dim, cache.page_tokens)
             ops.attention_decode(q, k if owns_cache else None, v if owns_cache else None, attn, cache.pages,
-                                 table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, self.n_heads,
-                                 self.n_kv_heads, self.head_dim, self.scale, self.window, n_pages,
-                                 part_o, part_ml)
+                                 table, cache.page_tokens, ctx.tok_pos, None, self.n_heads,
+                                 self.n_kv_heads, self.head_dim, self.scale, self.window,
+                                 ctx.decode_pages(cache.page_tokens))
         else:
             if owns_cache:
                 ops.kv_append(k, v, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens,

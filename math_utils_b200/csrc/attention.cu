@@ -44,6 +44,32 @@ __global__ void kv_append_kernel(const TE* __restrict__ k, long long ldk, const 
     }
 }
 
+// The same copy in 16-byte pieces, for rows and strides that allow it.
+template <typename TE>
+__global__ void kv_append_vec_kernel(const TE* __restrict__ k, long long ldk, const TE* __restrict__ v,
+                                     long long ldv, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                     int max_pages, int page_tokens, int n_kv_heads, int head_dim,
+                                     TE* __restrict__ kv) {
+    constexpr int E = 16 / (int)sizeof(TE);               // elements per piece
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const long long page = block_table[(long long)tok_seq[t] * max_pages + pos / page_tokens];
+    const int off = pos % page_tokens;
+    const int pieces_per_head = head_dim / E, pieces = n_kv_heads * pieces_per_head;
+    const long long head_stride = (long long)page_tokens * head_dim;
+    TE* kdst = kv + (page * 2 + 0) * n_kv_heads * head_stride + (long long)off * head_dim;
+    TE* vdst = kv + (page * 2 + 1) * n_kv_heads * head_stride + (long long)off * head_dim;
+#pragma unroll 2
+    for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+        const int h = i / pieces_per_head, d = (i % pieces_per_head) * E;
+        const uint4 kk = *reinterpret_cast<const uint4*>(k + (long long)t * ldk + h * head_dim + d);
+        const uint4 vv = *reinterpret_cast<const uint4*>(v + (long long)t * ldv + h * head_dim + d);
+        *reinterpret_cast<uint4*>(kdst + h * head_stride + d) = kk;
+        *reinterpret_cast<uint4*>(vdst + h * head_stride + d) = vv;
+    }
+}
+
 __device__ __forceinline__ float dot_row(const float* qs, const float* krow, int head_dim) {
     float s = 0.0f;
     for (int d = 0; d < head_dim; d += 4) {
@@ -204,6 +230,20 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
     if (!k || !v || !kv || !tok_pos || !tok_seq || !block_table) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = n_kv_heads * head_dim >= 256 ? 256 : 128;
+    const int e = is_bf16 ? 8 : 4;
+    if (ldk % e == 0 && ldv % e == 0 && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) && !((uintptr_t)kv & 15)) {
+        const int vthreads = n_kv_heads * head_dim / e >= 128 ? 128 : 64;
+        if (is_bf16)
+            mu::kv_append_vec_kernel<__nv_bfloat16><<<n_tokens, vthreads, 0, s>>>(
+                (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table,
+                max_pages, page_tokens, n_kv_heads, head_dim, (__nv_bfloat16*)kv);
+        else
+            mu::kv_append_vec_kernel<float><<<n_tokens, vthreads, 0, s>>>(
+                (const float*)k, ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages,
+                page_tokens, n_kv_heads, head_dim, (float*)kv);
+        MU_CHECK_LAUNCH();
+        return MU_OK;
+    }
     if (is_bf16)
         mu::kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(
             (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq,

@@ -58,6 +58,38 @@ __device__ __forceinline__ float dot_head(const float* qs, const __nv_bfloat16* 
     return s0 + s1;
 }
 
+// Two dot products at once: the loads of both rows are issued before either is used.
+__device__ __forceinline__ void dot_head2(const float* qs, const float* ka, const float* kb, int head_dim,
+                                          float& sa, float& sb) {
+    float a = 0.0f, b = 0.0f;
+#pragma unroll 4
+    for (int d = 0; d < head_dim; d += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(ka + d);
+        const float4 y = *reinterpret_cast<const float4*>(kb + d);
+        a = fmaf(qs[d], x.x, a); a = fmaf(qs[d + 1], x.y, a); a = fmaf(qs[d + 2], x.z, a); a = fmaf(qs[d + 3], x.w, a);
+        b = fmaf(qs[d], y.x, b); b = fmaf(qs[d + 1], y.y, b); b = fmaf(qs[d + 2], y.z, b); b = fmaf(qs[d + 3], y.w, b);
+    }
+    sa = a; sb = b;
+}
+__device__ __forceinline__ void dot_head2(const float* qs, const __nv_bfloat16* ka, const __nv_bfloat16* kb,
+                                          int head_dim, float& sa, float& sb) {
+    float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+#pragma unroll 8
+    for (int d = 0; d < head_dim; d += 8) {
+        const uint4 ra = *reinterpret_cast<const uint4*>(ka + d);
+        const uint4 rb = *reinterpret_cast<const uint4*>(kb + d);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+            a0 = fmaf(qs[d + 2 * i], fa.x, a0); a1 = fmaf(qs[d + 2 * i + 1], fa.y, a1);
+            b0 = fmaf(qs[d + 2 * i], fb.x, b0); b1 = fmaf(qs[d + 2 * i + 1], fb.y, b1);
+        }
+    }
+    sa = a0 + a1; sb = b0 + b1;
+}
+
 __device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
 __device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
     return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
@@ -95,8 +127,9 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     const int kvh = h / group;
     pdl_trigger();
     // positions and page lists were set before this step began: they may be read at once
-    const int pos = tok_pos[t];
     const int* pages = block_table + (long long)(tok_seq ? tok_seq[t] : t) * max_pages;
+    const int guess = pages[min(warp, max_pages - 1)];      // the warp's page if nothing is cut by a window
+    const int pos = tok_pos[t];
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = first / AD_PAGE, last_page = pos / AD_PAGE;
     const long long head_stride = (long long)AD_PAGE * head_dim;
@@ -115,7 +148,8 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     };
     auto view_of = [&](int page_idx) {
         PageView pv;
-        pv.kpage = kv + ((long long)pages[page_idx] * 2 * n_kv_heads + kvh) * head_stride;
+        const int page = (page_idx == warp) ? guess : pages[page_idx];
+        pv.kpage = kv + ((long long)page * 2 * n_kv_heads + kvh) * head_stride;
         pv.vpage = pv.kpage + (long long)n_kv_heads * head_stride;
         const int base = page_idx * AD_PAGE;
         pv.lo = max(first - base, 0);                          // first visible key inside the page
@@ -176,10 +210,14 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
             const int j0 = lane, j1 = lane + 32;
             const bool in0 = j0 >= lo && j0 < hi_cache, in1 = j1 >= lo && j1 < hi_cache;
             const bool new0 = has_new && j0 == hi - 1, new1 = has_new && j1 == hi - 1;
-            const TE* k0 = in0 ? kpage + (long long)j0 * head_dim : kn;
-            const TE* k1 = in1 ? kpage + (long long)j1 * head_dim : kn;
-            if (in0 || new0) s0 = dot_head(q_smem, k0, head_dim) * scale;
-            if (in1 || new1) s1 = dot_head(q_smem, k1, head_dim) * scale;
+            // a lane without a visible key reads the page's first visible row and drops the result
+            const TE* safe = (hi_cache > lo) ? kpage + (long long)lo * head_dim : kn;
+            const TE* k0 = in0 ? kpage + (long long)j0 * head_dim : (new0 ? kn : safe);
+            const TE* k1 = in1 ? kpage + (long long)j1 * head_dim : (new1 ? kn : safe);
+            float d0, d1;
+            dot_head2(q_smem, k0, k1, head_dim, d0, d1);
+            if (in0 || new0) s0 = d0 * scale;
+            if (in1 || new1) s1 = d1 * scale;
         }
         const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));        // finite: the page has a visible key
         const float p0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - m_new);
@@ -270,7 +308,12 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
     dim3 grid((unsigned)items);
     cudaStream_t s = (cudaStream_t)stream;
     const int dp = (head_dim + 63) / 64;
-    const int nw = n_splits >= 16 ? 16 : n_splits >= 8 ? 8 : n_splits >= 4 ? 4 : n_splits >= 2 ? 2 : 1;
+    // a warp per page while the GPU has room for them; with many sequences fewer warps per block,
+    // each folding several pages, so that several blocks share an SM and overlap their waits
+    long long room = (148ll * 16 * 2) / items;
+    if (room < 1) room = 1;
+    const int want = n_splits < room ? n_splits : (int)room;
+    const int nw = want >= 16 ? 16 : want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
     int rc = MU_OK;
 #define MU_AD(TE, DP, NW)                                                                               \
     rc = mu::launch_pdl(mu::attention_decode_kernel<TE, DP, NW>, grid, dim3(NW * 32), 0, s, 1,          \

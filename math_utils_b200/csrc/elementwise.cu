@@ -20,6 +20,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     const TW* src = table + row * hidden;
     const TW* psrc = pos_table ? pos_table + (long long)pos[t] * hidden : nullptr;
     float* dst = x + (long long)t * hidden;
+#pragma unroll 4
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
         float v = to_float(src[d]);
         if (psrc) v += to_float(psrc[d]);
@@ -59,6 +60,67 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     }
 }
 
+// One warp per row, the row read once as float4 into registers (every load of a lane issued
+// before the first use), statistics by warp shuffles.  Rows of up to 32 * 16 * 4 = 2048 values.
+constexpr int LN_V = 16;
+constexpr int LN_WARPS = 4;
+
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                      TO* __restrict__ y, int n_rows, int hidden, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * LN_WARPS + warp;
+    if (r >= n_rows) return;
+    const long long src_row = rows ? rows[r] : r;
+    const float4* src4 = reinterpret_cast<const float4*>(x + src_row * hidden);
+    const int n4 = hidden / 4;
+    float4 v[LN_V];
+#pragma unroll
+    for (int i = 0; i < LN_V; ++i) {
+        const int idx = lane + 32 * i;
+        v[i] = idx < n4 ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_V; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float mean = warp_sum(sum) / (float)hidden;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_V; ++i) {
+        if (lane + 32 * i < n4) {
+            const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+            sq += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)hidden + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    TO* dst = y + (long long)r * hidden;
+#pragma unroll
+    for (int i = 0; i < LN_V; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < n4) {
+            const float4 gg = g4[idx];
+            const float4 bb = beta ? b4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            store4(dst + 4 * idx, (v[i].x - mean) * inv * gg.x + bb.x, (v[i].y - mean) * inv * gg.y + bb.y,
+                   (v[i].z - mean) * inv * gg.z + bb.z, (v[i].w - mean) * inv * gg.w + bb.w);
+        }
+    }
+}
+
 }  // namespace mu
 
 // table_bf16: 1 if the tables hold bfloat16, 0 for float32.
@@ -80,10 +142,23 @@ MU_EXPORT int mu_layernorm(const float* x, const int* rows, const float* gamma, 
                            void* y, int n_rows, int hidden, float eps, int out_bf16, void* stream) {
     if (n_rows <= 0) return MU_OK;
     if (hidden <= 0 || !x || !gamma || !y) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool aligned = hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+                         ((uintptr_t)gamma & 15) == 0 && (!beta || ((uintptr_t)beta & 15) == 0);
+    if (aligned && hidden <= 32 * mu::LN_V * 4) {
+        const unsigned blocks = (n_rows + mu::LN_WARPS - 1) / mu::LN_WARPS;
+        if (out_bf16)
+            mu::layernorm_rows_kernel<__nv_bfloat16><<<blocks, mu::LN_WARPS * 32, 0, s>>>(
+                x, rows, gamma, beta, (__nv_bfloat16*)y, n_rows, hidden, eps);
+        else
+            mu::layernorm_rows_kernel<float><<<blocks, mu::LN_WARPS * 32, 0, s>>>(
+                x, rows, gamma, beta, (float*)y, n_rows, hidden, eps);
+        MU_CHECK_LAUNCH();
+        return MU_OK;
+    }
     if (hidden > 12288) return MU_ERR_UNSUPPORTED_SIZE;   // the row must fit 48 KB of shared memory
     const int threads = hidden >= 1024 ? 256 : 128;
     const size_t smem = (size_t)hidden * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
     if (out_bf16)
         mu::layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, s>>>(
             x, rows, gamma, beta, (__nv_bfloat16*)y, hidden, eps);

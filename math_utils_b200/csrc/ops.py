@@ -472,7 +472,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
             return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
         x = x.materialize()
-    if skinny_ok(x, weight):
+    # up to 16 rows the few-rows kernel; up to 64 too, unless the output is wide enough to give
+    # the tensor-core kernel a tile per SM (its TMA pipeline streams the weights faster)
+    if skinny_ok(x, weight) and (x.shape[0] <= 16 or weight.shape[0] < 128 * 148 or not tc_ok(x, weight)):
         return gemm_skinny(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
     if tc_ok(x, weight):
         return gemm_tc(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

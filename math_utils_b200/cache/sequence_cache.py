@@ -263,6 +263,20 @@ class SequenceCache:
             g.reserve(slot, old, new)
         return old
 
+    def reserve_one(self, slot: int) -> bool:
+        """``reserve(slot, 1)`` for the generation loop, which calls it for every
+        sequence at every step: True if a page was taken (the block tables on
+        the device are then out of date)."""
+        old = int(self.lengths[slot])
+        if old >= self.max_positions:
+            raise CacheError(f"slot {slot}: {old + 1} positions exceed the model's {self.max_positions}")
+        took = False
+        for g in self.kv_groups:
+            if old % self.page_tokens == 0 and g.table[slot, old // self.page_tokens] < 0:
+                g.reserve(slot, old, old + 1)
+                took = True
+        return took
+
     def commit(self, slot: int, n_new: int) -> None:
         self.lengths[slot] += n_new
         for g in self.kv_groups:

@@ -92,16 +92,20 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 
     // the first weights are asked for before anything else: they do not depend on the activations
     constexpr int UNROLL = 4;
-    uint4 wa[UNROLL], wb[UNROLL];
-    auto load_weights = [&](int kb) {
+    // two register sets when the accumulators are few: the next batch of weights is on its way
+    // while the tensor cores work on this one
+    constexpr bool DOUBLE = MT <= 2;
+    uint4 wa[UNROLL], wb[UNROLL], wa2[DOUBLE ? UNROLL : 1], wb2[DOUBLE ? UNROLL : 1];
+    auto load_into = [&](int kb, uint4* a, uint4* b) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (kb + u) * 32;
             const bool in = (kb + u) < kb1 && (k + 8 * t) < K;      // K is a multiple of 8
-            wa[u] = in ? load_stream(w0 + k) : make_uint4(0, 0, 0, 0);
-            wb[u] = in ? load_stream(w1 + k) : make_uint4(0, 0, 0, 0);
+            a[u] = in ? load_stream(w0 + k) : make_uint4(0, 0, 0, 0);
+            b[u] = in ? load_stream(w1 + k) : make_uint4(0, 0, 0, 0);
         }
     };
+    auto load_weights = [&](int kb) { load_into(kb, wa, wb); };
     pdl_trigger();
     load_weights(kb0);
     pdl_wait();                                            // activations, bias and residual from here on
@@ -191,8 +195,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-    for (int kb = kb0; kb < kb1; kb += UNROLL) {
-        if (kb != kb0) load_weights(kb);
+    auto multiply = [&](int kb, const uint4* a, const uint4* b) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (kb + u) * 32;
@@ -201,9 +204,22 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             for (int j = 0; j < MT; ++j) {
                 uint4 xb = make_uint4(0, 0, 0, 0);
                 if (in && xvalid[j]) xb = *reinterpret_cast<const uint4*>(xrow[j] + k);
-                mma_bf16_16816(acc[j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
-                mma_bf16_16816(acc[j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
+                mma_bf16_16816(acc[j], a[u].x, b[u].x, a[u].y, b[u].y, xb.x, xb.y);
+                mma_bf16_16816(acc[j], a[u].z, b[u].z, a[u].w, b[u].w, xb.z, xb.w);
             }
+        }
+    };
+    if (DOUBLE) {
+        for (int kb = kb0; kb < kb1; kb += 2 * UNROLL) {
+            if (kb + UNROLL < kb1) load_into(kb + UNROLL, wa2, wb2);
+            multiply(kb, wa, wb);
+            if (kb + 2 * UNROLL < kb1) load_into(kb + 2 * UNROLL, wa, wb);
+            if (kb + UNROLL < kb1) multiply(kb + UNROLL, wa2, wb2);
+        }
+    } else {
+        for (int kb = kb0; kb < kb1; kb += UNROLL) {
+            if (kb != kb0) load_weights(kb);
+            multiply(kb, wa, wb);
         }
     }
 

@@ -52,13 +52,13 @@ _SIGNATURES = {
     "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
     "mu_attention_prefill": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int,
                              _c_int, _c_int, _c_int, _c_f, _c_int, _c_p],
-    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p],
+    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
     "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                             _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p,
                             _c_int, _c_p],
-    "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p],
+    "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
 }
 
 
@@ -343,7 +343,10 @@ def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_
 
 
 # -------------------------------------------------------------------- sampling
-def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed=None) -> torch.Tensor:
+    """First maximum of each row.  ``feed`` = (token_ids, tok_pos, last_pos): the
+    tokens also become the next single-token step's inputs and the positions
+    move on by one (what ``advance`` does, without its launch)."""
     _need_cuda(logits, out)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("logits must be float32 [rows, vocab] with unit inner stride")
@@ -351,13 +354,15 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     ws = zeroed_workspace("argmax", logits.device, 2 * n * 8)
-    _check(library().mu_argmax(_ptr(logits), logits.stride(0), n, vocab, _ptr(out), _ptr(ws), _stream()), "argmax")
+    ids, pos, last = feed if feed is not None else (None, None, 0)
+    _check(library().mu_argmax(_ptr(logits), logits.stride(0), n, vocab, _ptr(out), _ptr(ws), _ptr(ids), _ptr(pos),
+                               int(last), _stream()), "argmax")
     return out
 
 
 def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
            request_ids: Optional[torch.Tensor], draw_index: torch.Tensor,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, feed=None) -> torch.Tensor:
     """One token per row by temperature / top-k; ``draw_index`` (int32 per row)
     counts the draws of each request and is advanced by one."""
     _need_cuda(logits, request_ids, draw_index, out)
@@ -371,7 +376,8 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     _check(library().mu_sample(_ptr(logits), logits.stride(0), n, vocab, float(temperature), int(top_k),
                                int(seed) & ((1 << 64) - 1), _ptr(request_ids), _ptr(draw_index), _ptr(out),
-                               _stream()), "sample")
+                               _ptr(feed[0]) if feed else None, _ptr(feed[1]) if feed else None,
+                               int(feed[2]) if feed else 0, _stream()), "sample")
     return out
 
 

@@ -52,7 +52,8 @@ constexpr int ARGMAX_PARTS = 16;
 
 __global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out,
-              unsigned long long* __restrict__ best_ws, unsigned int* __restrict__ ticket_ws) {
+              unsigned long long* __restrict__ best_ws, unsigned int* __restrict__ ticket_ws,
+              int* __restrict__ feed_ids, int* __restrict__ feed_pos, int last_pos) {
     __shared__ unsigned long long best_smem[ARGMAX_THREADS / 32];
     pdl_trigger();
     pdl_wait();
@@ -61,11 +62,24 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __
     const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
     const int begin = blockIdx.y * per, end = min(vocab, begin + per);
     unsigned long long best = 0;
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        // larger logit wins; among equals the lower index (larger ~index) wins
-        const unsigned long long cand =
-            ((unsigned long long)float_key(row[i]) << 32) | (unsigned int)(0xFFFFFFFFu - (unsigned)i);
-        best = cand > best ? cand : best;
+    constexpr int BATCH = 8;                    // loads of a batch are issued before any is compared
+    for (int i0 = begin + threadIdx.x; i0 < end; i0 += BATCH * ARGMAX_THREADS) {
+        float vals[BATCH];
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const int i = i0 + b * ARGMAX_THREADS;
+            vals[b] = i < end ? row[i] : -INFINITY;
+        }
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const int i = i0 + b * ARGMAX_THREADS;
+            if (i < end) {
+                // larger logit wins; among equals the lower index (larger ~index) wins
+                const unsigned long long cand =
+                    ((unsigned long long)float_key(vals[b]) << 32) | (unsigned int)(0xFFFFFFFFu - (unsigned)i);
+                best = cand > best ? cand : best;
+            }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -83,7 +97,13 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __
             __threadfence();
             const unsigned long long all = atomicExch(&best_ws[r], 0ull);
             ticket_ws[r] = 0;
-            out[r] = (int)(0xFFFFFFFFu - (unsigned int)(all & 0xFFFFFFFFull));
+            const int token = (int)(0xFFFFFFFFu - (unsigned int)(all & 0xFFFFFFFFull));
+            out[r] = token;
+            if (feed_ids) {                     // hand the token to the next single-token step
+                feed_ids[r] = token;
+                const int p = feed_pos[r] + 1;
+                feed_pos[r] = p < last_pos ? p : last_pos;
+            }
         }
     }
 }
@@ -136,7 +156,8 @@ struct RowView {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature, int top_k,
               unsigned long long seed, const long long* __restrict__ request_ids,
-              int* __restrict__ draw_index, int* __restrict__ out) {
+              int* __restrict__ draw_index, int* __restrict__ out, int* __restrict__ feed_ids,
+              int* __restrict__ feed_pos, int last_pos) {
     __shared__ unsigned long long hist[256];
     __shared__ unsigned long long sel[2];
     __shared__ float red[32];
@@ -284,32 +305,44 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     (void)group_mass;
     __syncthreads();
     if (tid == 0) {
-        out[r] = found_idx < vocab ? found_idx : 0;
+        const int token = found_idx < vocab ? found_idx : 0;
+        out[r] = token;
         draw_index[r] += 1;
+        if (feed_ids) {
+            feed_ids[r] = token;
+            const int p = feed_pos[r] + 1;
+            feed_pos[r] = p < last_pos ? p : last_pos;
+        }
     }
 }
 
 }  // namespace mu
 
 // logits [n_rows, ld] float32 -> out[n_rows] token ids.  workspace: 2 * n_rows 64-bit words that are
-// zero before the first launch (each launch leaves them zero).
+// zero before the first launch (each launch leaves them zero).  With feed_ids / feed_pos (both or
+// neither) the tokens are also written to feed_ids and feed_pos moves on by one, up to last_pos:
+// what mu_advance does, without its launch.
 MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out,
-                        unsigned long long* workspace, void* stream) {
+                        unsigned long long* workspace, int* feed_ids, int* feed_pos, int last_pos,
+                        void* stream) {
     if (n_rows <= 0) return MU_OK;
     if (!logits || !out || !workspace || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
+    if ((feed_ids == nullptr) != (feed_pos == nullptr)) return MU_ERR_BAD_ARGUMENT;
     dim3 grid(n_rows, mu::ARGMAX_PARTS);
     return mu::launch_pdl(mu::argmax_kernel, grid, dim3(mu::ARGMAX_THREADS), 0, (cudaStream_t)stream, 1, logits, ld,
-                          vocab, out, workspace, reinterpret_cast<unsigned int*>(workspace + n_rows));
+                          vocab, out, workspace, reinterpret_cast<unsigned int*>(workspace + n_rows), feed_ids,
+                          feed_pos, last_pos);
 }
 
 // request_ids [n_rows] int64 (null: the row index), draw_index [n_rows] int32 is read and
 // then incremented.  temperature must be > 0; the caller routes greedy to mu_argmax.
 MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature,
                         int top_k, unsigned long long seed, const long long* request_ids,
-                        int* draw_index, int* out, void* stream) {
+                        int* draw_index, int* out, int* feed_ids, int* feed_pos, int last_pos, void* stream) {
     if (n_rows <= 0) return MU_OK;
     if (!logits || !out || !draw_index || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
     if (!(temperature > 0.0f) || top_k < 0) return MU_ERR_BAD_ARGUMENT;
     return mu::launch_pdl(mu::sample_kernel, dim3(n_rows), dim3(mu::SAMPLE_THREADS), 0, (cudaStream_t)stream, 1,
-                          logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out);
+                          logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out, feed_ids,
+                          feed_pos, last_pos);
 }

@@ -113,12 +113,12 @@ class DecodeSession:
         ops = self.model.runtime.ops
         logits = self.model.forward(self.ctx, self.cache)
         self.logits = logits
+        feed = (self.token_ids, self.tok_pos, self.kv_bound - 1)     # samples become the next step's inputs
         if self.params.greedy:
-            ops.argmax(logits, out=self.next_tokens)
+            ops.argmax(logits, out=self.next_tokens, feed=feed)
         else:
             ops.sample(logits, self.params.temperature, self.params.top_k, self.params.seed,
-                       self.request_ids, self.draws, out=self.next_tokens)
-        ops.advance(self.token_ids, self.tok_pos, self.next_tokens, self.kv_bound - 1)
+                       self.request_ids, self.draws, out=self.next_tokens, feed=feed)
 
     def capture(self) -> None:
         """Runs the step once eagerly (first-use set-up must not happen inside a

@@ -146,32 +146,43 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
             else:
                 live.remove(k)
                 cache.release(slots.pop(k))
+        windowed = any(g.spec.window > 0 for g in cache.kv_groups)
         while live:
             members = list(live)                         # the graph's batch; some may park later
             session = session_for(model, cache, params, len(members))
             session.rebind([slots[k] for k in members], [states[k].index for k in members],
                            [draws[k] for k in members])
+            place = {k: i for i, k in enumerate(members)}
+            tokens_in = [feed[k] for k in members]
+            positions = [cache.length(slots[k]) for k in members]
             parked = set()
-            last = {k: (feed[k], cache.length(slots[k])) for k in members}
+            dirty = True
             while live and (len(live) * 2 > len(members) or len(members) == 1):
                 for k in live:
-                    cache.reserve(slots[k], 1)
-                    last[k] = (feed[k], cache.length(slots[k]))
-                session.sync_block_tables()
-                session.feed([last[k][0] for k in members], [last[k][1] for k in members])
+                    dirty |= cache.reserve_one(slots[k])
+                if dirty:
+                    session.sync_block_tables()
+                    dirty = False
+                session.feed(tokens_in, positions)
                 session.launch()
                 tokens = session.read_tokens()
+                still = []
                 for k in live:
-                    cache.commit(slots[k], 1)
+                    slot, i = slots[k], place[k]
+                    cache.lengths[slot] += 1             # what commit(slot, 1) does without a window
+                    if windowed:
+                        cache.commit(slot, 0)
                     draws[k] += 1
-                for k, tok in zip(members, tokens):
-                    if k in parked:
-                        continue
-                    if take_token(states[k], int(tok), stop_ids, max_tokens, context):
-                        feed[k] = int(tok)
+                    tok = tokens[i]
+                    if take_token(states[k], tok, stop_ids, max_tokens, context):
+                        tokens_in[i] = tok
+                        positions[i] += 1
+                        still.append(k)
                     else:
-                        parked.add(k)
-                        live.remove(k)
+                        parked.add(k)                    # keeps feeding its last token at its last position
+                live = still
+            for k in live:                               # what a smaller graph goes on with
+                feed[k] = tokens_in[place[k]]
             for k in parked:
                 cache.release(slots.pop(k))
     finally:

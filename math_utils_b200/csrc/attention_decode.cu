@@ -264,20 +264,25 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     if (lane == 0) { part_m[warp] = m_run; part_l[warp] = l_run; }
     __syncthreads();
 
-    // merge in warp order; warps without a page carry max = -inf and are skipped
+    // merge in warp order; warps without a page carry max = -inf and weigh nothing.  The weights
+    // exp(max_w - max) are computed once, by one thread each, not by every thread for itself.
+    __shared__ float weight[NW];
     float big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NW; ++w) big = fmaxf(big, part_m[w]);
-    float total = 0.0f;
+    if (threadIdx.x < NW) weight[threadIdx.x] = part_m[threadIdx.x] == -INFINITY ? 0.0f : expf(part_m[threadIdx.x] - big);
+    __syncthreads();
+    if (threadIdx.x < head_dim) {
+        float total = 0.0f;
 #pragma unroll
-    for (int w = 0; w < NW; ++w) total += part_m[w] == -INFINITY ? 0.0f : part_l[w] * expf(part_m[w] - big);
-    const float inv = 1.0f / total;
-    for (int d = threadIdx.x; d < head_dim; d += NW * 32) {
-        float o = 0.0f;
+        for (int w = 0; w < NW; ++w) total = fmaf(part_l[w], weight[w], total);
+        const float inv = 1.0f / total;
+        for (int d = threadIdx.x; d < head_dim; d += NW * 32) {
+            float o = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w)
-            if (part_m[w] != -INFINITY) o = fmaf(part_o[w][d], expf(part_m[w] - big), o);
-        out[(long long)t * ldo + h * head_dim + d] = from_float<TE>(o * inv);
+            for (int w = 0; w < NW; ++w) o = fmaf(part_o[w][d], weight[w], o);
+            out[(long long)t * ldo + h * head_dim + d] = from_float<TE>(o * inv);
+        }
     }
 }
 

@@ -164,6 +164,9 @@ def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Ten
         raise KernelError("embedding tables must be contiguous")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    if _recorder is not None:
+        _recorder.add_embed(ids, positions, table, pos_table, out)
+        return out
     _check(library().mu_embed(_ptr(ids), _ptr(positions), _ptr(table), _ptr(pos_table), _ptr(out),
                               n, hidden, _is_bf16(table), _stream()), "embed")
     return out
@@ -173,6 +176,7 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor]
               out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """LayerNorm of float32 rows (optionally the rows that ``rows`` picks)."""
+    _not_while_recording("layernorm")
     _need_cuda(x, gamma, beta, rows)
     _i32(rows, "rows")
     if x.dtype != torch.float32 or not x.is_contiguous():
@@ -225,6 +229,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
               out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """out = act(a @ w^T + bias) + residual on CUDA cores, any shape, any of the
     two dtypes; with float32 operands this is the true 32-bit product."""
+    _not_while_recording("gemm_simt")
     m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
     _check(library().mu_gemm_simt(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
@@ -267,6 +272,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
             act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
             out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """The product on the tcgen05 tensor cores (TMA loads, accumulator in tensor memory)."""
+    _not_while_recording("gemm_tc")
     m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
     _check(library().mu_gemm_tc(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
@@ -301,6 +307,7 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: t
               page_tokens: int, n_kv_heads: int, head_dim: int, kv_pages: torch.Tensor) -> None:
     """Copies keys and values of this step's tokens ([T, n_kv_heads * head_dim]
     views, unit inner stride) into their pages."""
+    _not_while_recording("kv_append")
     _need_cuda(k, v, tok_pos, tok_seq, block_table, kv_pages)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -320,6 +327,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_
               part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of each query token ([T, n_heads * head_dim] view) over the
     cached keys first..its position; writes ``out`` [T, n_heads * head_dim]."""
+    _not_while_recording("attention")
     _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, part_o, part_ml)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -429,6 +437,10 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
     many warps share a sequence's pages (its page count is a good choice; at most
     16 are used).  ``tok_seq`` None: token t is sequence t.  The scratch
     arguments are accepted for older callers and ignored."""
+    if _recorder is not None:
+        _recorder.add_attention(q, k_new, v_new, out, kv_pages, block_table, page_tokens, tok_pos, tok_seq,
+                                n_heads, n_kv_heads, head_dim, scale, window)
+        return out
     _need_cuda(q, k_new, v_new, out, kv_pages, block_table, tok_pos, tok_seq)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -472,6 +484,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     dtype and the shape.  float32 operands always take the CUDA-core kernel.
     ``x`` may be a ``NormedInput``: with few rows and bfloat16 weights the norm is
     made inside the product kernel, otherwise it is computed first."""
+    if _recorder is not None:
+        normed = isinstance(x, NormedInput)
+        m = x.n_rows if normed else x.shape[0]
+        if out is None:
+            want = out_dtype or (x.out_dtype if normed else x.dtype)
+            out = torch.empty((m, weight.shape[0]), dtype=want, device=weight.device)
+        _recorder.add_gemm(x, weight, bias, act, residual, out)
+        return out
     if isinstance(x, NormedInput):
         if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 16
                 and x.x.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
@@ -485,3 +505,144 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if tc_ok(x, weight):
         return gemm_tc(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
     return gemm_simt(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
+
+
+# ---------------------------------------------------- a single-token step as one recorded program
+class NotRecordable(RuntimeError):
+    """The step contains an operation the persistent step kernel does not have."""
+
+
+class ProgramOp(ctypes.Structure):
+    """One operation of a recorded step; the layout is ``mu::ProgramOp`` of decode_program.cu."""
+    _fields_ = (
+        [(n, _c_int) for n in ("type", "M", "N", "K", "act", "out_bf16", "has_ln", "ksplit")]
+        + [(n, _c_p) for n in ("a", "w", "bias", "residual", "c", "ln_x", "ln_rows", "ln_gamma", "ln_beta")]
+        + [(n, _c_ll) for n in ("lda", "ldw", "ldc", "ldr", "ln_ldx")]
+        + [("part", _c_p), ("tickets", _c_p), ("ln_eps", _c_f), ("scale", _c_f)]
+        + [(n, _c_p) for n in ("q", "k_new", "v_new", "out", "kv", "block_table", "tok_pos")]
+        + [(n, _c_ll) for n in ("ldq", "ldk", "ldv", "ldo")]
+        + [(n, _c_int) for n in ("max_pages", "n_heads", "n_kv_heads", "head_dim", "window", "n_tokens",
+                                 "hidden", "table_bf16")]
+        + [(n, _c_p) for n in ("ids", "table", "pos_table", "x")])
+
+
+OP_EMBED, OP_GEMM, OP_ATTENTION = 1, 2, 3
+PROGRAM_MAX_ROWS = 16
+
+
+class StepProgram:
+    """The operations of one single-token step, recorded from the model's own
+    forward pass, and everything they point at.  ``run`` executes them in one
+    cooperative kernel."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.ops = []
+        self.keep = []                 # tensors the records point into
+        self.max_rows = 1
+        self.max_ln_k = 0
+        self.n_blocks = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.device_ops = None
+        self.barrier = torch.zeros(2, dtype=torch.int32, device=self.device)
+
+    def _hold(self, *tensors):
+        self.keep.extend(t for t in tensors if t is not None)
+
+    def add_embed(self, ids, positions, table, pos_table, out):
+        op = ProgramOp()
+        op.type, op.n_tokens, op.hidden, op.table_bf16 = OP_EMBED, ids.numel(), table.shape[1], _is_bf16(table)
+        op.ids, op.tok_pos, op.table, op.pos_table, op.x = _ptr(ids), _ptr(positions), _ptr(table), _ptr(pos_table), _ptr(out)
+        self._hold(ids, positions, table, pos_table, out)
+        self.ops.append(op)
+
+    def add_gemm(self, x, w, bias, act, residual, out):
+        op = ProgramOp()
+        normed = isinstance(x, NormedInput)
+        m = x.n_rows if normed else x.shape[0]
+        n, k = w.shape
+        if w.dtype != torch.bfloat16 or m > PROGRAM_MAX_ROWS or k % 8 or w.stride(0) % 8 or w.data_ptr() % 16:
+            raise NotRecordable(f"product {m}x{n}x{k} of {w.dtype}")
+        op.type, op.M, op.N, op.K = OP_GEMM, m, n, k
+        op.act, op.out_bf16, op.has_ln = ACT_CODES[act], _is_bf16(out), int(normed)
+        if normed:
+            if (x.x.dtype != torch.float32 or x.x.stride(1) != 1 or x.x.stride(0) % 4 or x.x.data_ptr() % 16
+                    or k > 2048 or x.out_dtype != torch.bfloat16):
+                raise NotRecordable("a norm the step kernel cannot fold in")
+            op.ln_x, op.ln_ldx, op.ln_rows = _ptr(x.x), x.x.stride(0), _ptr(x.rows)
+            op.ln_gamma, op.ln_beta, op.ln_eps = _ptr(x.gamma), _ptr(x.beta), float(x.eps)
+            self.max_ln_k = max(self.max_ln_k, k)
+            self._hold(x.x, x.rows, x.gamma, x.beta)
+        else:
+            if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+                raise NotRecordable("activations the step kernel cannot read")
+            op.a, op.lda = _ptr(x), x.stride(0)
+            self._hold(x)
+        op.w, op.ldw, op.bias = _ptr(w), w.stride(0), _ptr(bias)
+        op.residual, op.ldr = _ptr(residual), residual.stride(0) if residual is not None else 0
+        op.c, op.ldc = _ptr(out), out.stride(0)
+        # narrow outputs: several blocks share a tile, each a slice of K with at least a k-block per warp
+        tiles, k_blocks = -(-n // 16), -(-k // 32)
+        op.ksplit = max(1, min(self.n_blocks // tiles, k_blocks // 8, 8)) if tiles * 2 <= self.n_blocks else 1
+        if op.ksplit > 1:
+            part = torch.empty(tiles * op.ksplit * 16 * 16, dtype=torch.float32, device=self.device)
+            tickets = torch.zeros(tiles, dtype=torch.int32, device=self.device)
+            op.part, op.tickets = _ptr(part), _ptr(tickets)
+            self._hold(part, tickets)
+        self.max_rows = max(self.max_rows, m)
+        self._hold(w, bias, residual, out)
+        self.ops.append(op)
+
+    def add_attention(self, q, k_new, v_new, out, kv_pages, block_table, page_tokens, tok_pos, tok_seq,
+                      n_heads, n_kv_heads, head_dim, scale, window):
+        if (kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim > 128 or head_dim % 16
+                or tok_seq is not None or q.shape[0] > PROGRAM_MAX_ROWS):
+            raise NotRecordable("attention the step kernel cannot run")
+        op = ProgramOp()
+        op.type, op.n_tokens = OP_ATTENTION, q.shape[0]
+        op.q, op.ldq, op.out, op.ldo = _ptr(q), q.stride(0), _ptr(out), out.stride(0)
+        op.k_new, op.ldk = _ptr(k_new), k_new.stride(0) if k_new is not None else 0
+        op.v_new, op.ldv = _ptr(v_new), v_new.stride(0) if v_new is not None else 0
+        op.kv, op.block_table, op.tok_pos, op.max_pages = _ptr(kv_pages), _ptr(block_table), _ptr(tok_pos), block_table.shape[1]
+        op.n_heads, op.n_kv_heads, op.head_dim, op.window, op.scale = n_heads, n_kv_heads, head_dim, int(window), float(scale)
+        self._hold(q, k_new, v_new, out, kv_pages, block_table, tok_pos)
+        self.ops.append(op)
+
+    def finish(self) -> "StepProgram":
+        size = ctypes.sizeof(ProgramOp)
+        if library().mu_decode_program_op_size() != size:
+            raise KernelError("the recorded-step layout of the Python side and of the kernel library differ")
+        raw = b"".join(bytes(op) for op in self.ops)
+        self.device_ops = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
+        self.dyn_smem = 16 * (self.max_ln_k + 8) * 2 if self.max_ln_k else 0
+        return self
+
+    def run(self, trace: Optional[torch.Tensor] = None) -> None:
+        """``trace``: optional int64 [2 * n_ops] that receives, per operation, when
+        block 0 began and ended its share (nanoseconds of the device's timer)."""
+        lib = library()
+        lib.mu_decode_program.argtypes = [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p]
+        lib.mu_decode_program.restype = _c_int
+        _check(lib.mu_decode_program(_ptr(self.device_ops), len(self.ops), self.max_rows, self.dyn_smem,
+                                     _ptr(self.barrier), _ptr(status_word(self.device)), _ptr(trace), _stream()),
+               "decode_program")
+
+
+_recorder: Optional[StepProgram] = None
+
+
+def begin_record(device) -> None:
+    """From here on ``embed``, ``linear`` and ``attention_decode`` add to a
+    program instead of launching; any other kernel raises ``NotRecordable``."""
+    global _recorder
+    _recorder = StepProgram(device)
+
+
+def end_record() -> Optional[StepProgram]:
+    global _recorder
+    rec, _recorder = _recorder, None
+    return rec
+
+
+def _not_while_recording(name: str) -> None:
+    if _recorder is not None:
+        raise NotRecordable(name)

@@ -317,7 +317,7 @@ decode_program_kernel(const ProgramOp* __restrict__ ops, int n_ops, BarrierState
                             for (int s = 0; s < DP_WARPS; ++s) v += red[s][r][m];
                         }
                         if (op.bias) v += op.bias[n];
-                        v = apply_act(v, op.act);
+                        v = op.out_bf16 ? apply_act_bf16(v, op.act) : apply_act(v, op.act);
                         if (op.residual) v += op.residual[(long long)m * op.ldr + n];
                         if (op.out_bf16) ((__nv_bfloat16*)op.c)[(long long)m * op.ldc + n] = __float2bfloat16_rn(v);
                         else ((float*)op.c)[(long long)m * op.ldc + n] = v;

@@ -260,7 +260,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             for (int c = 0; c < CK - 1; ++c) v += peer[c][r][m];
         }
         if (bias) v += bias[n];
-        v = apply_act(v, act);
+        v = sizeof(TC) == 2 ? apply_act_bf16(v, act) : apply_act(v, act);
         if (residual) v += residual[(long long)m * ldr + n];
         C[(long long)m * ldc + n] = from_float<TC>(v);
     }

@@ -1,17 +1,18 @@
 // C[M, N] = act(A[M, K] . W[N, K]^T + bias) (+ residual) on the 5th-generation tensor cores.
 //
-// The product kernel of whole prompts (bfloat16 in, float32 accumulate).  One
-// block computes one 128 x BN tile of C:
+// The product kernel of whole prompts (bfloat16 in, float32 accumulate).  A
+// block per SM walks over the 128 x BN tiles of C; in each block:
 //   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
 //            of 128 x 64 tiles of A and BN x 64 tiles of W into a ring of
 //            shared-memory stages and arms each stage's "full" mbarrier;
-//   warp 1   allocates BN columns of tensor memory; one lane issues
+//   warp 1   allocates 2 x BN columns of tensor memory (two accumulators that take turns, so
+//            that one tile is read out while the next is being computed); one lane issues
 //            tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per
 //            stage with shared-memory descriptors, the accumulator staying in
 //            tensor memory, and commits each stage back to the producer
 //            ("empty" mbarrier) and at the end the accumulator to the epilogue;
-//   warps 2-5  read the accumulator with tcgen05.ld (each warp its 32 lanes =
-//            32 rows of the tile), add bias, apply the activation, add the
+//   warps 2-9  read the accumulator with tcgen05.ld (each warp 32 rows and half the columns
+//            of the tile), add bias, apply the activation, add the
 //            float32 residual and store bfloat16 or float32.
 // Rows of A and W beyond M, N and K are zero-filled by TMA; the epilogue
 // predicates its stores.  Every wait on an mbarrier is bounded: if it runs out
@@ -22,11 +23,12 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 
 namespace mu {
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BK = 64, TC_EPI_WARPS = 8, TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr unsigned long long TC_WAIT_NS = 2000000000ull;      // a wait gives up after two seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -108,16 +110,24 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <int BN, int STAGES>
 struct TcSmem {
     __nv_bfloat16 a[STAGES][TC_BM * TC_BK];      // each tile 1024-byte aligned: 128 x 128 B
     __nv_bfloat16 b[STAGES][BN * TC_BK];
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
-    uint64_t accum;
+    uint64_t acc_full[2];                        // an accumulator is complete (tensor cores -> epilogue)
+    uint64_t acc_empty[2];                       // an accumulator has been read out (epilogue -> tensor cores)
     uint32_t tmem_base;
 };
 
+// Persistent: a block per SM walks over the tiles of C (tile = block, block + grid, ...); the ring of
+// shared-memory stages runs on across tiles, and two accumulators in tensor memory take turns, so the
+// read-out and the stores of one tile overlap the products of the next.
 template <int BN, int STAGES, typename TC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -127,15 +137,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     TcSmem<BN, STAGES>& sm =
         *reinterpret_cast<TcSmem<BN, STAGES>*>(((uintptr_t)tc_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
     constexpr uint32_t STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16);
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     bool ok = true;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-        mbar_init(&sm.accum, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], TC_EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -148,60 +159,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
 
+    // consecutive tiles share a column block of W and differ in their rows of A, so the blocks that
+    // run at the same time read few distinct tiles of either operand
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES) ok = mbar_wait(&sm.empty[s], ((kb / STAGES) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-                tma_load_2d(sm.a[s], &map_a, kb * TC_BK, m0, &sm.full[s]);
-                tma_load_2d(sm.b[s], &map_w, kb * TC_BK, n0, &sm.full[s]);
-                issued = kb + 1;
+            long long it = 0, issued = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    ok = mbar_wait(&sm.empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1));   // passes at once the first time round
+                    if (!ok) break;
+                    mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+                    tma_load_2d(sm.a[s], &map_a, kb * TC_BK, m0, &sm.full[s]);
+                    tma_load_2d(sm.b[s], &map_w, kb * TC_BK, n0, &sm.full[s]);
+                    issued = it + 1;
+                }
             }
             if (!ok) {
                 atomicExch(status, 1);
                 // let the copies already under way land before the block goes away
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-                    mbar_wait(&sm.full[kb % STAGES], (kb / STAGES) & 1);
+                for (long long j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j)
+                    mbar_wait(&sm.full[j % STAGES], (uint32_t)((j / STAGES) & 1));
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(&sm.full[s], (kb / STAGES) & 1);
+            long long it = 0;
+            int local = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                ok = mbar_wait(&sm.acc_empty[buf], (uint32_t)(((local >> 1) & 1) ^ 1));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    ok = mbar_wait(&sm.full[s], (uint32_t)((it / STAGES) & 1));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k) {
-                    // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
-                    umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                              (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
+                        umma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&sm.empty[s]);            // the stage is free once these have read it
                 }
-                umma_commit(&sm.empty[s]);            // the stage is free once these have read it
+                if (ok) umma_commit(&sm.acc_full[buf]);   // the accumulator is complete
             }
-            if (ok) umma_commit(&sm.accum);           // the accumulator is complete
-            else atomicExch(status, 2);
+            if (!ok) atomicExch(status, 2);
         }
     } else {
-        // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+        // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31; two warps share each
+        // quarter of the rows and take half of the columns each, so that every scheduler of the SM
+        // has two epilogue warps to switch between
         const int quad = warp & 3;
-        ok = mbar_wait(&sm.accum, 0);
-        if (!ok) {
-            if (lane == 0) atomicExch(status, 3);
-        } else {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int half = (warp - 2) / 4;
+        constexpr int COLS = BN / (TC_EPI_WARPS / 4);
+        const bool vec_ok = ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) &&
+                            (!residual || ((ldr % 4 == 0) && (((uintptr_t)residual) % 16 == 0)));
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
             const int row = m0 + quad * 32 + lane;
-            const bool vec_ok = ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) &&
-                                (!residual || ((ldr % 4 == 0) && (((uintptr_t)residual) % 16 == 0)));
+            ok = mbar_wait(&sm.acc_full[buf], (uint32_t)((local >> 1) & 1));
+            if (!ok) {
+                if (lane == 0) atomicExch(status, 3);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = half * COLS; c0 < (half + 1) * COLS; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+                if (c0 + 32 >= (half + 1) * COLS) {
+                    // this warp has read all it needs of the accumulator: the tensor cores may have it back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+                }
                 const int nb = n0 + c0;
                 if (row >= M || nb >= N) continue;
                 float v[32];
@@ -210,7 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int n = nb + i;
                     float x = __uint_as_float(r[i]);
                     if (bias && n < N) x += bias[n];
-                    v[i] = apply_act(x, act);
+                    v[i] = sizeof(TC) == 2 ? apply_act_bf16(x, act) : apply_act(x, act);
                 }
                 TC* crow = C + (long long)row * ldc + nb;
                 const float* rrow = residual ? residual + (long long)row * ldr + nb : nullptr;
@@ -307,7 +346,12 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
             return MU_ERR_LAUNCH;
         raised = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+        return MU_ERR_LAUNCH;
+    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     kernel<<<grid, TC_THREADS, smem, s>>>(map_a, map_w, bias, residual, C, M, N, K, ldc, ldr, act, status);
     return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
 }
@@ -327,15 +371,33 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
     if (lda < K || ldw < K || ldc < N || (residual && ldr < N)) return MU_ERR_BAD_ARGUMENT;
     if ((M + mu::TC_BM - 1) / mu::TC_BM > 65535) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    // narrow tiles when wide ones would leave most of the 148 SMs without a tile
-    const long long tiles128 = (long long)((N + 127) / 128) * ((M + 127) / 128);
-    const bool narrow = N <= 64 || tiles128 < 148;
+    // Tile width: wider tiles do more products per byte loaded, but the tiles must also fill whole
+    // rounds of the SMs; take the width with the best (fill of the last round) x (worth of the width).
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long long m_tiles = (M + mu::TC_BM - 1) / mu::TC_BM;
+    int best_bn = 64;
+    double best = -1.0;
+    const int widths[3] = {64, 128, 256};
+    const double worth[3] = {0.6, 0.85, 1.0};
+    for (int i = 0; i < 3; ++i) {
+        if (widths[i] > 64 && N <= widths[i] / 2) continue;
+        const long long tiles = m_tiles * ((N + widths[i] - 1) / widths[i]);
+        const long long rounds = (tiles + sms - 1) / sms;
+        const double score = (double)tiles / (double)(rounds * sms) * worth[i];
+        if (score > best) { best = score; best_bn = widths[i]; }
+    }
 #define MU_TC(BN, ST)                                                                                           \
     (out_bf16 ? mu::launch_tc<BN, ST, __nv_bfloat16>(A, W, bias, residual, (__nv_bfloat16*)C, M, N, K, lda, ldw, \
                                                      ldc, ldr, act, status, s)                                  \
               : mu::launch_tc<BN, ST, float>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc, ldr, act,  \
                                              status, s))
-    if (narrow) return MU_TC(64, 4);
-    return MU_TC(128, 3);
+    if (const char* forced = getenv("MU_B200_TC_TILE")) {       // for measurements: 64, 128 or 256
+        const int f = atoi(forced);
+        if (f == 64 || f == 128 || f == 256) best_bn = f;
+    }
+    if (best_bn == 64) return MU_TC(64, 6);
+    if (best_bn == 128) return MU_TC(128, 5);
+    return MU_TC(256, 4);
 #undef MU_TC
 }

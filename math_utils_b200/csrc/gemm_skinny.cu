@@ -108,7 +108,35 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     auto load_weights = [&](int kb) { load_into(kb, wa, wb); };
     pdl_trigger();
     load_weights(kb0);
-    pdl_wait();                                            // activations, bias and residual from here on
+    // bias and norm parameters are weights too: they set off before the wait as well
+    __shared__ float bias_s[ROWS];
+    if (threadIdx.x < ROWS) {
+        const int n = blockIdx.x * ROWS + threadIdx.x;
+        bias_s[threadIdx.x] = (bias && n < N) ? bias[n] : 0.0f;
+    }
+    float* gamma_s = reinterpret_cast<float*>(skinny_dyn + (size_t)MP * act_ld * sizeof(__nv_bfloat16));
+    float* beta_s = gamma_s + K;
+    if (LN) {
+        for (int k = threadIdx.x * 4; k < K; k += SK_WARPS * 32 * 4) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(gamma_s + k)),
+                         "l"(norm.gamma + k));
+            if (norm.beta)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(beta_s + k)),
+                             "l"(norm.beta + k));
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    pdl_wait();                                            // activations and residual from here on
+    // the residual of this thread's first two outputs, asked for now and used in the epilogue
+    float res_pre[2] = {0.0f, 0.0f};
+    if (residual && rank == 0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = threadIdx.x + i * SK_WARPS * 32;
+            const int m = idx / ROWS, n = blockIdx.x * ROWS + idx % ROWS;
+            if (idx < ROWS * M && n < N) res_pre[i] = residual[(long long)m * ldr + n];
+        }
+    }
 
     if (LN) {
         // One warp per row.  The row is read once, as float4, into registers (all loads of a lane
@@ -116,6 +144,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         // that are read three times with the same arithmetic.
         constexpr int LNV = 16;                               // float4 per lane kept in registers
         const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                      // gamma and beta are in shared memory
         const int n4 = K / 4;
         for (int m = w; m < MP; m += SK_WARPS) {
             __nv_bfloat16* dst = act_smem + (long long)m * act_ld;
@@ -145,8 +175,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                     }
                 }
                 const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
-                const float4* g4 = reinterpret_cast<const float4*>(norm.gamma);
-                const float4* b4 = reinterpret_cast<const float4*>(norm.beta);
+                const float4* g4 = reinterpret_cast<const float4*>(gamma_s);
+                const float4* b4 = reinterpret_cast<const float4*>(beta_s);
 #pragma unroll
                 for (int i = 0; i < LNV; ++i) {
                     const int idx = ln + 32 * i;
@@ -174,7 +204,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                 const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
 #pragma unroll 8
                 for (int k = ln; k < K; k += 32)
-                    dst[k] = __float2bfloat16_rn((src[k] - mean) * inv * norm.gamma[k] + (norm.beta ? norm.beta[k] : 0.0f));
+                    dst[k] = __float2bfloat16_rn((src[k] - mean) * inv * gamma_s[k] + (norm.beta ? beta_s[k] : 0.0f));
             }
         }
         __syncthreads();
@@ -259,9 +289,12 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
             for (int c = 0; c < CK - 1; ++c) v += peer[c][r][m];
         }
-        if (bias) v += bias[n];
+        v += bias_s[r];
         v = sizeof(TC) == 2 ? apply_act_bf16(v, act) : apply_act(v, act);
-        if (residual) v += residual[(long long)m * ldr + n];
+        if (residual) {
+            const int turn = idx / (SK_WARPS * 32);
+            v += turn == 0 ? res_pre[0] : turn == 1 ? res_pre[1] : residual[(long long)m * ldr + n];
+        }
         C[(long long)m * ldc + n] = from_float<TC>(v);
     }
 }
@@ -273,7 +306,7 @@ static int launch_skinny_as(const __nv_bfloat16* A, const __nv_bfloat16* W, cons
     auto kernel = gemm_skinny_kernel<MT, WN, WK, CK, TC, LN>;
     size_t dyn = 0;
     if (LN) {
-        dyn = (size_t)8 * MT * (K + 8) * sizeof(__nv_bfloat16);
+        dyn = (size_t)8 * MT * (K + 8) * sizeof(__nv_bfloat16) + (size_t)2 * K * sizeof(float);   // rows, gamma, beta
         if (dyn > 160 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
         if (dyn > 24 * 1024) {
             // more than the default limit allows next to the static part; asked for once per variant

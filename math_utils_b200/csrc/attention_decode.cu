@@ -24,6 +24,7 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <cstdlib>
 
 namespace mu {
 
@@ -318,7 +319,11 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
     long long room = (148ll * 16 * 2) / items;
     if (room < 1) room = 1;
     const int want = n_splits < room ? n_splits : (int)room;
-    const int nw = want >= 16 ? 16 : want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
+    int nw = want >= 16 ? 16 : want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
+    if (const char* cap = getenv("MU_B200_ATT_WARPS")) {       // for measurements: at most this many warps per block
+        const int c = atoi(cap);
+        while (nw > 1 && nw > c) nw /= 2;
+    }
     int rc = MU_OK;
 #define MU_AD(TE, DP, NW)                                                                               \
     rc = mu::launch_pdl(mu::attention_decode_kernel<TE, DP, NW>, grid, dim3(NW * 32), 0, s, 1,          \

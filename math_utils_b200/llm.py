@@ -40,6 +40,7 @@ class LLM:
         self.model: Optional[DecoderModel] = None
         self.current = ""
         self._cache = None
+        self._batch_cache = None
         self._slot = None
         self._turns = 0
         if model_dir is not None:
@@ -57,6 +58,7 @@ class LLM:
 
     def unload(self) -> None:
         self.model, self._cache, self._slot, self.current, self._turns = None, None, None, "", 0
+        self._batch_cache = None
 
     @property
     def loaded(self) -> bool:
@@ -129,10 +131,22 @@ class LLM:
         """Independent requests, run as batches of unequal prompts; returns the
         produced tokens of each, in order."""
         self._need_model()
-        return _generate(self.model, prompts,
-                         self.options.max_tokens if max_tokens is None else max_tokens,
-                         self._params(temperature, top_k, seed), stop_ids=stop_ids, context=self.context,
-                         max_batch=max_batch or self.options.max_batch)
+        max_tokens = self.options.max_tokens if max_tokens is None else max_tokens
+        max_batch = max_batch or self.options.max_batch
+        # One cache serves call after call (and with it the recorded graphs of its batch sizes); a
+        # call that needs more room than any before gets a larger one.
+        from .cache import PAGE_TOKENS
+        from .engine.generate import most_positions, round_up
+        need = sorted((round_up(max(most_positions(len(p), max_tokens, self.context), 1), PAGE_TOKENS)
+                       for p in prompts), reverse=True)
+        tokens = max(sum(need[:max_batch]), PAGE_TOKENS)
+        held = self._batch_cache
+        if held is None or held.n_pages * held.page_tokens < tokens or held.n_slots < min(max_batch, len(prompts)):
+            self._batch_cache = None
+            self.model.__dict__.pop("_decode_sessions", None)
+            held = self._batch_cache = self.model.new_cache(max_tokens=tokens, n_slots=max_batch)
+        return _generate(self.model, prompts, max_tokens, self._params(temperature, top_k, seed),
+                         stop_ids=stop_ids, context=self.context, max_batch=min(max_batch, held.n_slots), cache=held)
 
     def _need_model(self) -> None:
         if self.model is None:

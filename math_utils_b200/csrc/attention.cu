@@ -1,8 +1,12 @@
 // Attention over the paged key/value cache, on CUDA cores, for any element type.
 //
 // Cache of one layer: pages of `page_tokens` positions,
-//     kv[page][0 = keys | 1 = values][kv_head][position in page][head_dim]
-// and a block table `block_table[s][i]` = page that holds positions
+//     keys    kv[page][0][kv_head][position in page][head_dim]
+//     values  kv[page][1][kv_head][head_dim][position in page]     (transposed)
+// Keys lie position-major, so a query's dot product with one key reads one contiguous row;
+// values lie dimension-major, so the weighted sum over positions reads contiguous runs of
+// positions for each output dimension, which is also the operand layout the tensor-core
+// kernels want for both products.  A block table `block_table[s][i]` = page that holds positions
 // [i * page_tokens, (i + 1) * page_tokens) of the s-th sequence of the step
 // (`tok_seq[t]` says which sequence token t belongs to, `tok_pos[t]` where).
 //
@@ -36,16 +40,17 @@ __global__ void kv_append_kernel(const TE* __restrict__ k, long long ldk, const 
     const int width = n_kv_heads * head_dim;
     const long long head_stride = (long long)page_tokens * head_dim;
     TE* kdst = kv + (page * 2 + 0) * n_kv_heads * head_stride + (long long)off * head_dim;
-    TE* vdst = kv + (page * 2 + 1) * n_kv_heads * head_stride + (long long)off * head_dim;
+    TE* vdst = kv + (page * 2 + 1) * n_kv_heads * head_stride + off;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const int h = i / head_dim, d = i % head_dim;
         kdst[h * head_stride + d] = k[(long long)t * ldk + i];
-        vdst[h * head_stride + d] = v[(long long)t * ldv + i];
+        vdst[h * head_stride + (long long)d * page_tokens] = v[(long long)t * ldv + i];
     }
 }
 
-// The same copy in 16-byte pieces, for rows and strides that allow it.
-template <typename TE>
+// The same copy in 16-byte pieces, for rows and strides that allow it.  WITH_V false: keys only
+// (the values of a prompt go through v_append_tiles_kernel).
+template <typename TE, bool WITH_V>
 __global__ void kv_append_vec_kernel(const TE* __restrict__ k, long long ldk, const TE* __restrict__ v,
                                      long long ldv, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_seq, const int* __restrict__ block_table,
@@ -59,14 +64,48 @@ __global__ void kv_append_vec_kernel(const TE* __restrict__ k, long long ldk, co
     const int pieces_per_head = head_dim / E, pieces = n_kv_heads * pieces_per_head;
     const long long head_stride = (long long)page_tokens * head_dim;
     TE* kdst = kv + (page * 2 + 0) * n_kv_heads * head_stride + (long long)off * head_dim;
-    TE* vdst = kv + (page * 2 + 1) * n_kv_heads * head_stride + (long long)off * head_dim;
+    TE* vdst = kv + (page * 2 + 1) * n_kv_heads * head_stride + off;
 #pragma unroll 2
     for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
         const int h = i / pieces_per_head, d = (i % pieces_per_head) * E;
         const uint4 kk = *reinterpret_cast<const uint4*>(k + (long long)t * ldk + h * head_dim + d);
-        const uint4 vv = *reinterpret_cast<const uint4*>(v + (long long)t * ldv + h * head_dim + d);
         *reinterpret_cast<uint4*>(kdst + h * head_stride + d) = kk;
-        *reinterpret_cast<uint4*>(vdst + h * head_stride + d) = vv;
+        if (WITH_V) {
+            // the value's elements go one by one to their dimension rows
+            const uint4 vv = *reinterpret_cast<const uint4*>(v + (long long)t * ldv + h * head_dim + d);
+            const TE* ve = reinterpret_cast<const TE*>(&vv);
+#pragma unroll
+            for (int e = 0; e < E; ++e) vdst[h * head_stride + (long long)(d + e) * page_tokens] = ve[e];
+        }
+    }
+}
+
+// Values of a whole tile of prompt tokens (up to 64 consecutive tokens of one sequence) for one kv
+// head: the tile is turned in shared memory so that each dimension row of the page is written as a
+// run of consecutive positions.  tiles: int32 [n][2] = (first flat token, count).
+template <typename TE>
+__global__ void v_append_tiles_kernel(const TE* __restrict__ v, long long ldv, const int* __restrict__ tok_pos,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                      int max_pages, int page_tokens, const int* __restrict__ tiles,
+                                      int n_kv_heads, int head_dim, TE* __restrict__ kv) {
+    extern __shared__ __align__(16) unsigned char vt_raw[];
+    TE* tile = reinterpret_cast<TE*>(vt_raw);                    // [64][head_dim + pad]
+    const int pitch = head_dim + (sizeof(TE) == 2 ? 2 : 1);     // an odd number of 32-bit words per row: no bank conflicts
+    const int flat0 = tiles[2 * blockIdx.x], n = tiles[2 * blockIdx.x + 1];
+    const int h = blockIdx.y;
+    for (int i = threadIdx.x; i < n * head_dim; i += blockDim.x) {
+        const int r = i / head_dim, d = i % head_dim;
+        tile[r * pitch + d] = v[(long long)(flat0 + r) * ldv + h * head_dim + d];
+    }
+    __syncthreads();
+    const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
+    const int pos0 = tok_pos[flat0];
+    const long long head_stride = (long long)page_tokens * head_dim;
+    for (int i = threadIdx.x; i < n * head_dim; i += blockDim.x) {
+        const int r = i % n, d = i / n;                           // consecutive threads, consecutive positions
+        const int pos = pos0 + r;
+        TE* dst = kv + ((long long)pages[pos / page_tokens] * 2 + 1) * n_kv_heads * head_stride + h * head_stride;
+        dst[(long long)d * page_tokens + pos % page_tokens] = tile[r * pitch + d];
     }
 }
 
@@ -94,6 +133,27 @@ __device__ __forceinline__ float dot_row(const float* qs, const __nv_bfloat16* k
         }
     }
     return s;
+}
+
+// 32 consecutive values of one dimension row of a value page, widened.
+__device__ __forceinline__ void load_run32(const float* p, float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 x = reinterpret_cast<const float4*>(p)[i];
+        v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
+    }
+}
+__device__ __forceinline__ void load_run32(const __nv_bfloat16* p, float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 raw = reinterpret_cast<const uint4*>(p)[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[8 * i + 2 * j] = f.x; v[8 * i + 2 * j + 1] = f.y;
+        }
+    }
 }
 
 constexpr int ATT_WARPS = 4;
@@ -135,33 +195,31 @@ attention_kernel(const TE* __restrict__ q, long long ldq, TE* __restrict__ out, 
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
 
-    for (int base = lo; base < hi; base += 32) {
+    // keys in runs of 32 that start on multiples of 32, so that a run never crosses a page
+    for (int base = lo & ~31; base < hi; base += 32) {
         const int j = base + lane;
-        const bool valid = j < hi;
-        long long row_off = 0;        // offset of this key's row inside its page's head block
+        const bool valid = j >= lo && j < hi;
+        const long long page_off = (long long)pages[base / page_tokens] * page_stride;
         float s = -INFINITY;
-        if (valid) {
-            const long long page = pages[j / page_tokens];
-            row_off = page * page_stride + (long long)(j % page_tokens) * head_dim;
-            s = dot_row(qs, kv + row_off + k_base, head_dim) * scale;
-        }
+        if (valid) s = dot_row(qs, kv + page_off + k_base + (long long)(j % page_tokens) * head_dim, head_dim) * scale;
         const float m_new = fmaxf(m, warp_max(s));
-        const float p = valid ? expf(s - m_new) : 0.0f;
-        const float corr = expf(m - m_new);           // 0 on the first chunk (m = -inf)
+        const float p = valid ? expf(s - m_new) : 0.0f;   // the run holds at least one visible key
+        const float corr = expf(m - m_new);               // 0 on the first run (m = -inf)
         l = l * corr + warp_sum(p);
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[i] *= corr;
         m = m_new;
-        const int n_here = min(32, hi - base);
-        for (int jj = 0; jj < n_here; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const long long off = __shfl_sync(0xffffffffu, row_off, jj);
-            const TE* vrow = kv + off + v_base;
+        const TE* vhead = kv + page_off + v_base + (base % page_tokens);     // [head_dim][page_tokens], at this run
 #pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                const int d = lane + 32 * i;
-                if (d < head_dim) acc[i] = fmaf(pj, to_float(vrow[d]), acc[i]);
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            float v[32];
+            if (d < head_dim) load_run32(vhead + (long long)d * page_tokens, v);
+            float a = acc[i] * corr;
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);       // 0 for keys outside [lo, hi)
+                if (d < head_dim) a = fmaf(pj, v[jj], a);
             }
+            acc[i] = a;
         }
     }
 
@@ -217,14 +275,18 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 
 static int check_paged(int page_tokens, int n_kv_heads, int head_dim, int max_pages) {
     if (page_tokens <= 0 || n_kv_heads <= 0 || max_pages <= 0) return MU_ERR_BAD_ARGUMENT;
+    if (page_tokens % 32 != 0) return MU_ERR_UNSUPPORTED_SIZE;       // values are read in aligned runs of 32 positions
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;
     return MU_OK;
 }
 
+// tiles (optional): int32 [n_tiles][2] = (first flat token, count <= 64) covering all tokens, each tile
+// within one sequence; with them the values are written a tile at a time, position runs together.
 MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long long ldv,
                            const int* tok_pos, const int* tok_seq,
                            const int* block_table, int max_pages, int page_tokens, int n_tokens,
-                           int n_kv_heads, int head_dim, void* kv, int is_bf16, void* stream) {
+                           int n_kv_heads, int head_dim, void* kv, int is_bf16, const int* tiles, int n_tiles,
+                           void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (int e = check_paged(page_tokens, n_kv_heads, head_dim, max_pages)) return e;
     if (!k || !v || !kv || !tok_pos || !tok_seq || !block_table) return MU_ERR_BAD_ARGUMENT;
@@ -233,15 +295,36 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
     const int e = is_bf16 ? 8 : 4;
     if (ldk % e == 0 && ldv % e == 0 && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) && !((uintptr_t)kv & 15)) {
         const int vthreads = n_kv_heads * head_dim / e >= 128 ? 128 : 64;
-        if (is_bf16)
-            mu::kv_append_vec_kernel<__nv_bfloat16><<<n_tokens, vthreads, 0, s>>>(
-                (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table,
-                max_pages, page_tokens, n_kv_heads, head_dim, (__nv_bfloat16*)kv);
-        else
-            mu::kv_append_vec_kernel<float><<<n_tokens, vthreads, 0, s>>>(
-                (const float*)k, ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages,
-                page_tokens, n_kv_heads, head_dim, (float*)kv);
+        const bool tiled = tiles != nullptr && n_tiles > 0 && n_kv_heads <= 65535;
+#define MU_APPEND(TE, WITH_V)                                                                          \
+    mu::kv_append_vec_kernel<TE, WITH_V><<<n_tokens, vthreads, 0, s>>>(                                 \
+        (const TE*)k, ldk, (const TE*)v, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens,   \
+        n_kv_heads, head_dim, (TE*)kv)
+        if (is_bf16) { if (tiled) MU_APPEND(__nv_bfloat16, false); else MU_APPEND(__nv_bfloat16, true); }
+        else { if (tiled) MU_APPEND(float, false); else MU_APPEND(float, true); }
+#undef MU_APPEND
         MU_CHECK_LAUNCH();
+        if (tiled) {
+            dim3 grid(n_tiles, n_kv_heads);
+            const size_t smem = (size_t)64 * (head_dim + 2) * (is_bf16 ? 2 : 4);
+            if (is_bf16)
+                mu::v_append_tiles_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(
+                    (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens, tiles,
+                    n_kv_heads, head_dim, (__nv_bfloat16*)kv);
+            else {
+                if (smem > 48 * 1024) {
+                    static bool raised = false;
+                    if (!raised && cudaFuncSetAttribute(mu::v_append_tiles_kernel<float>,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+                        return MU_ERR_LAUNCH;
+                    raised = true;
+                }
+                mu::v_append_tiles_kernel<float><<<grid, 256, smem, s>>>(
+                    (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens, tiles,
+                    n_kv_heads, head_dim, (float*)kv);
+            }
+            MU_CHECK_LAUNCH();
+        }
         return MU_OK;
     }
     if (is_bf16)

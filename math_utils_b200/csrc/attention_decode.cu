@@ -91,27 +91,8 @@ __device__ __forceinline__ void dot_head2(const float* qs, const __nv_bfloat16* 
     sa = a0 + a1; sb = b0 + b1;
 }
 
-__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
-__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
-    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
-}
-
-// Two neighbouring elements as they lie in memory, widened only when used.
-template <typename TE> struct RawPair;
-template <> struct RawPair<float> {
-    float2 v;
-    __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float2*>(p); }
-    __device__ __forceinline__ void zero() { v = make_float2(0.0f, 0.0f); }
-    __device__ __forceinline__ float2 get() const { return v; }
-};
-template <> struct RawPair<__nv_bfloat16> {
-    __nv_bfloat162 v;
-    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const __nv_bfloat162*>(p); }
-    __device__ __forceinline__ void zero() { v = __floats2bfloat162_rn(0.0f, 0.0f); }
-    __device__ __forceinline__ float2 get() const { return __bfloat1622float2(v); }
-};
-
-// DP: pairs of head dimensions per lane (lane owns dims 2*lane + 64*i, +1).  NW: warps per block.
+// DP: the head holds at most 64 * DP dimensions; a lane owns dims lane + 32 * i, i < 2 * DP.
+// NW: warps per block.
 template <typename TE, int DP, int NW>
 __global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restrict__ k_new, long long ldk,
@@ -119,6 +100,10 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
                         TE* kv, const int* __restrict__ block_table, int max_pages,
                         const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
                         int n_kv_heads, int head_dim, float scale, int window) {
+    constexpr int D1 = 2 * DP;                                        // dimensions per lane
+    constexpr int ES = (int)sizeof(TE);
+    constexpr int VCK = 256 / (D1 * ES) > 64 ? 64 : 256 / (D1 * ES);  // keys fetched at once: 64 registers' worth
+    constexpr int VQ = VCK * ES / 16;                                 // 16-byte pieces per dimension and fetch
     __shared__ float q_smem[DP * 64];
     __shared__ float part_o[NW][DP * 64];
     __shared__ float part_m[NW], part_l[NW];
@@ -134,16 +119,15 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = first / AD_PAGE, last_page = pos / AD_PAGE;
     const long long head_stride = (long long)AD_PAGE * head_dim;
-    constexpr int VC = 64 / (DP * (int)(sizeof(TE) / 2));      // keys whose values fit 64 registers
 
     float m_run = -INFINITY, l_run = 0.0f;
-    float2 acc[DP];
+    float acc[D1];
 #pragma unroll
-    for (int i = 0; i < DP; ++i) acc[i] = make_float2(0.0f, 0.0f);
+    for (int i = 0; i < D1; ++i) acc[i] = 0.0f;
 
     // What a page needs: where it lies, which of its keys are visible, whether the new key is in it.
     struct PageView {
-        TE* kpage; TE* vpage;
+        TE* kpage; TE* vpage;                                  // keys [64][head_dim]; values [head_dim][64]
         int lo, hi, hi_cache;
         bool has_new;
     };
@@ -159,28 +143,26 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
         pv.hi_cache = pv.has_new ? pv.hi - 1 : pv.hi;          // keys to be read from the cache
         return pv;
     };
-    RawPair<TE> vreg[VC][DP];
+    // values of VCK positions from j0 on, for each of the lane's dimensions, as they lie in memory
+    uint4 vraw[D1][VQ];
     auto fetch_values = [&](const PageView& pv, int j0) {
 #pragma unroll
-        for (int jj = 0; jj < VC; ++jj) {
-            const int j = j0 + jj;
-            const TE* vrow = pv.vpage + (long long)j * head_dim;
+        for (int i = 0; i < D1; ++i) {
+            const int d = lane + 32 * i;
+            const uint4* src = reinterpret_cast<const uint4*>(pv.vpage + (long long)min(d, head_dim - 1) * AD_PAGE + j0);
 #pragma unroll
-            for (int i = 0; i < DP; ++i) {
-                const int d = 2 * lane + 64 * i;
-                if (j >= pv.lo && j < pv.hi_cache && d < head_dim) vreg[jj][i].load(vrow + d);
-                else vreg[jj][i].zero();
-            }
+            for (int c = 0; c < VQ; ++c) vraw[i][c] = src[c];
         }
     };
 
     // The warp's first page: its values are asked for before anything else (rows written by earlier
     // steps, untouched by the kernels ahead of this one), so that they travel during the wait.
+    // Positions of the page that hold nothing yet are read too; their weights are zero.
     const int my_first = first_page + warp;
     PageView pv = {};
     if (my_first <= last_page) {
         pv = view_of(my_first);
-        fetch_values(pv, (pv.lo / VC) * VC);
+        fetch_values(pv, (pv.lo / VCK) * VCK);
     }
     pdl_wait();                                                 // this step's query, key and value from here on
     for (int d = threadIdx.x; d < head_dim; d += NW * 32) q_smem[d] = to_float(q[(long long)t * ldq + h * head_dim + d]);
@@ -189,20 +171,22 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     for (int page_idx = my_first; page_idx <= last_page; page_idx += NW) {
         if (page_idx != my_first) {
             pv = view_of(page_idx);
-            fetch_values(pv, (pv.lo / VC) * VC);
+            fetch_values(pv, (pv.lo / VCK) * VCK);
         }
         TE* kpage = pv.kpage;
         TE* vpage = pv.vpage;
         const int lo = pv.lo, hi = pv.hi, hi_cache = pv.hi_cache;
         const bool has_new = pv.has_new;
-        const int v_first = (lo / VC) * VC;                     // chunk that holds the first visible key
+        const int v_first = (lo / VCK) * VCK;                   // fetch that holds the first visible key
         const TE* kn = has_new ? k_new + (long long)t * ldk + kvh * head_dim : nullptr;
         const TE* vn = has_new ? v_new + (long long)t * ldv + kvh * head_dim : nullptr;
         if (has_new && h % group == 0) {
             // append: this step's key and value of the kv head go to their place in the page
             TE* kd = kpage + (long long)(hi - 1) * head_dim;
-            TE* vd = vpage + (long long)(hi - 1) * head_dim;
-            for (int d = lane; d < head_dim; d += 32) { kd[d] = kn[d]; vd[d] = vn[d]; }
+            for (int d = lane; d < head_dim; d += 32) {
+                kd[d] = kn[d];
+                vpage[(long long)d * AD_PAGE + hi - 1] = vn[d];
+            }
         }
 
         // scores: lane -> keys lane and lane + 32 of the page
@@ -221,46 +205,42 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
             if (in1 || new1) s1 = d1 * scale;
         }
         const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));        // finite: the page has a visible key
-        const float p0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - m_new);
-        const float p1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - m_new);
+        const float p_new = (has_new && (hi - 1) % 32 == lane) ? 1.0f : 0.0f;     // marks the lane that scored the new key
+        float p0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - m_new);
+        float p1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - m_new);
         const float corr = expf(m_run - m_new);                          // 0 for the warp's first page
         l_run = l_run * corr + warp_sum(p0 + p1);
         m_run = m_new;
 #pragma unroll
-        for (int i = 0; i < DP; ++i) { acc[i].x *= corr; acc[i].y *= corr; }
+        for (int i = 0; i < D1; ++i) acc[i] *= corr;
+        // the new key's weight is taken out of the run over the cache and applied to v_new below
+        const float w_new = has_new ? __shfl_sync(0xffffffffu, (hi - 1 < 32) ? p0 : p1, (hi - 1) & 31) : 0.0f;
+        if (p_new != 0.0f) { if (hi - 1 < 32) p0 = 0.0f; else p1 = 0.0f; }
 
-        for (int c0 = v_first; c0 < hi_cache; c0 += VC) {
+        for (int c0 = v_first; c0 < hi_cache; c0 += VCK) {
             if (c0 != v_first) fetch_values(pv, c0);
 #pragma unroll
-            for (int jj = 0; jj < VC; ++jj) {
-                const int j = c0 + jj;                           // keys outside [lo, hi_cache) carry p = 0 or v = 0
+            for (int jj = 0; jj < VCK; ++jj) {
+                const int j = c0 + jj;                           // positions outside [lo, hi_cache) carry p = 0
                 const float pj = __shfl_sync(0xffffffffu, (j < 32) ? p0 : p1, j & 31);
 #pragma unroll
-                for (int i = 0; i < DP; ++i) {
-                    const float2 v = vreg[jj][i].get();
-                    acc[i].x = fmaf(pj, v.x, acc[i].x);
-                    acc[i].y = fmaf(pj, v.y, acc[i].y);
-                }
+                for (int i = 0; i < D1; ++i)
+                    acc[i] = fmaf(pj, to_float(reinterpret_cast<const TE*>(&vraw[i][0])[jj]), acc[i]);
             }
         }
         if (has_new) {
-            const int j = hi - 1;
-            const float pj = (j < 32) ? __shfl_sync(0xffffffffu, p0, j) : __shfl_sync(0xffffffffu, p1, j - 32);
 #pragma unroll
-            for (int i = 0; i < DP; ++i) {
-                const int d = 2 * lane + 64 * i;
-                if (d < head_dim) {
-                    const float2 v = load2(vn + d);
-                    acc[i].x = fmaf(pj, v.x, acc[i].x);
-                    acc[i].y = fmaf(pj, v.y, acc[i].y);
-                }
+            for (int i = 0; i < D1; ++i) {
+                const int d = lane + 32 * i;
+                if (d < head_dim) acc[i] = fmaf(w_new, to_float(vn[d]), acc[i]);
             }
         }
     }
+
 #pragma unroll
-    for (int i = 0; i < DP; ++i) {
-        const int d = 2 * lane + 64 * i;
-        if (d < head_dim) { part_o[warp][d] = acc[i].x; part_o[warp][d + 1] = acc[i].y; }
+    for (int i = 0; i < D1; ++i) {
+        const int d = lane + 32 * i;
+        if (d < head_dim) part_o[warp][d] = acc[i];
     }
     if (lane == 0) { part_m[warp] = m_run; part_l[warp] = l_run; }
     __syncthreads();

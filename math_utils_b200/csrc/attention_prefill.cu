@@ -6,8 +6,8 @@
 // memory (two pages in flight).  Per page: S = Q K^T with mma.sync.m16n8k16
 // (K fragments by ldmatrix), scale, causal / window mask, online softmax in
 // float32 registers (running max and sum per query row), P rounded to bfloat16
-// and fed straight back as the A operand of O += P V (V fragments by
-// ldmatrix.trans).  Queries sit at absolute positions (the cache may already
+// and fed straight back as the A operand of O += P V (V fragments by ldmatrix
+// too: a page keeps its values dimension-major).  Queries sit at absolute positions (the cache may already
 // hold earlier tokens of the sequence), so a prompt fed in parts gives the same
 // result as a prompt fed whole.  The step's own keys and values must have been
 // appended before (mu_kv_append).
@@ -49,7 +49,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// KD = head_dim / 16.  Shared memory: Q [64][P], then two stages of K [64][P] and V [64][P], P = head_dim + 8.
+// KD = head_dim / 16.  Shared memory: Q [64][P], two stages of K [64][P] (P = head_dim + 8) and two
+// stages of V [head_dim][72]: values lie dimension-major in the cache, which is the layout the second
+// product wants for its right operand, so both products take their fragments by plain ldmatrix.
 template <int KD>
 __global__ void __launch_bounds__(FP_THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __nv_bfloat16* __restrict__ out,
@@ -61,7 +63,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
     extern __shared__ __align__(16) unsigned char fp_smem[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(fp_smem);
     __nv_bfloat16* k_s = q_s + FP_QT * P;          // [2][64][P]
-    __nv_bfloat16* v_s = k_s + 2 * FP_KT * P;      // [2][64][P]
+    constexpr int VP = FP_KT + 8;                  // pitch of a value row (one dimension, 64 positions)
+    __nv_bfloat16* v_s = k_s + 2 * FP_KT * P;      // [2][DH][VP]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -78,11 +81,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
         const __nv_bfloat16* kp = kv + ((long long)pages[page_idx] * 2 * n_kv_heads + kvh) * head_stride;
         const __nv_bfloat16* vp = kp + (long long)n_kv_heads * head_stride;
         __nv_bfloat16* ks = k_s + stage * FP_KT * P;
-        __nv_bfloat16* vs = v_s + stage * FP_KT * P;
+        __nv_bfloat16* vs = v_s + stage * DH * VP;
         for (int c = tid; c < FP_KT * CHUNKS; c += FP_THREADS) {
             const int r = c / CHUNKS, o = (c % CHUNKS) * 8;
             cp_async16(ks + r * P + o, kp + r * DH + o);
-            cp_async16(vs + r * P + o, vp + r * DH + o);
+        }
+        for (int c = tid; c < DH * (FP_KT / 8); c += FP_THREADS) {
+            const int r = c / (FP_KT / 8), o = (c % (FP_KT / 8)) * 8;
+            cp_async16(vs + r * VP + o, vp + r * FP_KT + o);
         }
     };
 
@@ -116,7 +122,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
         if (page_idx + 1 <= last_page) load_page(page_idx + 1, stage ^ 1);
         cp_async_commit();
         const __nv_bfloat16* ks = k_s + stage * FP_KT * P;
-        const __nv_bfloat16* vs = v_s + stage * FP_KT * P;
+        const __nv_bfloat16* vs = v_s + stage * DH * VP;
 
         // S = Q K^T for 64 keys: 8 tiles of 8 keys
         float s_acc[8][4];
@@ -188,7 +194,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
 #pragma unroll
             for (int j = 0; j < 2 * KD; j += 2) {
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, vs + (16 * kk + (lane & 7) + 8 * ((lane >> 3) & 1)) * P + 8 * (j + (lane >> 4)));
+                ldmatrix_x4(b, vs + (8 * j + (lane & 7) + 8 * (lane >> 4)) * VP + 16 * kk + ((lane >> 3) & 1) * 8);
                 mma_16816(o_acc[j], pf[kk], b[0], b[1]);
                 mma_16816(o_acc[j + 1], pf[kk], b[2], b[3]);
             }
@@ -222,7 +228,7 @@ static int launch_prefill(const void* q, long long ldq, void* out, long long ldo
                           const int* tiles, int n_tiles, int n_heads, int n_kv_heads, float scale, int window,
                           cudaStream_t s) {
     constexpr int P = 16 * KD + 8;
-    const size_t smem = (size_t)(FP_QT + 4 * FP_KT) * P * sizeof(__nv_bfloat16);
+    const size_t smem = ((size_t)(FP_QT + 2 * FP_KT) * P + (size_t)2 * 16 * KD * (FP_KT + 8)) * sizeof(__nv_bfloat16);
     auto kernel = attention_prefill_kernel<KD>;
     if (smem > 48 * 1024) {
         static bool raised = false;

@@ -340,7 +340,7 @@ decode_program_kernel(const ProgramOp* __restrict__ ops, int n_ops, BarrierState
                     att_q[d] = __bfloat162float(op.q[(long long)tk * op.ldq + h * op.head_dim + d]);
                 __syncthreads();
                 float m_run = -INFINITY, l_run = 0.0f;
-                float2 acc[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // dims lane + 32 i
                 for (int page_idx = first_page + warp; page_idx <= last_page; page_idx += DP_WARPS) {
                     __nv_bfloat16* kpage = op.kv + ((long long)pages[page_idx] * 2 * op.n_kv_heads + kvh) * head_stride;
                     __nv_bfloat16* vpage = kpage + (long long)op.n_kv_heads * head_stride;
@@ -350,27 +350,12 @@ decode_program_kernel(const ProgramOp* __restrict__ ops, int n_ops, BarrierState
                     const int hi_cache = has_new ? hi - 1 : hi;
                     const __nv_bfloat16* kn = has_new ? op.k_new + (long long)tk * op.ldk + kvh * op.head_dim : nullptr;
                     const __nv_bfloat16* vn = has_new ? op.v_new + (long long)tk * op.ldv + kvh * op.head_dim : nullptr;
-                    // values of the first 32 keys on their way while the scores are computed
-                    __nv_bfloat162 vreg[32][2];
-                    auto fetch = [&](int j0) {
-#pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            const int j = j0 + jj;
-#pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                const int d = 2 * lane + 64 * i;
-                                if (j >= lo && j < hi_cache && d < op.head_dim)
-                                    vreg[jj][i] = *reinterpret_cast<const __nv_bfloat162*>(vpage + (long long)j * op.head_dim + d);
-                                else vreg[jj][i] = __floats2bfloat162_rn(0.0f, 0.0f);
-                            }
-                        }
-                    };
-                    const int v_first = (lo / 32) * 32;
-                    fetch(v_first);
                     if (has_new && h % group == 0) {
                         __nv_bfloat16* kd = kpage + (long long)(hi - 1) * op.head_dim;
-                        __nv_bfloat16* vd = vpage + (long long)(hi - 1) * op.head_dim;
-                        for (int d = lane; d < op.head_dim; d += 32) { kd[d] = kn[d]; vd[d] = vn[d]; }
+                        for (int d = lane; d < op.head_dim; d += 32) {
+                            kd[d] = kn[d];
+                            vpage[(long long)d * DP_PAGE + hi - 1] = vn[d];      // values lie dimension-major
+                        }
                     }
                     float s0 = -INFINITY, s1 = -INFINITY;
                     {
@@ -403,39 +388,44 @@ decode_program_kernel(const ProgramOp* __restrict__ ops, int n_ops, BarrierState
                     const float corr = expf(m_run - m_new);
                     l_run = l_run * corr + warp_sum(p0 + p1);
                     m_run = m_new;
-                    acc[0].x *= corr; acc[0].y *= corr; acc[1].x *= corr; acc[1].y *= corr;
-                    for (int c0 = v_first; c0 < hi_cache; c0 += 32) {
-                        if (c0 != v_first) fetch(c0);
 #pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            const int j = c0 + jj;
-                            const float pj = __shfl_sync(0xffffffffu, (j < 32) ? p0 : p1, j & 31);
+                    for (int i = 0; i < 4; ++i) acc[i] *= corr;
+                    // the new key's weight goes with v_new; in the runs over the cache it counts as zero
+                    const float w_new = has_new ? __shfl_sync(0xffffffffu, (hi - 1 < 32) ? p0 : p1, (hi - 1) & 31) : 0.0f;
+                    float r0 = p0, r1 = p1;
+                    if (has_new && ((hi - 1) & 31) == lane) { if (hi - 1 < 32) r0 = 0.0f; else r1 = 0.0f; }
 #pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                const float2 v = __bfloat1622float2(vreg[jj][i]);
-                                acc[i].x = fmaf(pj, v.x, acc[i].x);
-                                acc[i].y = fmaf(pj, v.y, acc[i].y);
-                            }
+                    for (int half = 0; half < 2; ++half) {
+                        if (32 * half >= hi_cache || 32 * half + 32 <= lo) continue;      // no visible key in this run
+                        const float pr = half ? r1 : r0;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (32 * i >= op.head_dim) continue;                          // uniform over the warp
+                            const int d = min(lane + 32 * i, op.head_dim - 1);          // idle lanes read a row that exists
+                            const uint4* src = reinterpret_cast<const uint4*>(vpage + (long long)d * DP_PAGE + 32 * half);
+                            uint4 raw[4];
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) raw[c] = src[c];
+                            const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(raw);
+                            float a = acc[i];
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj)
+                                a = fmaf(__shfl_sync(0xffffffffu, pr, jj), __bfloat162float(v[jj]), a);
+                            acc[i] = a;
                         }
                     }
                     if (has_new) {
-                        const int j = hi - 1;
-                        const float pj = (j < 32) ? __shfl_sync(0xffffffffu, p0, j) : __shfl_sync(0xffffffffu, p1, j - 32);
 #pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            const int d = 2 * lane + 64 * i;
-                            if (d < op.head_dim) {
-                                const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vn + d));
-                                acc[i].x = fmaf(pj, v.x, acc[i].x);
-                                acc[i].y = fmaf(pj, v.y, acc[i].y);
-                            }
+                        for (int i = 0; i < 4; ++i) {
+                            const int d = lane + 32 * i;
+                            if (d < op.head_dim) acc[i] = fmaf(w_new, __bfloat162float(vn[d]), acc[i]);
                         }
                     }
                 }
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int d = 2 * lane + 64 * i;
-                    if (d < op.head_dim) { att_o[warp][d] = acc[i].x; att_o[warp][d + 1] = acc[i].y; }
+                for (int i = 0; i < 4; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < op.head_dim) att_o[warp][d] = acc[i];
                 }
                 if (lane == 0) { att_m[warp] = m_run; att_l[warp] = l_run; }
                 __syncthreads();

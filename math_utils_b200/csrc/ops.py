@@ -46,7 +46,7 @@ _SIGNATURES = {
     "mu_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                    _c_int, _c_int, _c_p, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
-                     _c_int, _c_p, _c_int, _c_p],
+                     _c_int, _c_p, _c_int, _c_p, _c_int, _c_p],
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
                      _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p],
     "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
@@ -304,9 +304,12 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
 
 # ------------------------------------------------------------------- attention
 def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: torch.Tensor,
-              page_tokens: int, n_kv_heads: int, head_dim: int, kv_pages: torch.Tensor) -> None:
+              page_tokens: int, n_kv_heads: int, head_dim: int, kv_pages: torch.Tensor,
+              tiles: Optional[torch.Tensor] = None) -> None:
     """Copies keys and values of this step's tokens ([T, n_kv_heads * head_dim]
-    views, unit inner stride) into their pages."""
+    views, unit inner stride) into their pages (values transposed: dimension-major
+    within a page).  ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of
+    runs of tokens of one sequence) lets prompt values be written a tile at a time."""
     _not_while_recording("kv_append")
     _need_cuda(k, v, tok_pos, tok_seq, block_table, kv_pages)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
@@ -318,7 +321,8 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: t
     _check(library().mu_kv_append(
         _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(tok_pos), _ptr(tok_seq),
         _ptr(block_table), block_table.shape[1], page_tokens, k.shape[0], n_kv_heads, head_dim,
-        _ptr(kv_pages), _is_bf16(kv_pages), _stream()), f"kv_append(head_dim={head_dim})")
+        _ptr(kv_pages), _is_bf16(kv_pages), _ptr(tiles), tiles.shape[0] if tiles is not None else 0, _stream()),
+        f"kv_append(head_dim={head_dim})", launches=2 if tiles is not None else 1)
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor,

@@ -73,7 +73,7 @@ class CausalSelfAttention(Mixer):
         else:
             if owns_cache:
                 ops.kv_append(k, v, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens,
-                              self.n_kv_heads, self.head_dim, cache.pages)
+                              self.n_kv_heads, self.head_dim, cache.pages, tiles=ctx.q_tiles)
             if ctx.q_tiles is not None and ops.prefill_ok(q, self.head_dim, cache.page_tokens):
                 ops.attention_prefill(q, attn, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq,
                                       ctx.q_tiles, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,

@@ -93,19 +93,25 @@ __global__ void v_append_tiles_kernel(const TE* __restrict__ v, long long ldv, c
     const int pitch = head_dim + (sizeof(TE) == 2 ? 2 : 1);     // an odd number of 32-bit words per row: no bank conflicts
     const int flat0 = tiles[2 * blockIdx.x], n = tiles[2 * blockIdx.x + 1];
     const int h = blockIdx.y;
-    for (int i = threadIdx.x; i < n * head_dim; i += blockDim.x) {
-        const int r = i / head_dim, d = i % head_dim;
-        tile[r * pitch + d] = v[(long long)(flat0 + r) * ldv + h * head_dim + d];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    // rows in: a warp per token, lanes along the head (coalesced reads)
+    for (int r = warp; r < n; r += n_warps) {
+        const TE* src = v + (long long)(flat0 + r) * ldv + h * head_dim;
+#pragma unroll 4
+        for (int d = lane; d < head_dim; d += 32) tile[r * pitch + d] = src[d];
     }
     __syncthreads();
     const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
     const int pos0 = tok_pos[flat0];
     const long long head_stride = (long long)page_tokens * head_dim;
-    for (int i = threadIdx.x; i < n * head_dim; i += blockDim.x) {
-        const int r = i % n, d = i / n;                           // consecutive threads, consecutive positions
-        const int pos = pos0 + r;
-        TE* dst = kv + ((long long)pages[pos / page_tokens] * 2 + 1) * n_kv_heads * head_stride + h * head_stride;
-        dst[(long long)d * page_tokens + pos % page_tokens] = tile[r * pitch + d];
+    // rows out: a warp per dimension, lanes along the positions (runs of consecutive positions)
+    for (int d = warp; d < head_dim; d += n_warps) {
+#pragma unroll 2
+        for (int r = lane; r < n; r += 32) {
+            const int pos = pos0 + r;
+            TE* dst = kv + ((long long)pages[pos / page_tokens] * 2 + 1) * n_kv_heads * head_stride + h * head_stride;
+            dst[(long long)d * page_tokens + pos % page_tokens] = tile[r * pitch + d];
+        }
     }
 }
 

@@ -319,8 +319,34 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// A [rows, cols] bfloat16 matrix with `ld` elements between rows, cut into boxes of box_rows x 64.
+// Descriptors are pure functions of (address, shape, stride, box): the last few hundred are kept, since a
+// model asks for the same ones step after step (weights always, activations whenever the allocator hands
+// the same buffer back).
+struct MapKey {
+    const void* base; int rows, cols, box_rows; long long ld;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && ld == o.ld;
+    }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+static MapSlot map_cache[512];
+static std::mutex map_mutex;
+
+static bool make_map_uncached(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows);
+
 static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
+    const MapKey key = {base, rows, cols, box_rows, ld};
+    const size_t h = ((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)rows * 31 + (size_t)cols * 131 + box_rows;
+    MapSlot& slot = map_cache[(h >> 20) & 511];
+    std::lock_guard<std::mutex> lock(map_mutex);
+    if (slot.used && slot.key == key) { *map = slot.map; return true; }
+    if (!make_map_uncached(map, base, rows, cols, ld, box_rows)) return false;
+    slot.key = key; slot.map = *map; slot.used = true;
+    return true;
+}
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows, cut into boxes of box_rows x 64.
+static bool make_map_uncached(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -330,6 +356,18 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, lon
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// SMs of the current device (asked once: this library drives one device per process).
+static int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+            sms = 0;
+    }
+    return sms;
 }
 
 template <int BN, int STAGES, typename TC>
@@ -346,10 +384,8 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
             return MU_ERR_LAUNCH;
         raised = true;
     }
-    int device = 0, sms = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
-        return MU_ERR_LAUNCH;
+    const int sms = sm_count();
+    if (sms <= 0) return MU_ERR_LAUNCH;
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     kernel<<<grid, TC_THREADS, smem, s>>>(map_a, map_w, bias, residual, C, M, N, K, ldc, ldr, act, status);
@@ -373,8 +409,7 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
     cudaStream_t s = (cudaStream_t)stream;
     // Tile width: wider tiles do more products per byte loaded, but the tiles must also fill whole
     // rounds of the SMs; take the width with the best (fill of the last round) x (worth of the width).
-    int device = 0, sms = 148;
-    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int sms = mu::sm_count() > 0 ? mu::sm_count() : 148;
     const long long m_tiles = (M + mu::TC_BM - 1) / mu::TC_BM;
     int best_bn = 64;
     double best = -1.0;

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                             _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p,
                             _c_int, _c_p],
+    "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
+                               _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
 }
 
@@ -105,7 +107,15 @@ def _check(code: int, what: str, launches: int = 1) -> None:
     launch_count += launches
 
 
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream        # the current stream's handle without a Stream object
+except AttributeError:                                       # pragma: no cover
+    _raw_stream = None
+
+
 def _stream() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -431,6 +441,23 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
     return out
 
 
+def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv_heads: int,
+                 head_dim: int) -> bool:
+    """Whether the tensor-core single-token attention takes this case (else the
+    CUDA-core kernel does): bfloat16, head sizes 32 and 64, at most 16 query
+    heads per kv head, 16-byte aligned rows.  MU_B200_ATT_TC=0 switches it off."""
+    if os.environ.get("MU_B200_ATT_TC", "1") == "0":
+        return False
+    if kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim not in (32, 64):
+        return False
+    if n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 16:
+        return False
+    for t in (q, k_new, v_new):
+        if t is not None and (t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0):
+            return False
+    return True
+
+
 def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
                      out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, page_tokens: int,
                      tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
@@ -449,6 +476,15 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     n_tokens = q.shape[0]
+    if decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens, n_heads, n_kv_heads, head_dim):
+        warps = int(os.environ.get("MU_B200_ATT_TC_WARPS", "0")) or min(8, max(1, int(n_splits)))
+        _check(library().mu_attention_decode_tc(
+            _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
+            v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
+            _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
+            n_heads, n_kv_heads, head_dim, float(scale), int(window), warps, _stream()),
+            f"attention_decode_tc(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+        return out
     _check(library().mu_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
         v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),

@@ -299,6 +299,51 @@ def test_single_token_attention_kernel(n_heads, n_kv_heads, head_dim, window, dt
     assert_close(out2.float().cpu().numpy(), want, dtype, "after the append")
 
 
+@pytest.mark.parametrize("warps", [1, 2, 8])
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (5, 5, 64, 0), (16, 1, 64, 0), (12, 4, 32, 0), (9, 3, 64, 100), (6, 3, 32, 64), (22, 2, 64, 0), (34, 2, 32, 0)])
+def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window, warps, monkeypatch):
+    """The tensor-core kernel of single-token steps at every number of warps
+    (one page per warp, several pages per warp), with grouped heads up to 16
+    per kv head and windows that start inside a page; one key far back is made
+    to carry most of the weight of its head, so a misplaced column shows."""
+    from math_utils_b200.csrc import ops
+    monkeypatch.setenv("MU_B200_ATT_TC_WARPS", str(warps))
+    rng = np.random.default_rng(1000 * warps + head_dim + n_heads)
+    seq_lens = [1, 2, 63, 64, 65, 128, 700, 1000]
+    kv, table, ks, vs = paged_setup(rng, seq_lens, n_kv_heads, head_dim, "bfloat16")
+    scale = 1.0 / math.sqrt(head_dim)
+    q = dev(rng.standard_normal((len(seq_lens), n_heads * head_dim)), torch.bfloat16)
+    # the last sequences: the key at `far` answers head 1's query
+    for s, far in ((6, 37), (7, 901)):
+        if window and seq_lens[s] - far > window:
+            far = seq_lens[s] - window            # the first position the window still holds
+        h, g = 1, 1 // (n_heads // n_kv_heads)
+        ks[s][far, g * head_dim:(g + 1) * head_dim] = (6.0 * q[s, h * head_dim:(h + 1) * head_dim].float()).to(torch.bfloat16)
+    tok_pos = torch.tensor([p for n in seq_lens for p in range(n - 1)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([s for s, n in enumerate(seq_lens) for _ in range(n - 1)], dtype=torch.int32, device="cuda")
+    ops.kv_append(torch.cat([k[:-1] for k in ks]), torch.cat([v[:-1] for v in vs]), tok_pos, tok_seq, table, 64,
+                  n_kv_heads, head_dim, kv)
+    k_new = torch.stack([k[-1] for k in ks]).contiguous()
+    v_new = torch.stack([v[-1] for v in vs]).contiguous()
+    pos1 = torch.tensor([n - 1 for n in seq_lens], dtype=torch.int32, device="cuda")
+    assert ops.decode_tc_ok(q, k_new, v_new, kv, 64, n_heads, n_kv_heads, head_dim) == (n_heads // n_kv_heads <= 16)
+    want = np.stack([plain_gpt2.causal_attention(
+        np.repeat(q[s:s + 1].double().cpu().numpy(), n, axis=0), ks[s].double().cpu().numpy(),
+        vs[s].double().cpu().numpy(), n_heads, n_kv_heads, scale, window)[-1] for s, n in enumerate(seq_lens)])
+    vmax = max(float(v.abs().max()) for v in vs)
+    for round_ in range(2):                       # with the append, then over the appended cache
+        out = torch.full_like(q, float("nan"))
+        ops.attention_decode(q, k_new if round_ == 0 else None, v_new if round_ == 0 else None, out, kv, table, 64,
+                             pos1, None, n_heads, n_kv_heads, head_dim, scale, window, table.shape[1])
+        # probabilities are rounded to bfloat16 before they meet the values: 2^-9 of a value's size each
+        assert_close(out.float().cpu().numpy(), want, "bfloat16", f"launch {round_}", extra_abs=2.0 ** -8 * vmax)
+    out2 = torch.empty_like(q)
+    seq1 = torch.arange(len(seq_lens), dtype=torch.int32, device="cuda")
+    ops.attention(q, out2, kv, table, 64, pos1, seq1, n_heads, n_kv_heads, head_dim, scale, window)
+    assert_close(out2.float().cpu().numpy(), want, "bfloat16", "the general kernel over the appended cache")
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 50, 24), (8, 2304, 768), (13, 77, 40), (16, 1031, 96), (3, 130, 1600)])
 @pytest.mark.parametrize("act", [None, "gelu_new"])
 def test_product_with_the_norm_inside(m, n, k, act):

@@ -48,8 +48,7 @@ __global__ void kv_append_kernel(const TE* __restrict__ k, long long ldk, const 
     }
 }
 
-// The same copy in 16-byte pieces, for rows and strides that allow it.  WITH_V false: keys only
-// (the values of a prompt go through v_append_tiles_kernel).
+// The same copy in 16-byte pieces, for rows and strides that allow it.  (WITH_V false: keys only.)
 template <typename TE, bool WITH_V>
 __global__ void kv_append_vec_kernel(const TE* __restrict__ k, long long ldk, const TE* __restrict__ v,
                                      long long ldv, const int* __restrict__ tok_pos,
@@ -80,38 +79,60 @@ __global__ void kv_append_vec_kernel(const TE* __restrict__ k, long long ldk, co
     }
 }
 
-// Values of a whole tile of prompt tokens (up to 64 consecutive tokens of one sequence) for one kv
-// head: the tile is turned in shared memory so that each dimension row of the page is written as a
-// run of consecutive positions.  tiles: int32 [n][2] = (first flat token, count).
+// Keys and values of a whole tile of prompt tokens (up to 64 consecutive tokens of one sequence) for
+// one kv head.  Keys are copied row by row in 16-byte pieces.  Values are turned in shared memory so
+// that each dimension row of the page is written as runs of consecutive positions: 16 bytes at a time
+// where the tile starts at a position that allows it, element by element otherwise.
+// tiles: int32 [n][2] = (first flat token, count).
 template <typename TE>
-__global__ void v_append_tiles_kernel(const TE* __restrict__ v, long long ldv, const int* __restrict__ tok_pos,
-                                      const int* __restrict__ tok_seq, const int* __restrict__ block_table,
-                                      int max_pages, int page_tokens, const int* __restrict__ tiles,
-                                      int n_kv_heads, int head_dim, TE* __restrict__ kv) {
+__global__ void __launch_bounds__(256)
+kv_append_tiles_kernel(const TE* __restrict__ k, long long ldk, const TE* __restrict__ v, long long ldv,
+                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                       const int* __restrict__ block_table, int max_pages, int page_tokens,
+                       const int* __restrict__ tiles, int n_kv_heads, int head_dim, TE* __restrict__ kv) {
+    constexpr int E = 16 / (int)sizeof(TE);                      // elements per 16-byte piece
+    constexpr int W = 4 / (int)sizeof(TE);                       // elements per 32-bit word
     extern __shared__ __align__(16) unsigned char vt_raw[];
-    TE* tile = reinterpret_cast<TE*>(vt_raw);                    // [64][head_dim + pad]
-    const int pitch = head_dim + (sizeof(TE) == 2 ? 2 : 1);     // an odd number of 32-bit words per row: no bank conflicts
-    const int flat0 = tiles[2 * blockIdx.x], n = tiles[2 * blockIdx.x + 1];
+    uint32_t* tile = reinterpret_cast<uint32_t*>(vt_raw);        // [64][pitch] words
+    const int pitch = head_dim / W + 1;                          // an odd number of words per row
+    const int flat0 = tiles[2 * blockIdx.x], n = min(tiles[2 * blockIdx.x + 1], 64);   // the tile buffer holds 64 rows
     const int h = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    // rows in: a warp per token, lanes along the head (coalesced reads)
-    for (int r = warp; r < n; r += n_warps) {
-        const TE* src = v + (long long)(flat0 + r) * ldv + h * head_dim;
-#pragma unroll 4
-        for (int d = lane; d < head_dim; d += 32) tile[r * pitch + d] = src[d];
-    }
-    __syncthreads();
     const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
     const int pos0 = tok_pos[flat0];
     const long long head_stride = (long long)page_tokens * head_dim;
-    // rows out: a warp per dimension, lanes along the positions (runs of consecutive positions)
-    for (int d = warp; d < head_dim; d += n_warps) {
-#pragma unroll 2
-        for (int r = lane; r < n; r += 32) {
-            const int pos = pos0 + r;
-            TE* dst = kv + ((long long)pages[pos / page_tokens] * 2 + 1) * n_kv_heads * head_stride + h * head_stride;
-            dst[(long long)d * page_tokens + pos % page_tokens] = tile[r * pitch + d];
-        }
+    const int ppr = head_dim / E;                                // pieces per row
+    for (int i = threadIdx.x; i < n * ppr; i += blockDim.x) {
+        const int r = i / ppr, c = i % ppr, pos = pos0 + r;
+        const long long src = (long long)(flat0 + r) * ldk + h * head_dim + c * E;
+        TE* kdst = kv + ((long long)pages[pos / page_tokens] * 2 * n_kv_heads + h) * head_stride;
+        *reinterpret_cast<uint4*>(kdst + (long long)(pos % page_tokens) * head_dim + c * E) =
+            *reinterpret_cast<const uint4*>(k + src);
+        const uint4 vv = *reinterpret_cast<const uint4*>(v + (long long)(flat0 + r) * ldv + h * head_dim + c * E);
+        uint32_t* row = tile + r * pitch + c * 4;
+        row[0] = vv.x; row[1] = vv.y; row[2] = vv.z; row[3] = vv.w;
+    }
+    __syncthreads();
+    const TE* te = reinterpret_cast<const TE*>(tile);
+    const int pitch_e = pitch * W;
+    const int runs = (pos0 % E == 0) ? n / E : 0;                // whole 16-byte runs of positions
+    // lanes along the runs of a dimension row (one row of the page is contiguous), then along dimensions
+    const int rpd = 64 / E;                                      // runs a dimension row of a full tile has
+    for (int i = threadIdx.x; i < head_dim * rpd; i += blockDim.x) {
+        const int run = i % rpd, d = i / rpd;
+        if (run >= runs) continue;
+        const int pos = pos0 + run * E;
+        __align__(16) TE piece[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) piece[e] = te[(run * E + e) * pitch_e + d];
+        TE* vdst = kv + (((long long)pages[pos / page_tokens] * 2 + 1) * n_kv_heads + h) * head_stride;
+        *reinterpret_cast<uint4*>(vdst + (long long)d * page_tokens + pos % page_tokens) =
+            *reinterpret_cast<const uint4*>(piece);
+    }
+    const int rest0 = runs * E;                                  // what the runs left: one element at a time
+    for (int i = threadIdx.x; i < (n - rest0) * head_dim; i += blockDim.x) {
+        const int r = rest0 + i % (n - rest0), d = i / (n - rest0), pos = pos0 + r;
+        TE* vdst = kv + (((long long)pages[pos / page_tokens] * 2 + 1) * n_kv_heads + h) * head_stride;
+        vdst[(long long)d * page_tokens + pos % page_tokens] = te[r * pitch_e + d];
     }
 }
 
@@ -301,36 +322,38 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
     const int e = is_bf16 ? 8 : 4;
     if (ldk % e == 0 && ldv % e == 0 && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) && !((uintptr_t)kv & 15)) {
         const int vthreads = n_kv_heads * head_dim / e >= 128 ? 128 : 64;
-        const bool tiled = tiles != nullptr && n_tiles > 0 && n_kv_heads <= 65535;
-#define MU_APPEND(TE, WITH_V)                                                                          \
-    mu::kv_append_vec_kernel<TE, WITH_V><<<n_tokens, vthreads, 0, s>>>(                                 \
-        (const TE*)k, ldk, (const TE*)v, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens,   \
-        n_kv_heads, head_dim, (TE*)kv)
-        if (is_bf16) { if (tiled) MU_APPEND(__nv_bfloat16, false); else MU_APPEND(__nv_bfloat16, true); }
-        else { if (tiled) MU_APPEND(float, false); else MU_APPEND(float, true); }
-#undef MU_APPEND
-        MU_CHECK_LAUNCH();
+        const bool tiled = tiles != nullptr && n_tiles > 0 && n_kv_heads <= 65535 && page_tokens % 8 == 0;
         if (tiled) {
             dim3 grid(n_tiles, n_kv_heads);
-            const size_t smem = (size_t)64 * (head_dim + 2) * (is_bf16 ? 2 : 4);
+            const size_t smem = (size_t)64 * (head_dim * (is_bf16 ? 2 : 4) + 4);
             if (is_bf16)
-                mu::v_append_tiles_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(
-                    (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens, tiles,
-                    n_kv_heads, head_dim, (__nv_bfloat16*)kv);
+                mu::kv_append_tiles_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(
+                    (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table,
+                    max_pages, page_tokens, tiles, n_kv_heads, head_dim, (__nv_bfloat16*)kv);
             else {
                 if (smem > 48 * 1024) {
                     static bool raised = false;
-                    if (!raised && cudaFuncSetAttribute(mu::v_append_tiles_kernel<float>,
+                    if (!raised && cudaFuncSetAttribute(mu::kv_append_tiles_kernel<float>,
                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
                         return MU_ERR_LAUNCH;
                     raised = true;
                 }
-                mu::v_append_tiles_kernel<float><<<grid, 256, smem, s>>>(
-                    (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens, tiles,
-                    n_kv_heads, head_dim, (float*)kv);
+                mu::kv_append_tiles_kernel<float><<<grid, 256, smem, s>>>(
+                    (const float*)k, ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages,
+                    page_tokens, tiles, n_kv_heads, head_dim, (float*)kv);
             }
             MU_CHECK_LAUNCH();
+            return MU_OK;
         }
+        if (is_bf16)
+            mu::kv_append_vec_kernel<__nv_bfloat16, true><<<n_tokens, vthreads, 0, s>>>(
+                (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table,
+                max_pages, page_tokens, n_kv_heads, head_dim, (__nv_bfloat16*)kv);
+        else
+            mu::kv_append_vec_kernel<float, true><<<n_tokens, vthreads, 0, s>>>(
+                (const float*)k, ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages,
+                page_tokens, n_kv_heads, head_dim, (float*)kv);
+        MU_CHECK_LAUNCH();
         return MU_OK;
     }
     if (is_bf16)

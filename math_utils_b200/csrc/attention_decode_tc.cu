@@ -123,6 +123,15 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
         pv = view_of(my_first);
         fetch(pv);
     }
+    // later pages of this warp: ask for them now, so that their turn finds them in L2
+    for (int p = my_first + NW; p <= last_page; p += NW) {
+        const char* kb = reinterpret_cast<const char*>(kv + ((long long)pages[p] * 2 * n_kv_heads + kvh) * head_stride);
+        const char* vb = kb + (long long)n_kv_heads * head_stride * (long long)sizeof(__nv_bfloat16);
+        for (int off = lane * 128; off < TD_PAGE * DH * (int)sizeof(__nv_bfloat16); off += 32 * 128) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + off));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + off));
+        }
+    }
     pdl_wait();                                    // this step's query, key and value from here on
 
     // the query rows as left-operand fragments: thread (g, t) holds dims [t dh/4, (t+1) dh/4) of rows g, g + 8

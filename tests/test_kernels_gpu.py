@@ -433,3 +433,39 @@ def test_prompt_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window)
         assert_close(out[o:o + n - s].float().cpu().numpy(), want, "bfloat16", f"sequence {i}",
                      extra_abs=2.0 ** -8 * vmax)
         o += n - s
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_kv_heads,head_dim", [(3, 16), (2, 64), (1, 80), (5, 256)])
+def test_append_by_tiles_writes_the_same_cache(n_kv_heads, head_dim, dtype):
+    """Keys and values appended a tile at a time (16-byte runs of positions
+    where the tile's first position allows it) leave the cache as the
+    token-by-token append does: whole tiles, tails, tiles that start inside a
+    page at positions that are and are not multiples of 8."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(head_dim + n_kv_heads)
+    totals = [1, 64, 65, 200, 333, 100]
+    starts = [0, 0, 0, 70, 128, 8]
+    kv_a, table, ks, vs = paged_setup(rng, totals, n_kv_heads, head_dim, dtype)
+    kv_b = torch.zeros_like(kv_a)
+    tok_pos = torch.tensor([p for n, s in zip(totals, starts) for p in range(s, n)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([i for i, (n, s) in enumerate(zip(totals, starts)) for _ in range(s, n)],
+                           dtype=torch.int32, device="cuda")
+    k_all = torch.cat([k[s:] for k, s in zip(ks, starts)])
+    v_all = torch.cat([v[s:] for v, s in zip(vs, starts)])
+    tiles, flat = [], 0
+    for n, s in zip(totals, starts):
+        for o in range(0, n - s, 64):
+            tiles.append((flat + o, min(64, n - s - o)))
+        flat += n - s
+    tiles_t = torch.tensor(tiles, dtype=torch.int32, device="cuda")
+    ops.kv_append(k_all, v_all, tok_pos, tok_seq, table, 64, n_kv_heads, head_dim, kv_a)
+    ops.kv_append(k_all, v_all, tok_pos, tok_seq, table, 64, n_kv_heads, head_dim, kv_b, tiles=tiles_t)
+    assert torch.equal(kv_a, kv_b)
+    # and the layout itself: a key row per position, a value row per dimension
+    page = int(table[4, 2])                                   # sequence 4, positions 128..191
+    flat_k = kv_a[page, 0].reshape(n_kv_heads, 64, head_dim)
+    flat_v = kv_a[page, 1].reshape(n_kv_heads, head_dim, 64)
+    want_k = ks[4][128:192].reshape(64, n_kv_heads, head_dim).permute(1, 0, 2)
+    want_v = vs[4][128:192].reshape(64, n_kv_heads, head_dim).permute(1, 2, 0)
+    assert torch.equal(flat_k, want_k) and torch.equal(flat_v, want_v)

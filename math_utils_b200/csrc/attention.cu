@@ -95,6 +95,8 @@ kv_append_tiles_kernel(const TE* __restrict__ k, long long ldk, const TE* __rest
     extern __shared__ __align__(16) unsigned char vt_raw[];
     uint32_t* tile = reinterpret_cast<uint32_t*>(vt_raw);        // [64][pitch] words
     const int pitch = head_dim / W + 1;                          // an odd number of words per row
+    pdl_trigger();
+    pdl_wait();
     const int flat0 = tiles[2 * blockIdx.x], n = min(tiles[2 * blockIdx.x + 1], 64);   // the tile buffer holds 64 rows
     const int h = blockIdx.y;
     const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
@@ -327,9 +329,10 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
             dim3 grid(n_tiles, n_kv_heads);
             const size_t smem = (size_t)64 * (head_dim * (is_bf16 ? 2 : 4) + 4);
             if (is_bf16)
-                mu::kv_append_tiles_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(
-                    (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq, block_table,
-                    max_pages, page_tokens, tiles, n_kv_heads, head_dim, (__nv_bfloat16*)kv);
+                return mu::launch_pdl(mu::kv_append_tiles_kernel<__nv_bfloat16>, grid, dim3(256), smem, s, 1,
+                                      (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq,
+                                      block_table, max_pages, page_tokens, tiles, n_kv_heads, head_dim,
+                                      (__nv_bfloat16*)kv);
             else {
                 if (smem > 48 * 1024) {
                     static bool raised = false;
@@ -338,9 +341,9 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
                         return MU_ERR_LAUNCH;
                     raised = true;
                 }
-                mu::kv_append_tiles_kernel<float><<<grid, 256, smem, s>>>(
-                    (const float*)k, ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages,
-                    page_tokens, tiles, n_kv_heads, head_dim, (float*)kv);
+                return mu::launch_pdl(mu::kv_append_tiles_kernel<float>, grid, dim3(256), smem, s, 1, (const float*)k,
+                                      ldk, (const float*)v, ldv, tok_pos, tok_seq, block_table, max_pages,
+                                      page_tokens, tiles, n_kv_heads, head_dim, (float*)kv);
             }
             MU_CHECK_LAUNCH();
             return MU_OK;

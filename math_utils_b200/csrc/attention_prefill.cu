@@ -76,6 +76,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
     const int first_key = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int first_page = first_key / FP_KT, last_page = pos_last / FP_KT;
     const long long head_stride = (long long)FP_KT * DH;
+    pdl_trigger();
+    pdl_wait();                                    // queries and this step's cache rows come from the kernels before
 
     auto load_page = [&](int page_idx, int stage) {
         const __nv_bfloat16* kp = kv + ((long long)pages[page_idx] * 2 * n_kv_heads + kvh) * head_stride;
@@ -239,10 +241,9 @@ static int launch_prefill(const void* q, long long ldq, void* out, long long ldo
         }
     }
     dim3 grid(n_tiles, n_heads);
-    kernel<<<grid, FP_THREADS, smem, s>>>((const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo,
-                                          (const __nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, tiles,
-                                          n_heads, n_kv_heads, scale, window);
-    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+    return launch_pdl(kernel, grid, dim3(FP_THREADS), smem, s, 1, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out,
+                      ldo, (const __nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, tiles, n_heads,
+                      n_kv_heads, scale, window);
 }
 
 }  // namespace mu

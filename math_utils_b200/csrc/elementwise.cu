@@ -83,6 +83,8 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                       TO* __restrict__ y, int n_rows, int hidden, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * LN_WARPS + warp;
+    pdl_trigger();
+    pdl_wait();
     if (r >= n_rows) return;
     const long long src_row = rows ? rows[r] : r;
     const float4* src4 = reinterpret_cast<const float4*>(x + src_row * hidden);
@@ -148,13 +150,10 @@ MU_EXPORT int mu_layernorm(const float* x, const int* rows, const float* gamma, 
     if (aligned && hidden <= 32 * mu::LN_V * 4) {
         const unsigned blocks = (n_rows + mu::LN_WARPS - 1) / mu::LN_WARPS;
         if (out_bf16)
-            mu::layernorm_rows_kernel<__nv_bfloat16><<<blocks, mu::LN_WARPS * 32, 0, s>>>(
-                x, rows, gamma, beta, (__nv_bfloat16*)y, n_rows, hidden, eps);
-        else
-            mu::layernorm_rows_kernel<float><<<blocks, mu::LN_WARPS * 32, 0, s>>>(
-                x, rows, gamma, beta, (float*)y, n_rows, hidden, eps);
-        MU_CHECK_LAUNCH();
-        return MU_OK;
+            return mu::launch_pdl(mu::layernorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0, s,
+                                  1, x, rows, gamma, beta, (__nv_bfloat16*)y, n_rows, hidden, eps);
+        return mu::launch_pdl(mu::layernorm_rows_kernel<float>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0, s, 1, x,
+                              rows, gamma, beta, (float*)y, n_rows, hidden, eps);
     }
     if (hidden > 12288) return MU_ERR_UNSUPPORTED_SIZE;   // the row must fit 48 KB of shared memory
     const int threads = hidden >= 1024 ? 256 : 128;

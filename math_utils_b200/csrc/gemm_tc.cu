@@ -158,6 +158,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    pdl_trigger();
+    pdl_wait();                                  // barriers and tensor memory are set up while the kernel before ends
 
     // consecutive tiles share a column block of W and differ in their rows of A, so the blocks that
     // run at the same time read few distinct tiles of either operand
@@ -388,8 +390,8 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
     if (sms <= 0) return MU_ERR_LAUNCH;
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-    kernel<<<grid, TC_THREADS, smem, s>>>(map_a, map_w, bias, residual, C, M, N, K, ldc, ldr, act, status);
-    return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+    return launch_pdl(kernel, grid, dim3(TC_THREADS), smem, s, 1, map_a, map_w, bias, residual, C, M, N, K, ldc, ldr,
+                      act, status);
 }
 
 }  // namespace mu

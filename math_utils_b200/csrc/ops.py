@@ -100,9 +100,13 @@ def declare(name: str, argtypes) -> None:
 launch_count = 0      # kernels of this library launched so far (a merge after a split counts too)
 
 
-def _check(code: int, what: str, launches: int = 1) -> None:
+def _check(code: int, what, launches: int = 1) -> None:
+    """``what`` names the call for the error message: a string, or a tuple of a
+    format and its arguments, put together only when there is an error."""
     global launch_count
     if code != 0:
+        if isinstance(what, tuple):
+            what = what[0].format(*what[1:])
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
     launch_count += launches
 
@@ -113,9 +117,12 @@ except AttributeError:                                       # pragma: no cover
     _raw_stream = None
 
 
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
-    if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+    if _raw_stream is not None and _current_device is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -198,7 +205,7 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor]
     if out is None:
         out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
     _check(library().mu_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), n, hidden,
-                                  float(eps), _is_bf16(out), _stream()), f"layernorm(hidden={hidden})")
+                                  float(eps), _is_bf16(out), _stream()), ("layernorm(hidden={})", hidden))
     return out
 
 
@@ -244,7 +251,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     _check(library().mu_gemm_simt(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
         out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
-        _is_bf16(a), _is_bf16(out), _stream()), f"gemm_simt({m}x{n}x{k})")
+        _is_bf16(a), _is_bf16(out), _stream()), ("gemm_simt({}x{}x{})", m, n, k))
     return out
 
 
@@ -287,7 +294,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     _check(library().mu_gemm_tc(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
         out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
-        _is_bf16(out), _ptr(status_word(a.device)), _stream()), f"gemm_tc({m}x{n}x{k})")
+        _is_bf16(out), _ptr(status_word(a.device)), _stream()), ("gemm_tc({}x{}x{})", m, n, k))
     return out
 
 
@@ -308,7 +315,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     _check(library().mu_gemm_skinny(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
         out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
-        _is_bf16(out), _stream()), f"gemm_skinny({m}x{n}x{k})")
+        _is_bf16(out), _stream()), ("gemm_skinny({}x{}x{})", m, n, k))
     return out
 
 
@@ -332,7 +339,7 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: t
         _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(tok_pos), _ptr(tok_seq),
         _ptr(block_table), block_table.shape[1], page_tokens, k.shape[0], n_kv_heads, head_dim,
         _ptr(kv_pages), _is_bf16(kv_pages), _ptr(tiles), tiles.shape[0] if tiles is not None else 0, _stream()),
-        f"kv_append(head_dim={head_dim})", launches=2 if tiles is not None else 1)
+        ("kv_append(head_dim={})", head_dim))
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor,
@@ -360,7 +367,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_
         block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
         n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), int(split_keys),
         _ptr(part_o), _ptr(part_ml), _is_bf16(kv_pages), _stream()),
-        f"attention(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})", launches=2 if n_splits > 1 else 1)
+        ("attention(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim), launches=2 if n_splits > 1 else 1)
     return out
 
 
@@ -437,7 +444,7 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
         _ptr(x.x), x.x.stride(0), _ptr(x.rows), _ptr(x.gamma), _ptr(x.beta), float(x.eps), _ptr(w), _ptr(bias),
         _ptr(residual), _ptr(out), m, n, k, w.stride(0), out.stride(0),
         residual.stride(0) if residual is not None else 0, ACT_CODES[act], _is_bf16(out), _stream()),
-        f"gemm_skinny_ln({m}x{n}x{k})")
+        ("gemm_skinny_ln({}x{}x{})", m, n, k))
     return out
 
 
@@ -483,7 +490,7 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
             v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
             _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
             n_heads, n_kv_heads, head_dim, float(scale), int(window), warps, _stream()),
-            f"attention_decode_tc(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+            ("attention_decode_tc(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
         return out
     _check(library().mu_attention_decode(
         _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
@@ -491,7 +498,7 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
         n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), None, None, None,
         _is_bf16(kv_pages), _stream()),
-        f"attention_decode(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+        ("attention_decode(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
     return out
 
 
@@ -512,7 +519,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor
     _check(library().mu_attention_prefill(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv_pages), _ptr(block_table), block_table.shape[1],
         page_tokens, _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles), tiles.shape[0], n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), _stream()), f"attention_prefill(heads={n_heads}/{n_kv_heads}, head_dim={head_dim})")
+        float(scale), int(window), _stream()), ("attention_prefill(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
     return out
 
 

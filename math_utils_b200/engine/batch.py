@@ -82,6 +82,22 @@ class StepContext:
     def is_decode(self) -> bool:
         return self.max_q_len == 1
 
+    def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+        """An activation buffer of this shape that lives from step to step and is
+        shared by every layer that asks under the same name: layers run one after
+        another on one stream, so a layer's intermediate results are dead when the
+        next layer writes them.  Only the last shape asked for is kept."""
+        key = ("buffer", name, dtype)
+        held = self.workspace.get(key)
+        if held is not None and held[0] == shape:
+            return held[1]
+        numel = 1
+        for n in shape:
+            numel *= n
+        view = self.scratch(name, numel, dtype)[:numel].view(shape)
+        self.workspace[key] = (shape, view)
+        return view
+
     def scratch(self, name: str, numel: int, dtype=torch.float32) -> torch.Tensor:
         """A reusable device buffer of at least ``numel`` elements."""
         key = (name, dtype)

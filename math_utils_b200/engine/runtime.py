@@ -8,6 +8,9 @@ import torch
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
+_ops = None            # the kernel module, imported when first asked for
+
+
 @dataclass
 class Runtime:
     """``dtype`` is the compute dtype: bfloat16 (the serving path: bfloat16
@@ -19,8 +22,11 @@ class Runtime:
 
     @property
     def ops(self):
-        from ..csrc import ops
-        return ops
+        global _ops
+        if _ops is None:
+            from ..csrc import ops
+            _ops = ops
+        return _ops
 
     @property
     def is_fp32(self) -> bool:

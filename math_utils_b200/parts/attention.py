@@ -57,13 +57,14 @@ class CausalSelfAttention(Mixer):
 
     def forward(self, h, residual, ctx, cache, owns_cache: bool) -> None:
         ops = self.runtime.ops
-        qkv = self.qkv(h)
+        qkv = self.qkv(h, out=ctx.buffer("attention.qkv", (ctx.n_tokens, self.q_width + 2 * self.kv_width),
+                                         self.runtime.dtype))
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
         ctx.position.rotate(q, k, ctx)
         table = ctx.block_tables[cache.group]
-        attn = torch.empty((ctx.n_tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
+        attn = ctx.buffer("attention.out", (ctx.n_tokens, self.q_width), qkv.dtype)
         if ctx.is_decode and cache.page_tokens == 64:
             # one launch: append this token's key and value, attend page by page, merge
             ops.attention_decode(q, k if owns_cache else None, v if owns_cache else None, attn, cache.pages,

@@ -40,7 +40,9 @@ class DenseFeedForward(FeedForward):
         self.down = Linear(tensors[self.tensor_name("down_weight")], tensors[self.tensor_name("down_bias")], runtime)
 
     def forward(self, h, residual, ctx) -> None:
-        u = self.up(h, act=self.activation)
+        hidden = None if ctx is None else ctx.buffer("feed_forward.hidden", (ctx.n_tokens, self.inner_size),
+                                                     self.runtime.dtype)
+        u = self.up(h, act=self.activation, out=hidden)
         self.down(u, residual=residual, out=residual)
 
 

@@ -302,15 +302,300 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The same kernel with the pages staged in shared memory.  A key page and a value page of one kv head
+// are each one contiguous run of the cache, so one thread brings a page in with two bulk copies
+// (cp.async.bulk, completion counted by an mbarrier); every warp owns a ring of RING page buffers and
+// keeps that many of its pages in flight while it works on the oldest.  The bytes in flight no longer
+// sit in registers, so more warps fit on an SM and memory streams while the tensor cores work: this is
+// the variant for many sequences, and it lets a block of few sequences ask for all of its pages at once.
+// Fragments are read from shared memory with the same addressing as from the cache (rows of a page are
+// 64 or 128 bytes apart, so the two rows that a quarter of a warp reads together collide on banks two
+// ways at most).  Waits on a copy are bounded; a wait that runs out sets *status to 4 and the block
+// writes nothing.
+constexpr unsigned long long TD_WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t td_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool td_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = td_smem(bar);
+    unsigned long long start = 0;
+    for (unsigned int spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 1023u) == 1023u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > TD_WAIT_NS) return false;
+        }
+    }
+}
+
+template <int KD, int NW, int RING>
+__global__ void __launch_bounds__(NW * 32)
+attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
+                             const __nv_bfloat16* __restrict__ k_new, long long ldk,
+                             const __nv_bfloat16* __restrict__ v_new, long long ldv,
+                             __nv_bfloat16* __restrict__ out, long long ldo, __nv_bfloat16* kv,
+                             const int* __restrict__ block_table, int max_pages,
+                             const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
+                             int n_kv_heads, float scale, int window, int* status) {
+    constexpr int DH = 16 * KD;
+    constexpr int KV4 = KD / 2;                    // 16-byte pieces of a key row that a thread holds
+    constexpr int PAGE_ELEMS = TD_PAGE * DH;       // one kv head's keys (or values) of a page
+    constexpr uint32_t PAGE_BYTES = PAGE_ELEMS * sizeof(__nv_bfloat16);
+    extern __shared__ __align__(128) unsigned char ring_raw[];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(ring_raw);              // [NW][RING][2][PAGE_ELEMS]
+    float* part_o = reinterpret_cast<float*>(ring_raw + (size_t)NW * RING * 2 * PAGE_BYTES);   // [NW][rows][DH + 1]
+    __shared__ uint64_t full[NW][RING];
+    __shared__ float part_m[NW][16], part_l[NW][16];
+    __shared__ float weight[NW][16];
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int tk = blockIdx.x / n_kv_heads, kvh = blockIdx.x % n_kv_heads;
+    const int rows = n_heads / n_kv_heads;
+    pdl_trigger();
+    if (threadIdx.x == 0) failed = 0;
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < RING; ++r)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(td_smem(&full[warp][r])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int* pages = block_table + (long long)(tok_seq ? tok_seq[tk] : tk) * max_pages;
+    const int pos = tok_pos[tk];
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int first_page = first / TD_PAGE, last_page = pos / TD_PAGE;
+    const long long head_stride = (long long)PAGE_ELEMS;
+    const int my_first = first_page + warp;
+    const int n_mine = my_first <= last_page ? (last_page - my_first) / NW + 1 : 0;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * RING * 2 * PAGE_ELEMS;
+
+    // one lane asks for the warp's i-th page: two contiguous runs of the cache, one barrier
+    auto issue = [&](int i) {
+        const int slot = i % RING;
+        const long long page = pages[my_first + i * NW];
+        const __nv_bfloat16* ksrc = kv + (page * 2 * n_kv_heads + kvh) * head_stride;
+        const __nv_bfloat16* vsrc = ksrc + (long long)n_kv_heads * head_stride;
+        const uint32_t bar = td_smem(&full[warp][slot]);
+        const uint32_t dst = td_smem(my_ring + (size_t)slot * 2 * PAGE_ELEMS);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * PAGE_BYTES) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst), "l"(ksrc), "r"(PAGE_BYTES), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst + PAGE_BYTES), "l"(vsrc), "r"(PAGE_BYTES), "r"(bar) : "memory");
+    };
+    // rows written by earlier steps, which no kernel of this step touches, may be asked for at once
+    int issued = 0;
+    if (lane == 0)
+        for (; issued < n_mine && issued < RING; ++issued) issue(issued);
+    pdl_wait();                                    // this step's query, key and value from here on
+
+    uint32_t qa[KD][4];
+    {
+        uint4 lo4[KV4], hi4[KV4];
+#pragma unroll
+        for (int c = 0; c < KV4; ++c) { lo4[c] = make_uint4(0, 0, 0, 0); hi4[c] = make_uint4(0, 0, 0, 0); }
+        if (g < rows) {
+            const uint4* src = reinterpret_cast<const uint4*>(q + (long long)tk * ldq + (long long)(kvh * rows + g) * DH + (DH / 4) * t);
+#pragma unroll
+            for (int c = 0; c < KV4; ++c) lo4[c] = src[c];
+        }
+        if (g + 8 < rows) {
+            const uint4* src = reinterpret_cast<const uint4*>(q + (long long)tk * ldq + (long long)(kvh * rows + g + 8) * DH + (DH / 4) * t);
+#pragma unroll
+            for (int c = 0; c < KV4; ++c) hi4[c] = src[c];
+        }
+        const uint32_t* lw = reinterpret_cast<const uint32_t*>(lo4);
+        const uint32_t* hw = reinterpret_cast<const uint32_t*>(hi4);
+#pragma unroll
+        for (int kk = 0; kk < KD; ++kk) {
+            qa[kk][0] = lw[2 * kk]; qa[kk][1] = hw[2 * kk]; qa[kk][2] = lw[2 * kk + 1]; qa[kk][3] = hw[2 * kk + 1];
+        }
+    }
+    const float c_log2 = scale * 1.4426950408889634f;
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o_acc[2 * KD][4];
+#pragma unroll
+    for (int j = 0; j < 2 * KD; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_acc[j][i] = 0.0f;
+
+    bool ok = true;
+    for (int i = 0; i < n_mine; ++i) {
+        const int slot = i % RING;
+        const int page_idx = my_first + i * NW;
+        if (!td_wait(&full[warp][slot], (uint32_t)((i / RING) & 1))) { ok = false; break; }
+        const __nv_bfloat16* ks = my_ring + (size_t)slot * 2 * PAGE_ELEMS;
+        const __nv_bfloat16* vs = ks + PAGE_ELEMS;
+        const int base = page_idx * TD_PAGE;
+        const int lo = max(first - base, 0), hi = min(pos + 1 - base, TD_PAGE);
+        const bool has_new = (k_new != nullptr) && page_idx == last_page;
+        const __nv_bfloat16* kn = has_new ? k_new + (long long)tk * ldk + kvh * DH : nullptr;
+        const __nv_bfloat16* vn = has_new ? v_new + (long long)tk * ldv + kvh * DH : nullptr;
+        const int new_key = hi - 1;
+        if (has_new) {
+            // append to the cache: this block is the only one for this (sequence, kv head)
+            const long long page = pages[page_idx];
+            __nv_bfloat16* kpage = kv + (page * 2 * n_kv_heads + kvh) * head_stride;
+            __nv_bfloat16* vpage = kpage + (long long)n_kv_heads * head_stride;
+            for (int d = lane; d < DH; d += 32) {
+                kpage[(long long)new_key * DH + d] = kn[d];
+                vpage[(long long)d * TD_PAGE + new_key] = vn[d];
+            }
+        }
+        const int jn = (new_key & 15) >> 1;
+        const bool mine_new = has_new && (16 * (g >> 1) + 2 * jn + (g & 1) == new_key);
+
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+            const int key = 16 * (g >> 1) + 2 * j + (g & 1);
+            uint4 kf[KV4];
+            const uint4* src = (mine_new && j == jn) ? reinterpret_cast<const uint4*>(kn + (DH / 4) * t)
+                                                     : reinterpret_cast<const uint4*>(ks + key * DH + (DH / 4) * t);
+#pragma unroll
+            for (int c = 0; c < KV4; ++c) kf[c] = src[c];
+            const uint32_t* kw = reinterpret_cast<const uint32_t*>(kf);
+#pragma unroll
+            for (int kk = 0; kk < KD; ++kk) td_mma(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kw[2 * kk], kw[2 * kk + 1]);
+        }
+        float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = 16 * t + 2 * j + (e & 1);
+                const float v = (key >= lo && key < hi) ? s[j][e] * c_log2 : -INFINITY;
+                s[j][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2], sum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            corr[r] = exp2f(m_run[r] - mx[r]);
+            m_run[r] = mx[r];
+        }
+        float w_new[2] = {0.0f, 0.0f};
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = exp2f(s[j][e] - mx[e >> 1]);
+                sum[e >> 1] += p[e];
+                if (has_new && 16 * t + 2 * j + (e & 1) == new_key) { w_new[e >> 1] = p[e]; p[e] = 0.0f; }
+            }
+            pa[j >> 1][(j & 1) * 2] = td_pack(p[0], p[1]);
+            pa[j >> 1][(j & 1) * 2 + 1] = td_pack(p[2], p[3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + sum[r];
+#pragma unroll
+        for (int j = 0; j < 2 * KD; ++j) {
+            o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0]; o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+            const uint4* src = reinterpret_cast<const uint4*>(vs + (8 * j + g) * TD_PAGE + 16 * t);
+            uint4 vf[2] = {src[0], src[1]};
+            const uint32_t* vw = reinterpret_cast<const uint32_t*>(vf);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                td_mma(o_acc[j], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], vw[2 * kk], vw[2 * kk + 1]);
+        }
+        if (has_new) {
+            const int src_lane = (lane & ~3) | ((new_key >> 4) & 3);
+            const float w0 = __shfl_sync(0xffffffffu, w_new[0], src_lane);
+            const float w1 = __shfl_sync(0xffffffffu, w_new[1], src_lane);
+#pragma unroll
+            for (int j = 0; j < 2 * KD; ++j) {
+                const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vn + 8 * j + 2 * t));
+                o_acc[j][0] = fmaf(w0, v.x, o_acc[j][0]); o_acc[j][1] = fmaf(w0, v.y, o_acc[j][1]);
+                o_acc[j][2] = fmaf(w1, v.x, o_acc[j][2]); o_acc[j][3] = fmaf(w1, v.y, o_acc[j][3]);
+            }
+        }
+        __syncwarp();                              // every lane has read the buffer: it may be filled again
+        if (lane == 0 && issued < n_mine) issue(issued++);
+    }
+    if (!ok) {
+        // let the copies still under way land before the block goes away, then report
+        if (lane == 0) {
+            for (int i = 0; i < issued; ++i)
+                if (i + RING >= issued) td_wait(&full[warp][i % RING], (uint32_t)((i / RING) & 1));
+            atomicExch(status, 4);
+            failed = 1;
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* mine = part_o + (long long)warp * rows * (DH + 1);
+#pragma unroll
+    for (int j = 0; j < 2 * KD; ++j) {
+        if (g < rows) {
+            mine[g * (DH + 1) + 8 * j + 2 * t] = o_acc[j][0];
+            mine[g * (DH + 1) + 8 * j + 2 * t + 1] = o_acc[j][1];
+        }
+        if (g + 8 < rows) {
+            mine[(g + 8) * (DH + 1) + 8 * j + 2 * t] = o_acc[j][2];
+            mine[(g + 8) * (DH + 1) + 8 * j + 2 * t + 1] = o_acc[j][3];
+        }
+    }
+    if (t == 0) {
+        part_m[warp][g] = m_run[0]; part_m[warp][g + 8] = m_run[1];
+        part_l[warp][g] = l_run[0]; part_l[warp][g + 8] = l_run[1];
+    }
+    __syncthreads();
+    if (failed) return;
+    if (threadIdx.x < NW * 16) {
+        const int w = threadIdx.x / 16, r = threadIdx.x % 16;
+        float big = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < NW; ++x) big = fmaxf(big, part_m[x][r]);
+        weight[w][r] = part_m[w][r] == -INFINITY ? 0.0f : exp2f(part_m[w][r] - big);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32) {
+        const int r = idx / DH, d = idx % DH;
+        float total = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            total = fmaf(part_l[w][r], weight[w][r], total);
+            o = fmaf(part_o[(w * rows + r) * (DH + 1) + d], weight[w][r], o);
+        }
+        out[(long long)tk * ldo + (long long)(kvh * rows + r) * DH + d] = __float2bfloat16_rn(o / total);
+    }
+}
+
 }  // namespace mu
 
-// Arguments as mu_attention_decode (bfloat16 only).  n_warps: warps per block (1, 2, 4 or 8).
+// Arguments as mu_attention_decode (bfloat16 only).  ring 0: pages go from the cache straight into
+// registers, n_warps (1, 2, 4 or 8) warps per block.  ring 1: pages are staged in shared memory by bulk
+// copies, n_warps 2 (many blocks: three of them share an SM) or 6 (few blocks); `status` is a device word
+// that is set to 4 if a wait for a copy runs out.
 MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k_new, long long ldk,
                                      const void* v_new, long long ldv, void* out, long long ldo, void* kv,
                                      const int* block_table, int max_pages, int page_tokens,
                                      const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads,
                                      int n_kv_heads, int head_dim, float scale, int window, int n_warps,
-                                     void* stream) {
+                                     int ring, int* status, void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (page_tokens != mu::TD_PAGE) return MU_ERR_UNSUPPORTED_SIZE;
     if (head_dim != 32 && head_dim != 64) return MU_ERR_UNSUPPORTED_SIZE;
@@ -323,11 +608,41 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
     const long long blocks = (long long)n_tokens * n_kv_heads;
     if (blocks > 2147483647ll) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const int nw = n_warps >= 8 ? 8 : n_warps >= 4 ? 4 : n_warps >= 2 ? 2 : 1;
     int rc = MU_ERR_UNSUPPORTED_SIZE;
+    if (ring) {
+        if (!status) return MU_ERR_BAD_ARGUMENT;
+        const int rows = n_heads / n_kv_heads;
+#define MU_TR(KD, NW)                                                                                          \
+    do {                                                                                                       \
+        auto kernel = mu::attention_decode_ring_kernel<KD, NW, 2>;                                             \
+        const size_t smem = (size_t)NW * 2 * 2 * mu::TD_PAGE * 16 * KD * sizeof(__nv_bfloat16) +               \
+                            (size_t)NW * rows * (16 * KD + 1) * sizeof(float);                                 \
+        static bool raised = false;                                                                            \
+        if (!raised) {                                                                                         \
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=       \
+                cudaSuccess)                                                                                   \
+                return MU_ERR_LAUNCH;                                                                          \
+            raised = true;                                                                                     \
+        }                                                                                                      \
+        if (smem > 200 * 1024) return MU_ERR_UNSUPPORTED_SIZE;                                                 \
+        rc = mu::launch_pdl(kernel, dim3((unsigned)blocks), dim3(NW * 32), smem, s, 1,                         \
+            (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_new, ldk, (const __nv_bfloat16*)v_new, ldv,  \
+            (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, n_heads,   \
+            n_kv_heads, scale, window, status);                                                                \
+    } while (0)
+        // six warps with their rings and many query heads per kv head may not fit: then two warps do it
+        const size_t six = (size_t)6 * 2 * 2 * mu::TD_PAGE * head_dim * sizeof(__nv_bfloat16) +
+                           (size_t)6 * rows * (head_dim + 1) * sizeof(float);
+        const bool wide = n_warps >= 6 && six <= 200 * 1024;
+        if (head_dim == 32) { if (wide) MU_TR(2, 6); else MU_TR(2, 2); }
+        else { if (wide) MU_TR(4, 6); else MU_TR(4, 2); }
+#undef MU_TR
+        return rc;
+    }
+    const int nw = n_warps >= 8 ? 8 : n_warps >= 4 ? 4 : n_warps >= 2 ? 2 : 1;
 #define MU_TD(KD, NW)                                                                                       \
     rc = mu::launch_pdl(mu::attention_decode_tc_kernel<KD, NW>, dim3((unsigned)blocks), dim3(NW * 32), \
-        (size_t)NW * (n_heads / n_kv_heads) * (16 * KD + 1) * sizeof(float), s, 1, \
+        (size_t)NW * (n_heads / n_kv_heads) * (16 * KD + 1) * sizeof(float), s, 1,                          \
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_new, ldk, (const __nv_bfloat16*)v_new, ldv,   \
         (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, n_heads,    \
         n_kv_heads, scale, window)

@@ -59,7 +59,8 @@ _SIGNATURES = {
                             _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p,
                             _c_int, _c_p],
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
-                               _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p],
+                               _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p,
+                               _c_p],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
 }
 
@@ -448,6 +449,16 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
     return out
 
 
+_sm_counts = {}
+
+
+def _sm_count(device) -> int:
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
 def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv_heads: int,
                  head_dim: int) -> bool:
     """Whether the tensor-core single-token attention takes this case (else the
@@ -484,12 +495,19 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         _i32(t, name)
     n_tokens = q.shape[0]
     if decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens, n_heads, n_kv_heads, head_dim):
-        warps = int(os.environ.get("MU_B200_ATT_TC_WARPS", "0")) or min(8, max(1, int(n_splits)))
+        ring = os.environ.get("MU_B200_ATT_RING", "1") != "0"
+        warps = int(os.environ.get("MU_B200_ATT_TC_WARPS", "0"))
+        if not warps:
+            if ring:          # many blocks: small ones, three to an SM; few blocks: all pages in flight at once
+                warps = 2 if n_tokens * n_kv_heads >= 2 * _sm_count(q.device) else 6
+            else:
+                warps = min(8, max(1, int(n_splits)))
         _check(library().mu_attention_decode_tc(
             _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
             v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
             _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
-            n_heads, n_kv_heads, head_dim, float(scale), int(window), warps, _stream()),
+            n_heads, n_kv_heads, head_dim, float(scale), int(window), warps, int(ring),
+            _ptr(status_word(q.device)), _stream()),
             ("attention_decode_tc(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
         return out
     _check(library().mu_attention_decode(

@@ -299,18 +299,21 @@ def test_single_token_attention_kernel(n_heads, n_kv_heads, head_dim, window, dt
     assert_close(out2.float().cpu().numpy(), want, dtype, "after the append")
 
 
-@pytest.mark.parametrize("warps", [1, 2, 8])
+@pytest.mark.parametrize("staged,warps", [(0, 1), (0, 2), (0, 8), (1, 2), (1, 6)])
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
     (5, 5, 64, 0), (16, 1, 64, 0), (12, 4, 32, 0), (9, 3, 64, 100), (6, 3, 32, 64), (22, 2, 64, 0), (34, 2, 32, 0)])
-def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window, warps, monkeypatch):
-    """The tensor-core kernel of single-token steps at every number of warps
-    (one page per warp, several pages per warp), with grouped heads up to 16
-    per kv head and windows that start inside a page; one key far back is made
-    to carry most of the weight of its head, so a misplaced column shows."""
+def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window, staged, warps, monkeypatch):
+    """The tensor-core kernels of single-token steps (pages straight into
+    registers, or staged in shared memory by bulk copies) at every number of
+    warps (one page per warp, several pages per warp, more pages than the ring
+    holds), with grouped heads up to 16 per kv head and windows that start inside
+    a page; one key far back is made to carry most of the weight of its head, so
+    a misplaced column shows."""
     from math_utils_b200.csrc import ops
     monkeypatch.setenv("MU_B200_ATT_TC_WARPS", str(warps))
+    monkeypatch.setenv("MU_B200_ATT_RING", str(staged))
     rng = np.random.default_rng(1000 * warps + head_dim + n_heads)
-    seq_lens = [1, 2, 63, 64, 65, 128, 700, 1000]
+    seq_lens = [1, 2, 63, 64, 65, 128, 700, 1000]     # 16 pages: 8 per warp of 2, a ring holds 2
     kv, table, ks, vs = paged_setup(rng, seq_lens, n_kv_heads, head_dim, "bfloat16")
     scale = 1.0 / math.sqrt(head_dim)
     q = dev(rng.standard_normal((len(seq_lens), n_heads * head_dim)), torch.bfloat16)
@@ -342,6 +345,7 @@ def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, w
     seq1 = torch.arange(len(seq_lens), dtype=torch.int32, device="cuda")
     ops.attention(q, out2, kv, table, 64, pos1, seq1, n_heads, n_kv_heads, head_dim, scale, window)
     assert_close(out2.float().cpu().numpy(), want, "bfloat16", "the general kernel over the appended cache")
+    ops.check_status()
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 50, 24), (8, 2304, 768), (13, 77, 40), (16, 1031, 96), (3, 130, 1600)])

@@ -30,6 +30,22 @@ namespace mu {
 
 constexpr int TC_BM = 128, TC_BK = 64, TC_EPI_WARPS = 8, TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr unsigned long long TC_WAIT_NS = 2000000000ull;      // a wait gives up after two seconds
+constexpr int TC_PATCH_PITCH = 33;               // floats per row of an epilogue patch: odd, so columns and rows both spread over the banks
+
+// Optional time stamps for measurements (mu_gemm_tc_trace): per block TC_TRACE_WORDS words of
+// %globaltimer: [0] set-up done, [1] the kernel before has ended, then for each of the block's first
+// TC_TRACE_TILES tiles: first and last load issued, first stage arrived, last product issued,
+// accumulator seen complete by the epilogue, epilogue's stores issued.
+constexpr int TC_TRACE_TILES = 4, TC_TRACE_WORDS = 2 + 6 * TC_TRACE_TILES;
+__device__ unsigned long long* g_tc_trace = nullptr;
+
+__device__ __forceinline__ void tc_stamp(unsigned long long* trace, int word) {
+    if (trace) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        trace[(long long)blockIdx.x * TC_TRACE_WORDS + word] = now;
+    }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -123,6 +139,7 @@ struct TcSmem {
     uint64_t acc_full[2];                        // an accumulator is complete (tensor cores -> epilogue)
     uint64_t acc_empty[2];                       // an accumulator has been read out (epilogue -> tensor cores)
     uint32_t tmem_base;
+    float patch[TC_EPI_WARPS][32 * TC_PATCH_PITCH];   // where each epilogue warp turns a 32 x 32 block
 };
 
 // Persistent: a block per SM walks over the tiles of C (tile = block, block + grid, ...); the ring of
@@ -158,15 +175,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
+    unsigned long long* const trace = g_tc_trace;
+    if (threadIdx.x == 0) tc_stamp(trace, 0);
     pdl_trigger();
     pdl_wait();                                  // barriers and tensor memory are set up while the kernel before ends
+    if (threadIdx.x == 0) tc_stamp(trace, 1);
 
     // consecutive tiles share a column block of W and differ in their rows of A, so the blocks that
     // run at the same time read few distinct tiles of either operand
     if (warp == 0) {
         if (lane == 0) {
             long long it = 0, issued = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            int local = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
                 const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = (int)(it % STAGES);
@@ -176,6 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tma_load_2d(sm.a[s], &map_a, kb * TC_BK, m0, &sm.full[s]);
                     tma_load_2d(sm.b[s], &map_w, kb * TC_BK, n0, &sm.full[s]);
                     issued = it + 1;
+                    if (local < TC_TRACE_TILES && (kb == 0 || kb == num_kb - 1)) tc_stamp(trace, 2 + 6 * local + (kb == 0 ? 0 : 1));
                 }
             }
             if (!ok) {
@@ -200,6 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int s = (int)(it % STAGES);
                     ok = mbar_wait(&sm.full[s], (uint32_t)((it / STAGES) & 1));
                     if (!ok) break;
+                    if (kb == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
@@ -211,89 +234,106 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     umma_commit(&sm.empty[s]);            // the stage is free once these have read it
                 }
                 if (ok) umma_commit(&sm.acc_full[buf]);   // the accumulator is complete
+                if (local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 3);
             }
             if (!ok) atomicExch(status, 2);
         }
     } else {
         // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31; two warps share each
         // quarter of the rows and take half of the columns each, so that every scheduler of the SM
-        // has two epilogue warps to switch between
+        // has two epilogue warps to switch between.  tcgen05.ld hands every thread one row of a 32 x 32
+        // block.
         const int quad = warp & 3;
         const int half = (warp - 2) / 4;
         constexpr int COLS = BN / (TC_EPI_WARPS / 4);
-        const bool vec_ok = ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) &&
-                            (!residual || ((ldr % 4 == 0) && (((uintptr_t)residual) % 16 == 0)));
+        float* patch = sm.patch[warp - 2];
+        constexpr int CHUNKS = COLS / 32;
+        const bool vec_ok = sizeof(TC) == 2 && ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) && !residual;
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-            const int row = m0 + quad * 32 + lane;
+            const int row0 = m0 + quad * 32;
+            // float32 path: the bias of this lane's columns, fetched while the tensor cores are still at work
+            float bias_col[CHUNKS];
+#pragma unroll
+            for (int q = 0; q < CHUNKS; ++q) {
+                const int n = n0 + half * COLS + 32 * q + lane;
+                bias_col[q] = (bias && !vec_ok && n < N) ? bias[n] : 0.0f;
+            }
             ok = mbar_wait(&sm.acc_full[buf], (uint32_t)((local >> 1) & 1));
             if (!ok) {
                 if (lane == 0) atomicExch(status, 3);
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int c0 = half * COLS; c0 < (half + 1) * COLS; c0 += 32) {
+            if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 4);
+#pragma unroll
+            for (int q = 0; q < CHUNKS; ++q) {
+                const int c0 = half * COLS + 32 * q;
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-                if (c0 + 32 >= (half + 1) * COLS) {
+                if (q == CHUNKS - 1) {
                     // this warp has read all it needs of the accumulator: the tensor cores may have it back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
                 }
                 const int nb = n0 + c0;
-                if (row >= M || nb >= N) continue;
-                float v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int n = nb + i;
-                    float x = __uint_as_float(r[i]);
-                    if (bias && n < N) x += bias[n];
-                    v[i] = sizeof(TC) == 2 ? apply_act_bf16(x, act) : apply_act(x, act);
-                }
-                TC* crow = C + (long long)row * ldc + nb;
-                const float* rrow = residual ? residual + (long long)row * ldr + nb : nullptr;
+                if (row0 >= M || nb >= N) continue;                   // the same for the whole warp
                 if (vec_ok && nb + 32 <= N) {
-                    if (rrow) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float4 q = *reinterpret_cast<const float4*>(rrow + i);
-                            v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
-                        }
-                    }
-                    if (sizeof(TC) == 4) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(crow) + i) =
-                                make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                    } else {
+                    // bfloat16 without a residual: every thread packs its row of the block and stores it in
+                    // 16-byte pieces (measured faster here than turning the block for row-wise stores)
+                    if (row0 + lane < M) {
+                        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(C) + (long long)(row0 + lane) * ldc + nb;
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                v[e] = apply_act_bf16(__uint_as_float(r[i + e]) + (bias ? bias[nb + i + e] : 0.0f), act);
                             uint4 packed;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
                             packed.x = *reinterpret_cast<uint32_t*>(&h0);
                             packed.y = *reinterpret_cast<uint32_t*>(&h1);
                             packed.z = *reinterpret_cast<uint32_t*>(&h2);
                             packed.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(crow) + i) = packed;
+                            *reinterpret_cast<uint4*>(crow + i) = packed;
                         }
                     }
-                } else {
+                    continue;
+                }
+                // otherwise the block is turned in the warp's patch of shared memory and handled a row per
+                // instruction, a lane per column: whole 128-byte runs of float32.  All of the residual is
+                // asked for before any of it is used (it may be C itself: every element is read and written
+                // by the same lane).
+                __syncwarp();                                         // the patch's last readers are done
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (nb + i < N) {
-                            float x = v[i];
-                            if (rrow) x += rrow[i];
-                            crow[i] = from_float<TC>(x);
-                        }
-                    }
+                for (int i = 0; i < 32; ++i) patch[lane * TC_PATCH_PITCH + i] = __uint_as_float(r[i]);
+                __syncwarp();
+                const int n_rows = min(32, M - row0);
+                const int n = nb + lane;
+                const bool live = n < N;
+                const float bv = vec_ok ? ((bias && live) ? bias[n] : 0.0f) : bias_col[q];
+                TC* cc = C + (long long)row0 * ldc + n;
+                const float* rr = (residual && live) ? residual + (long long)row0 * ldr + n : nullptr;
+                float x[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x[i] = (rr && i < n_rows) ? rr[(long long)i * ldr] : 0.0f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float y = patch[i * TC_PATCH_PITCH + lane] + bv;
+                    x[i] += sizeof(TC) == 2 ? apply_act_bf16(y, act) : apply_act(y, act);
+                }
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (i < n_rows) cc[(long long)i * ldc] = from_float<TC>(x[i]);
                 }
             }
+            if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 5);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -395,6 +435,14 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
 }
 
 }  // namespace mu
+
+// For measurements: a device buffer of (blocks x TC_TRACE_WORDS) 64-bit words that the kernel's roles
+// stamp with %globaltimer from now on (see tc_stamp), or null to stop.  Returns the words per block.
+MU_EXPORT int mu_gemm_tc_trace(void* buffer) {
+    unsigned long long* p = (unsigned long long*)buffer;
+    if (cudaMemcpyToSymbol(mu::g_tc_trace, &p, sizeof(p)) != cudaSuccess) return -1;
+    return mu::TC_TRACE_WORDS;
+}
 
 // bfloat16 A [M, K] (lda) and W [N, K] (ldw): K, lda, ldw multiples of 8, bases 16-byte aligned.
 // C bfloat16 or float32 (ldc); residual float32 (ldr), may be C itself.  `status` is a device word

@@ -43,6 +43,7 @@ _SIGNATURES = {
                      _c_int, _c_int, _c_int, _c_p],
     "mu_gemm_skinny": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                        _c_int, _c_int, _c_p],
+    "mu_gemm_tc_trace": [_c_p],
     "mu_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                    _c_int, _c_int, _c_p, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
@@ -297,6 +298,18 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
         _is_bf16(out), _ptr(status_word(a.device)), _stream()), ("gemm_tc({}x{}x{})", m, n, k))
     return out
+
+
+def gemm_tc_trace(buffer: Optional[torch.Tensor]) -> int:
+    """For measurements: from now on every gemm_tc block stamps the device clock
+    into ``buffer`` (int64, blocks x the returned number of words: set-up done,
+    wait for the kernel before over, then per tile first/last load issued, first
+    stage arrived, last product issued, accumulator complete, stores issued);
+    ``None`` stops it."""
+    words = library().mu_gemm_tc_trace(_ptr(buffer))
+    if words < 0:
+        raise KernelError("gemm_tc_trace: the trace pointer could not be set")
+    return words
 
 
 def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -563,9 +576,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
             return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
         x = x.materialize()
-    # up to 16 rows the few-rows kernel; up to 64 too, unless the output is wide enough to give
-    # the tensor-core kernel a tile per SM (its TMA pipeline streams the weights faster)
-    if skinny_ok(x, weight) and (x.shape[0] <= 16 or weight.shape[0] < 128 * 148 or not tc_ok(x, weight)):
+    # up to 32 rows the few-rows kernel; up to 64 too where the weight is deeper than wide (its split
+    # along k fills the SMs); wider weights go to the tensor-core kernel from 33 rows on, whose TMA
+    # pipeline streams them faster once every block has to read that many rows of activations anyway
+    if skinny_ok(x, weight) and (x.shape[0] <= 32 or weight.shape[0] < weight.shape[1] or not tc_ok(x, weight)):
         return gemm_skinny(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
     if tc_ok(x, weight):
         return gemm_tc(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)

@@ -1,9 +1,10 @@
 // Causal attention of whole prompts over the paged cache on tensor cores (bfloat16).
 //
 // Flash-style: a block takes 64 consecutive query tokens of one sequence and one
-// head (4 warps x 16 queries) and walks the sequence's cache pages; a page is 64
-// keys, contiguous per head, and is copied with cp.async into padded shared
-// memory (two pages in flight).  Per page: S = Q K^T with mma.sync.m16n8k16
+// head and walks the sequence's cache pages in two groups of 4 warps (16 queries
+// a warp), one group on the even and one on the odd pages, which are merged at the
+// end; a page is 64 keys, contiguous per head, and is copied with cp.async into
+// padded shared memory (two pages in flight per group).  Per page: S = Q K^T with mma.sync.m16n8k16
 // (K fragments by ldmatrix), scale, causal / window mask, online softmax in
 // float32 registers (running max and sum per query row), P rounded to bfloat16
 // and fed straight back as the A operand of O += P V (V fragments by ldmatrix
@@ -15,13 +16,21 @@
 // Formulas: include/ai/Kernels.hpp:132-161.  Head sizes 16..128 in steps of 16.
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <math.h>
 
 namespace mu {
 
 constexpr int FP_QT = 64;       // queries per block
 constexpr int FP_KT = 64;       // keys per page
-constexpr int FP_THREADS = 128;
+constexpr int FP_THREADS = 256;  // two groups of 4 warps: each group takes every other page of the tile's keys
+constexpr int FP_GROUP = 128;
+
+__device__ __forceinline__ void group_sync(int grp) {     // the 128 threads of one group
+    if (grp == 0) asm volatile("bar.sync 1, %0;" ::"n"(FP_GROUP) : "memory");
+    else asm volatile("bar.sync 2, %0;" ::"n"(FP_GROUP) : "memory");
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
@@ -57,38 +66,51 @@ __global__ void __launch_bounds__(FP_THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __nv_bfloat16* __restrict__ out,
                          long long ldo, const __nv_bfloat16* __restrict__ kv, const int* __restrict__ block_table,
                          int max_pages, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                         const int* __restrict__ tiles, int n_heads, int n_kv_heads, float scale, int window) {
+                         const int* __restrict__ tiles, int n_items, int* counter, int n_heads, int n_kv_heads,
+                         float scale, int window) {
     constexpr int DH = 16 * KD, P = DH + 8;
     constexpr int CHUNKS = DH / 8;                 // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char fp_smem[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(fp_smem);
-    __nv_bfloat16* k_s = q_s + FP_QT * P;          // [2][64][P]
     constexpr int VP = FP_KT + 8;                  // pitch of a value row (one dimension, 64 positions)
-    __nv_bfloat16* v_s = k_s + 2 * FP_KT * P;      // [2][DH][VP]
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int GROUP_ELEMS = 2 * FP_KT * P + 2 * DH * VP;     // a group's two stages of keys and of values
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int grp = tid / FP_GROUP, gtid = tid % FP_GROUP, warp = gtid >> 5;      // warp: which 16 queries
+    __nv_bfloat16* k_s = q_s + FP_QT * P + grp * GROUP_ELEMS;    // [2][64][P]
+    __nv_bfloat16* v_s = k_s + 2 * FP_KT * P;                    // [2][DH][VP]
+    float* merge_o = reinterpret_cast<float*>(q_s + FP_QT * P + GROUP_ELEMS);      // over the second group's stages
+    float* merge_ml = merge_o + FP_QT * DH;                      // [64][2]
     const int g = lane >> 2, t = lane & 3;
-    const int flat0 = tiles[2 * blockIdx.x], nq = tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, kvh = h / (n_heads / n_kv_heads);
+    __shared__ int next_item;
+    pdl_trigger();
+    pdl_wait();                                    // queries and this step's cache rows come from the kernels before
+    // The blocks take (tile, head) items from a counter until none is left.  The caller lists the tiles
+    // longest first, so the long ones start at once on every SM and the short ones fill the gaps.
+    for (;;) {
+    if (tid == 0) next_item = atomicAdd(&counter[0], 1);
+    __syncthreads();
+    const int item = next_item;
+    if (item >= n_items) break;
+    const int tile = item / n_heads;
+    const int flat0 = tiles[2 * tile], nq = tiles[2 * tile + 1];
+    const int h = item % n_heads, kvh = h / (n_heads / n_kv_heads);
     const int pos0 = tok_pos[flat0];
     const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
     const int pos_last = pos0 + nq - 1;
     const int first_key = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int first_page = first_key / FP_KT, last_page = pos_last / FP_KT;
     const long long head_stride = (long long)FP_KT * DH;
-    pdl_trigger();
-    pdl_wait();                                    // queries and this step's cache rows come from the kernels before
 
     auto load_page = [&](int page_idx, int stage) {
         const __nv_bfloat16* kp = kv + ((long long)pages[page_idx] * 2 * n_kv_heads + kvh) * head_stride;
         const __nv_bfloat16* vp = kp + (long long)n_kv_heads * head_stride;
         __nv_bfloat16* ks = k_s + stage * FP_KT * P;
         __nv_bfloat16* vs = v_s + stage * DH * VP;
-        for (int c = tid; c < FP_KT * CHUNKS; c += FP_THREADS) {
+        for (int c = gtid; c < FP_KT * CHUNKS; c += FP_GROUP) {
             const int r = c / CHUNKS, o = (c % CHUNKS) * 8;
             cp_async16(ks + r * P + o, kp + r * DH + o);
         }
-        for (int c = tid; c < DH * (FP_KT / 8); c += FP_THREADS) {
+        for (int c = gtid; c < DH * (FP_KT / 8); c += FP_GROUP) {
             const int r = c / (FP_KT / 8), o = (c % (FP_KT / 8)) * 8;
             cp_async16(vs + r * VP + o, vp + r * FP_KT + o);
         }
@@ -100,7 +122,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
         if (r < nq) cp_async16(q_s + r * P + o, q + (long long)(flat0 + r) * ldq + h * DH + o);
         else *reinterpret_cast<uint4*>(q_s + r * P + o) = make_uint4(0, 0, 0, 0);
     }
-    load_page(first_page, 0);
+    const int my_first = first_page + grp;         // this group's pages: my_first, my_first + 2, ...
+    if (my_first <= last_page) load_page(my_first, 0);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
@@ -119,9 +142,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
     const float c_log2 = scale * 1.4426950408889634f;          // scores are exponentiated in base 2
     const int qpos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
 
-    for (int page_idx = first_page; page_idx <= last_page; ++page_idx) {
-        const int stage = (page_idx - first_page) & 1;
-        if (page_idx + 1 <= last_page) load_page(page_idx + 1, stage ^ 1);
+    for (int page_idx = my_first; page_idx <= last_page; page_idx += 2) {
+        const int stage = ((page_idx - my_first) >> 1) & 1;
+        if (page_idx + 2 <= last_page) load_page(page_idx + 2, stage ^ 1);
         cp_async_commit();
         const __nv_bfloat16* ks = k_s + stage * FP_KT * P;
         const __nv_bfloat16* vs = v_s + stage * DH * VP;
@@ -202,7 +225,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
             }
         }
         cp_async_wait<0>();
-        __syncthreads();
+        group_sync(grp);
     }
 
 #pragma unroll
@@ -210,16 +233,45 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
+    // the second group hands its share over (its stages are free: its last group_sync is behind it)
+    if (grp == 1) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + g + 8 * r;
-        if (row >= nq) continue;
-        const float inv = 1.0f / l_run[r];
-        __nv_bfloat16* dst = out + (long long)(flat0 + row) * ldo + h * DH;
+        for (int r = 0; r < 2; ++r) {
+            const int row = warp * 16 + g + 8 * r;
 #pragma unroll
-        for (int j = 0; j < 2 * KD; ++j) {
-            *reinterpret_cast<uint32_t*>(dst + 8 * j + 2 * t) =
-                pack_bf16(o_acc[j][2 * r] * inv, o_acc[j][2 * r + 1] * inv);
+            for (int j = 0; j < 2 * KD; ++j)
+                *reinterpret_cast<float2*>(merge_o + row * DH + 8 * j + 2 * t) =
+                    make_float2(o_acc[j][2 * r], o_acc[j][2 * r + 1]);
+            if (t == 0) *reinterpret_cast<float2*>(merge_ml + 2 * row) = make_float2(m_run[r], l_run[r]);
+        }
+    }
+    __syncthreads();
+    if (grp == 0) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = warp * 16 + g + 8 * r;
+            if (row >= nq) continue;
+            const float2 ml = *reinterpret_cast<const float2*>(merge_ml + 2 * row);
+            const float m = fmaxf(m_run[r], ml.x);             // finite: the row sees at least its own key
+            const float w0 = exp2f(m_run[r] - m), w1 = exp2f(ml.x - m);
+            const float inv = 1.0f / (l_run[r] * w0 + ml.y * w1);
+            __nv_bfloat16* dst = out + (long long)(flat0 + row) * ldo + h * DH;
+#pragma unroll
+            for (int j = 0; j < 2 * KD; ++j) {
+                const float2 o1 = *reinterpret_cast<const float2*>(merge_o + row * DH + 8 * j + 2 * t);
+                *reinterpret_cast<uint32_t*>(dst + 8 * j + 2 * t) =
+                    pack_bf16((o_acc[j][2 * r] * w0 + o1.x * w1) * inv, (o_acc[j][2 * r + 1] * w0 + o1.y * w1) * inv);
+            }
+        }
+    }
+    __syncthreads();                               // shared memory and next_item are free again
+    }
+    // the last block to leave puts the counters back to zero for the next launch
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&counter[1], 1) == (int)gridDim.x - 1) {
+            counter[0] = 0;
+            counter[1] = 0;
         }
     }
 }
@@ -227,10 +279,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, __n
 template <int KD>
 static int launch_prefill(const void* q, long long ldq, void* out, long long ldo, const void* kv,
                           const int* block_table, int max_pages, const int* tok_pos, const int* tok_seq,
-                          const int* tiles, int n_tiles, int n_heads, int n_kv_heads, float scale, int window,
-                          cudaStream_t s) {
+                          const int* tiles, int n_tiles, int* counter, int n_heads, int n_kv_heads, float scale,
+                          int window, cudaStream_t s) {
     constexpr int P = 16 * KD + 8;
-    const size_t smem = ((size_t)(FP_QT + 2 * FP_KT) * P + (size_t)2 * 16 * KD * (FP_KT + 8)) * sizeof(__nv_bfloat16);
+    const size_t smem = ((size_t)FP_QT * P + 2 * ((size_t)2 * FP_KT * P + (size_t)2 * 16 * KD * (FP_KT + 8))) *
+                        sizeof(__nv_bfloat16);
     auto kernel = attention_prefill_kernel<KD>;
     if (smem > 48 * 1024) {
         static bool raised = false;
@@ -240,22 +293,40 @@ static int launch_prefill(const void* q, long long ldq, void* out, long long ldo
             raised = true;
         }
     }
-    dim3 grid(n_tiles, n_heads);
+    // as many blocks as the device holds at once (or as there are items)
+    static int resident = 0;
+    if (resident == 0) {
+        int dev = 0, sms = 0, per_sm = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, FP_THREADS, smem) != cudaSuccess ||
+            sms <= 0 || per_sm <= 0)
+            return MU_ERR_LAUNCH;
+        int cap = 2;                                // measured: two blocks per SM balance better than all that fit
+        if (const char* e = getenv("MU_B200_PREFILL_BLOCKS_PER_SM")) cap = atoi(e) > 0 ? atoi(e) : cap;
+        resident = sms * (per_sm < cap ? per_sm : cap);
+    }
+    const long long items = (long long)n_tiles * n_heads;
+    if (items > 2147483647ll) return MU_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((unsigned)(items < resident ? items : resident));
     return launch_pdl(kernel, grid, dim3(FP_THREADS), smem, s, 1, (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out,
-                      ldo, (const __nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, tiles, n_heads,
-                      n_kv_heads, scale, window);
+                      ldo, (const __nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, tiles, (int)items,
+                      counter, n_heads, n_kv_heads, scale, window);
 }
 
 }  // namespace mu
 
 // tiles: int32 [n_tiles][2] = (flat index of the tile's first query token, number of queries <= 64);
 // a tile's queries belong to one sequence and follow one another.  bfloat16 only; pages of 64
-// positions; head_dim 16..128 in steps of 16; q rows and the cache 16-byte aligned.
+// positions; head_dim 16..128 in steps of 16; q rows and the cache 16-byte aligned.  The blocks take
+// (tile, head) items in the order of `tiles`, all heads of a tile together: list the tiles with the most
+// keys first.  counter: two device ints that are zero between launches (the kernel leaves them zero).
 MU_EXPORT int mu_attention_prefill(const void* q, long long ldq, void* out, long long ldo, const void* kv,
                                    const int* block_table, int max_pages, int page_tokens, const int* tok_pos,
                                    const int* tok_seq, const int* tiles, int n_tiles, int n_heads, int n_kv_heads,
-                                   int head_dim, float scale, int window, void* stream) {
+                                   int head_dim, float scale, int window, int* counter, void* stream) {
     if (n_tiles <= 0) return MU_OK;
+    if (!counter) return MU_ERR_BAD_ARGUMENT;
     if (page_tokens != mu::FP_KT) return MU_ERR_UNSUPPORTED_SIZE;
     if (head_dim < 16 || head_dim > 128 || head_dim % 16 != 0) return MU_ERR_UNSUPPORTED_SIZE;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0 || n_heads > 65535)
@@ -267,7 +338,7 @@ MU_EXPORT int mu_attention_prefill(const void* q, long long ldq, void* out, long
 #define MU_FP(KD)                                                                                              \
     case KD:                                                                                                   \
         return mu::launch_prefill<KD>(q, ldq, out, ldo, kv, block_table, max_pages, tok_pos, tok_seq, tiles,   \
-                                      n_tiles, n_heads, n_kv_heads, scale, window, s)
+                                      n_tiles, counter, n_heads, n_kv_heads, scale, window, s)
     switch (head_dim / 16) {
         MU_FP(1); MU_FP(2); MU_FP(3); MU_FP(4); MU_FP(5); MU_FP(6); MU_FP(7); MU_FP(8);
     }

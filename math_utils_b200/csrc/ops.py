@@ -52,7 +52,7 @@ _SIGNATURES = {
                      _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p],
     "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
     "mu_attention_prefill": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int,
-                             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p],
+                             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p],
     "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
@@ -263,10 +263,10 @@ _status = {}
 def status_word(device) -> torch.Tensor:
     """A device word that kernels with bounded waits write to when a wait runs
     out (it stays 0 otherwise); ``check_status`` reads it."""
-    key = str(device)
-    if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status[key]
+    word = _status.get(device)
+    if word is None:
+        word = _status[device] = _status[str(device)] = torch.zeros(1, dtype=torch.int32, device=device)
+    return word
 
 
 def check_status(device="cuda:0") -> None:
@@ -543,14 +543,17 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor
                       page_tokens: int, tok_pos, tok_seq, tiles: torch.Tensor, n_heads: int, n_kv_heads: int,
                       head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
     """Flash-style causal attention of prompt tokens on tensor cores.  ``tiles``
-    int32 [n, 2]: first flat query index and query count (<= 64) of each tile."""
+    int32 [n, 2]: first flat query index and query count (<= 64) of each tile;
+    the kernel's blocks take them in this order, so the tiles with the most keys
+    should come first."""
     _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, tiles)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table"), (tiles, "tiles")):
         _i32(t, name)
+    counter = zeroed_workspace("attention_prefill_items", q.device, 8)
     _check(library().mu_attention_prefill(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv_pages), _ptr(block_table), block_table.shape[1],
         page_tokens, _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles), tiles.shape[0], n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), _stream()), ("attention_prefill(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
+        float(scale), int(window), _ptr(counter), _stream()), ("attention_prefill(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
     return out
 
 
@@ -576,14 +579,52 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
             return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
         x = x.materialize()
+    # One pass over what the kernels need, then straight to the library (this is the call a prompt
+    # step makes a hundred times): the shapes must agree here; alignment, strides and sizes that a
+    # kernel cannot take come back from the library as an error code.
+    if x.dim() != 2 or weight.dim() != 2:
+        raise KernelError(f"gemm shapes do not agree: a {tuple(x.shape)}, w {tuple(weight.shape)}")
+    m, k = x.shape
+    n, kw = weight.shape
+    dtype = x.dtype
+    if k != kw or dtype != weight.dtype or x.stride(1) != 1 or weight.stride(1) != 1:
+        raise KernelError(f"gemm operands do not agree: a {tuple(x.shape)} {dtype}, w {tuple(weight.shape)} "
+                          f"{weight.dtype}, unit stride along k needed")
+    if not (x.is_cuda and weight.is_cuda):
+        raise KernelError("math_utils_b200 kernels run on CUDA tensors only")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or dtype, device=x.device)
+    elif out.shape != (m, n) or out.stride(1) != 1 or not out.is_cuda:
+        raise KernelError("gemm output has the wrong shape, stride or device")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != n or not bias.is_cuda):
+        raise KernelError("gemm bias must be float32 of length n on the device")
+    ldr = 0
+    if residual is not None:
+        if residual.dtype != torch.float32 or residual.shape != (m, n) or residual.stride(1) != 1 or not residual.is_cuda:
+            raise KernelError("gemm residual must be float32 [m, n] on the device")
+        ldr = residual.stride(0)
+    lda, ldw = x.stride(0), weight.stride(0)
+    pa, pw = x.data_ptr(), weight.data_ptr()
+    pb = None if bias is None else bias.data_ptr()
+    pr = None if residual is None else residual.data_ptr()
+    lib = library()
+    code = ACT_CODES[act]
+    tensor_cores = (dtype == torch.bfloat16 and k % 8 == 0 and lda % 8 == 0 and ldw % 8 == 0
+                    and pa % 16 == 0 and pw % 16 == 0)
     # up to 32 rows the few-rows kernel; up to 64 too where the weight is deeper than wide (its split
-    # along k fills the SMs); wider weights go to the tensor-core kernel from 33 rows on, whose TMA
+    # along k fills the SMs); wider weights go to the tcgen05 kernel from 33 rows on, whose TMA
     # pipeline streams them faster once every block has to read that many rows of activations anyway
-    if skinny_ok(x, weight) and (x.shape[0] <= 32 or weight.shape[0] < weight.shape[1] or not tc_ok(x, weight)):
-        return gemm_skinny(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
-    if tc_ok(x, weight):
-        return gemm_tc(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
-    return gemm_simt(x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
+    if tensor_cores and m <= 64 and (m <= 32 or n < k):
+        _check(lib.mu_gemm_skinny(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
+                                  _is_bf16(out), _stream()), ("gemm_skinny({}x{}x{})", m, n, k))
+    elif tensor_cores:
+        _check(lib.mu_gemm_tc(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
+                              _is_bf16(out), status_word(x.device).data_ptr(), _stream()),
+               ("gemm_tc({}x{}x{})", m, n, k))
+    else:
+        _check(lib.mu_gemm_simt(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
+                                _is_bf16(x), _is_bf16(out), _stream()), ("gemm_simt({}x{}x{})", m, n, k))
+    return out
 
 
 # ---------------------------------------------------- a single-token step as one recorded program

@@ -139,10 +139,14 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     tables = [cache.block_table_rows(g.index, [e.slot for e in entries]) for g in cache.kv_groups]
     tiles = []                            # query tiles of 64 for the prompt attention kernel
     if max(q_lens) > 1:
-        flat = 0
-        for n in q_lens:
-            tiles.extend((flat + o, min(TILE_QUERIES, n - o)) for o in range(0, n, TILE_QUERIES))
+        flat, ends = 0, []
+        for n, start in zip(q_lens, starts):
+            for o in range(0, n, TILE_QUERIES):
+                tiles.append((flat + o, min(TILE_QUERIES, n - o)))
+                ends.append(start + o + tiles[-1][1])
             flat += n
+        # the tiles with the most keys first: the attention kernel's blocks take them in this order
+        tiles = [tiles[i] for i in sorted(range(len(tiles)), key=lambda i: -ends[i])]
     sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * len(tiles)] + [t.size for t in tables]
     offsets = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])])   # 16-byte aligned parts
     total = int(offsets[-1])

@@ -296,6 +296,50 @@ def run_part(args):
     return 0
 
 
+def run_product_trace(args):
+    """The tensor-core product kernel on the four products of a layer (and two
+    large ones) with its time stamps switched on: prints, per shape, when the
+    blocks' loads, products and stores happened (median over the blocks, in
+    microseconds after the first block's set-up).  Not a bench record."""
+    import numpy as np
+    import torch
+    from math_utils_b200.csrc import ops
+    cfg = baseline_config()
+    e, inner, rows = cfg["n_embd"], cfg["n_inner"], PREFILL_SEQS * CONTEXT
+    shapes = [("qkv", rows, 3 * e, e, None, False), ("out", rows, e, e, None, True),
+              ("fc", rows, inner, e, cfg["activation_function"], False), ("proj", rows, e, inner, None, True),
+              ("4096^3", 4096, 4096, 4096, None, False), ("8192^3", 8192, 8192, 8192, None, False)]
+    torch.manual_seed(0)
+    names = ["set-up", "wait over"] + [f"tile{i} {w}" for i in range(4) for w in
+                                       ("first load", "last load", "first stage in", "last product", "accumulator", "stores")]
+    for name, m, n, k, act, res in shapes:
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(n, k, device="cuda") / k ** 0.5).to(torch.bfloat16)
+        bias = torch.randn(n, device="cuda")
+        x = torch.randn(m, n, device="cuda") if res else None
+        out = x if res else torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        for _ in range(3):
+            ops.gemm_tc(a, w, bias, act=act, residual=x, out=out)
+        buf = torch.zeros(148 * 64, dtype=torch.int64, device="cuda")
+        words = ops.gemm_tc_trace(buf)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        ops.gemm_tc(a, w, bias, act=act, residual=x, out=out)
+        end.record()
+        torch.cuda.synchronize()
+        ops.gemm_tc_trace(None)
+        t = buf.cpu().numpy()[:148 * words].reshape(148, words).astype(np.float64)
+        t = t[t[:, 0] > 0]
+        rel = np.where(t > 0, (t - t[:, 0].min()) / 1e3, np.nan)
+        stamps = {nm: round(float(np.nanmedian(rel[:, i])), 1) for i, nm in enumerate(names[:words])
+                  if not np.isnan(rel[:, i]).all()}
+        print(json.dumps({"part": "product_trace", "shape": name, "m": m, "n": n, "k": k, "blocks": int(t.shape[0]),
+                          "event_us": round(start.elapsed_time(end) * 1e3, 1), "us": stamps}), flush=True)
+    ops.check_status()
+    return 0
+
+
 def run_reference(args):
     # The reference is a header-only C++ project with a makefile and no Python packaging, so the
     # offline `pip install --target baseline/_ref /root/reference` has nothing to install.
@@ -313,7 +357,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "product_trace"],
                     help="run one part only and print a short line (for profiling a small case)")
     ap.add_argument("--layers", type=int, default=0, help="with --only: fewer layers than the model has")
     args = ap.parse_args()
@@ -323,6 +367,8 @@ def main():
         print(f"bench.py measures one GPU only: this library has no multi-GPU path (asked for {args.gpus})",
               flush=True)
         return 2
+    if args.only == "product_trace":
+        return run_product_trace(args)
     if args.only != "all":
         return run_part(args)
     return run_ours(args)

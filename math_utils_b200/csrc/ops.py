@@ -151,6 +151,14 @@ def _i32(t: Optional[torch.Tensor], name: str) -> None:
         raise KernelError(f"{name} must be a contiguous int32 tensor")
 
 
+def set_pdl(enabled: bool) -> None:
+    """Switches programmatic stream serialization of the launches on or off
+    (on unless MU_B200_PDL=0): with it a kernel may start, and fetch what no
+    kernel of the step writes, while the kernel before it ends.  Launches
+    already recorded in a CUDA graph keep the mode they were recorded with."""
+    library().mu_set_pdl(1 if enabled else 0)
+
+
 _workspaces = {}
 _retired = []
 

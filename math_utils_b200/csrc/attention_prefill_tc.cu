@@ -1,0 +1,399 @@
+// Causal attention of whole prompts over the paged cache on the 5th-generation tensor cores
+// (bfloat16, head size 64, pages of 64 positions).
+//
+// A block takes up to 128 consecutive query tokens of one sequence and one head and walks the
+// sequence's cache pages.  Both products of a page run as tcgen05.mma with the accumulators in tensor
+// memory, and the operands come by TMA in the layout the instruction reads:
+//   S = Q K^T   Q [128 queries][64 dims] is loaded once; a page's keys are [64 positions][64 dims],
+//               64 contiguous rows of the cache: the right operand, K-major, as it lies;
+//   O = P V     a page's values lie dimension-major in the cache, [64 dims][64 positions]: again the
+//               right operand, K-major, as it lies.  P is written by the softmax threads into shared
+//               memory in the 128-byte-swizzled layout the left operand wants.
+// Roles: warp 0 loads (one lane), warp 1 owns tensor memory and issues the products (one lane), warps 2-9
+// are the softmax in two groups that take the tile's pages in turn: a thread of a group owns a query row
+// (tcgen05.ld hands a thread a row, so maximum and sum need no shuffle), reads its 64 scores of the page
+// from tensor memory, writes its row of P, and adds each of its pages' P V, which the tensor cores leave in a
+// buffer of its own, into the float32 output row in its registers, scaled by the change of the running
+// maximum; at the end the two groups' rows are merged.  Two score buffers and two P V buffers take turns, so the products
+// of the next page run while the softmax of this one is computed.
+// Softmax, running maximum and sum, and the output accumulation are float32; P is rounded to bfloat16 for
+// the second product, as in the mma.sync kernel (attention_prefill.cu), which stays for other head sizes.
+// Every mbarrier wait is bounded; a wait that runs out sets *status (5 loads, 6 products, 7 softmax) and the
+// block leaves without storing.
+//
+// Formulas: include/ai/Kernels.hpp:132-161.
+#include "tcgen05.cuh"
+
+#include <cstdlib>
+#include <math.h>
+
+namespace mu {
+
+constexpr int PT_Q = 128;            // queries per block
+constexpr int PT_K = 64;             // keys per page
+constexpr int PT_D = 64;             // head size
+constexpr int PT_STAGES = 3;         // pages of keys and of values in flight
+constexpr int PT_THREADS = 320;      // loader, issuer, two groups of four softmax warps
+
+struct PtSmem {
+    __nv_bfloat16 q[PT_Q * PT_D];                    // 1024-byte aligned tiles, rows of 128 bytes, swizzled
+    __nv_bfloat16 k[PT_STAGES][PT_K * PT_D];
+    __nv_bfloat16 v[PT_STAGES][PT_D * PT_K];
+    __nv_bfloat16 p[2][PT_Q * PT_K];
+    uint64_t q_full;
+    uint64_t k_full[PT_STAGES], k_empty[PT_STAGES];
+    uint64_t v_full[PT_STAGES], v_empty[PT_STAGES];
+    uint64_t s_full[2], s_free[2];                   // scores ready (products -> softmax) / read (softmax -> products)
+    uint64_t p_full[2];                              // P written (softmax -> products); it is free again when its P V is complete
+    uint64_t pv_full[2], pv_free[2];                 // P V ready / read
+    uint64_t x_full[2];                              // [0]: the second group's rows are handed over
+    uint32_t tmem_base;
+    int failed;
+};
+
+// Optional time stamps for measurements (mu_attention_prefill_tc_trace): block 0 writes its SM's clock per page:
+// [4 j + 0] scores issued, [4 j + 1] P V issued (the issuing lane), [4 j + 2] scores loaded, [4 j + 3] P handed
+// over (first thread of the page's softmax group); 64 pages at most.
+__device__ unsigned long long* g_pt_trace = nullptr;
+__device__ __forceinline__ void pt_stamp(unsigned long long* trace, int word) {
+    if (trace && blockIdx.x == 0 && word < 256) {
+        trace[word] = (unsigned long long)clock64();
+    }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(PT_THREADS)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            __nv_bfloat16* __restrict__ out, long long ldo, const int* __restrict__ block_table,
+                            int max_pages, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                            const int* __restrict__ tiles, int n_heads, int n_kv_heads, float scale, int window,
+                            int* status) {
+    extern __shared__ unsigned char pt_raw[];
+    PtSmem& sm = *reinterpret_cast<PtSmem*>(((uintptr_t)pt_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x;
+    const int tile = item / n_heads, h = item % n_heads, kvh = h / (n_heads / n_kv_heads);
+    constexpr uint32_t TMEM_COLS = 256;              // scores 0 / 64, P V 128 / 192
+    constexpr uint32_t PAGE_BYTES = PT_K * PT_D * sizeof(__nv_bfloat16);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < PT_STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&sm.s_full[b], 1); mbar_init(&sm.s_free[b], 4);
+            mbar_init(&sm.p_full[b], 4);
+            mbar_init(&sm.pv_full[b], 1); mbar_init(&sm.pv_free[b], 4);
+            mbar_init(&sm.x_full[b], 4);
+        }
+        sm.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sm.tmem_base;
+    unsigned long long* const trace = g_pt_trace;
+    pdl_trigger();
+    pdl_wait();                                      // queries and this step's cache rows come from the kernels before
+
+    const int flat0 = tiles[2 * tile], nq = tiles[2 * tile + 1];
+    const int pos0 = tok_pos[flat0];
+    const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
+    const int pos_last = pos0 + nq - 1;
+    const int first_key = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int first_page = first_key / PT_K, last_page = pos_last / PT_K;
+    const int n_pages = last_page - first_page + 1;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&sm.q_full, PT_Q * PT_D * sizeof(__nv_bfloat16));
+            tma_load_2d(sm.q, &map_q, h * PT_D, flat0, &sm.q_full);
+            int issued = 0;
+            for (int j = 0; j < n_pages; ++j) {
+                const int s = j % PT_STAGES;
+                const uint32_t wrap = (uint32_t)((j / PT_STAGES) & 1);
+                const long long page = pages[first_page + j];
+                const int krow = (int)(((page * 2 + 0) * n_kv_heads + kvh) * PT_K);      // rows of 64 elements
+                const int vrow = (int)(((page * 2 + 1) * n_kv_heads + kvh) * PT_D);
+                ok = mbar_wait(&sm.k_empty[s], wrap ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(&sm.k_full[s], PAGE_BYTES);
+                tma_load_2d(sm.k[s], &map_kv, 0, krow, &sm.k_full[s]);
+                ok = mbar_wait(&sm.v_empty[s], wrap ^ 1);
+                if (!ok) { issued = j; break; }                // (its keys are counted below)
+                mbar_expect_tx(&sm.v_full[s], PAGE_BYTES);
+                tma_load_2d(sm.v[s], &map_kv, 0, vrow, &sm.v_full[s]);
+                issued = j + 1;
+            }
+            if (!ok) {
+                atomicExch(status, 5);
+                sm.failed = 1;
+            }
+            // every copy has landed before the block may go away (in the good case they have long been used)
+            mbar_wait(&sm.q_full, 0);
+            for (int j = issued > PT_STAGES ? issued - PT_STAGES : 0; j < issued; ++j) {
+                mbar_wait(&sm.k_full[j % PT_STAGES], (uint32_t)((j / PT_STAGES) & 1));
+                mbar_wait(&sm.v_full[j % PT_STAGES], (uint32_t)((j / PT_STAGES) & 1));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16(PT_Q, PT_K);       // 128 x 64 for both products (head size = page size)
+            const uint32_t q_addr = smem_u32(sm.q);
+            auto issue_pv = [&](int i) -> bool {
+                const int b = i & 1, s = i % PT_STAGES;
+                if (!mbar_wait_poll(&sm.p_full[b], (uint32_t)((i >> 1) & 1))) return false;
+                if (!mbar_wait_poll(&sm.v_full[s], (uint32_t)((i / PT_STAGES) & 1))) return false;
+                if (!mbar_wait_poll(&sm.pv_free[b], (uint32_t)(((i >> 1) & 1) ^ 1))) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t p_addr = smem_u32(sm.p[b]), v_addr = smem_u32(sm.v[s]);
+#pragma unroll
+                for (int k = 0; k < PT_K / 16; ++k)
+                    umma_bf16(tmem_base + 128 + 64 * b, smem_desc_sw128(p_addr + k * 32), smem_desc_sw128(v_addr + k * 32),
+                              idesc, k > 0 ? 1u : 0u);
+                umma_commit(&sm.v_empty[s]);
+                umma_commit(&sm.pv_full[b]);
+                pt_stamp(trace, 4 * i + 1);
+                return true;
+            };
+            ok = mbar_wait_poll(&sm.q_full, 0);
+            for (int j = 0; j < n_pages && ok; ++j) {
+                const int b = j & 1, s = j % PT_STAGES;
+                ok = mbar_wait_poll(&sm.k_full[s], (uint32_t)((j / PT_STAGES) & 1));
+                if (!ok) break;
+                ok = mbar_wait_poll(&sm.s_free[b], (uint32_t)(((j >> 1) & 1) ^ 1));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_u32(sm.k[s]);
+#pragma unroll
+                for (int k = 0; k < PT_D / 16; ++k)
+                    umma_bf16(tmem_base + 64 * b, smem_desc_sw128(q_addr + k * 32), smem_desc_sw128(k_addr + k * 32), idesc,
+                              k > 0 ? 1u : 0u);
+                umma_commit(&sm.k_empty[s]);
+                umma_commit(&sm.s_full[b]);
+                pt_stamp(trace, 4 * j);
+                if (j >= 1) ok = issue_pv(j - 1);
+            }
+            if (ok) ok = issue_pv(n_pages - 1);
+            if (!ok) {
+                atomicExch(status, 6);
+                sm.failed = 1;
+            }
+        }
+    } else {
+        // softmax: two groups of four warps; group g takes the pages j = g, g + 2, ... of the tile (whose
+        // scores, P and P V use buffer g), thread `row` of a group owns query row `row`; at the end the
+        // second group hands its running maximum, sum and output row to the first, which stores
+        const int quad = warp & 3, grp = (warp - 2) >> 2;
+        const int row = quad * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const int qpos = pos0 + row;
+        const float c_log2 = scale * 1.4426950408889634f;      // scores are exponentiated in base 2
+        float m_run = -INFINITY, l_run = 0.0f, corr_prev = 0.0f;
+        float o[PT_D];
+#pragma unroll
+        for (int d = 0; d < PT_D; ++d) o[d] = 0.0f;
+        const int b = grp;                                      // this group's buffers
+
+        // P V of this group's page i (its use number i >> 1 of buffer b) joins the output row
+        auto take_pv = [&](int i, float corr) -> bool {
+            if (!mbar_wait(&sm.pv_full[b], (uint32_t)((i >> 1) & 1))) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32_nowait(lane_base + 128 + 64 * b, r0);
+            tmem_ld_32x32_nowait(lane_base + 128 + 64 * b + 32, r1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.pv_free[b]);
+#pragma unroll
+            for (int d = 0; d < 32; ++d) {
+                o[d] = fmaf(o[d], corr, __uint_as_float(r0[d]));
+                o[32 + d] = fmaf(o[32 + d], corr, __uint_as_float(r1[d]));
+            }
+            return true;
+        };
+
+        for (int j = grp; j < n_pages; j += 2) {
+            const int key0 = (first_page + j) * PT_K;
+            // this group's page before this one: its P V joins the output row; with it complete, the P it
+            // read may be overwritten (and its 64 registers are free again before the scores take theirs)
+            if (j >= 2) {
+                ok = take_pv(j - 2, corr_prev);
+                if (!ok) break;
+            }
+            ok = mbar_wait(&sm.s_full[b], (uint32_t)((j >> 1) & 1));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the row's 64 scores, in two pieces; the buffer is free for this group's next page right away
+            uint32_t r[2][32];
+            tmem_ld_32x32_nowait(lane_base + 64 * b, r[0]);
+            tmem_ld_32x32_nowait(lane_base + 64 * b + 32, r[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.s_free[b]);
+            if (row == 0) pt_stamp(trace, 4 * j + 2);
+            // columns [lo, hi] of the page are visible to this row (all 64 if the page lies before the tile)
+            const int hi = min(qpos - key0, PT_K - 1);
+            const int lo = window > 0 ? max(qpos - window + 1 - key0, 0) : 0;
+            const bool plain = lo == 0 && hi == PT_K - 1;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float sc = __uint_as_float(r[half][c]);
+                    if (!plain && (32 * half + c < lo || 32 * half + c > hi)) sc = -INFINITY;
+                    r[half][c] = __float_as_uint(sc);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], sc);
+                }
+            // maximum and exponent in units of scale * log2(e) (scale > 0)
+            const float mx = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c_log2);
+            const float base = (mx == -INFINITY) ? 0.0f : mx;          // a row that has seen no key yet
+            const float corr = fast_exp2(m_run - base);
+            m_run = mx;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            unsigned char* prow = reinterpret_cast<unsigned char*>(sm.p[b]) + row * 128;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(r[half][c]), c_log2, -base));      // 0 for a hidden key
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(r[half][c + 1]), c_log2, -base));
+                    sum4[(c >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    r[half][c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                // 16-byte piece c of a row sits at piece (c ^ (row & 7)) of its 128 bytes
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int piece = (4 * half + c) ^ (row & 7);
+                    *reinterpret_cast<uint4*>(prow + 16 * piece) =
+                        make_uint4(r[half][4 * c], r[half][4 * c + 1], r[half][4 * c + 2], r[half][4 * c + 3]);
+                }
+            }
+            l_run = fmaf(l_run, corr, (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the tensor cores read P through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_full[b]);
+            if (row == 0) pt_stamp(trace, 4 * j + 3);
+            corr_prev = corr;
+        }
+        const int my_last = n_pages - 1 - ((n_pages - 1 - grp) & 1);      // this group's last page (< grp: none)
+        if (ok && my_last >= grp) ok = take_pv(my_last, corr_prev);
+        if (!ok && lane == 0) {
+            atomicExch(status, 7);
+            sm.failed = 1;
+        }
+        // With its last P V complete, every product issued before it is complete: all of S (the last S is
+        // issued before the last but one P V), so the tiles of Q and of the keys are free.  The second group
+        // leaves its row there: 64 outputs, maximum, sum.
+        float* hand = reinterpret_cast<float*>(sm.q);                    // [128][66] floats in 40 KB
+        const bool two = n_pages >= 2;
+        if (grp == 1 && two) {
+#pragma unroll
+            for (int d = 0; d < PT_D; ++d) hand[row * 66 + d] = o[d];
+            hand[row * 66 + 64] = m_run;
+            hand[row * 66 + 65] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.x_full[0]);
+        }
+        if (grp == 0) {
+            float w0 = 1.0f, w1 = 0.0f, l1 = 0.0f;
+            if (two && ok) {
+                ok = mbar_wait(&sm.x_full[0], 0);
+                if (ok) {
+                    const float m1 = hand[row * 66 + 64];
+                    l1 = hand[row * 66 + 65];
+                    const float m = fmaxf(m_run, m1);                    // finite for a row that is stored
+                    w0 = fast_exp2(m_run - m);
+                    w1 = fast_exp2(m1 - m);
+                }
+            }
+            if (ok && !sm.failed && row < nq) {
+                const float inv = 1.0f / (l_run * w0 + l1 * w1);
+                __nv_bfloat16* dst = out + (long long)(flat0 + row) * ldo + h * PT_D;
+#pragma unroll
+                for (int d = 0; d < PT_D; d += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = (o[d + e] * w0 + (w1 != 0.0f ? hand[row * 66 + d + e] * w1 : 0.0f)) * inv;
+                    uint4 packed;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+                    packed.x = *reinterpret_cast<uint32_t*>(&h0);
+                    packed.y = *reinterpret_cast<uint32_t*>(&h1);
+                    packed.z = *reinterpret_cast<uint32_t*>(&h2);
+                    packed.w = *reinterpret_cast<uint32_t*>(&h3);
+                    *reinterpret_cast<uint4*>(dst + d) = packed;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace mu
+
+// For measurements: a device buffer of 256 64-bit words for block 0's time stamps (see pt_stamp), or null.
+MU_EXPORT int mu_attention_prefill_tc_trace(void* buffer) {
+    unsigned long long* p = (unsigned long long*)buffer;
+    return cudaMemcpyToSymbol(mu::g_pt_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
+}
+
+// q: bfloat16 rows of n_heads x 64 (ldq elements apart, n_tokens of them); kv: the paged cache of
+// n_cache_pages pages; tiles: int32 [n_tiles][2] = (flat index of the tile's first query token, number of
+// queries <= 128), a tile's queries belonging to one sequence and following one another, longest tiles
+// first (blocks start in this order).  out rows ldo apart, 16-byte aligned.  head_dim 64, pages of 64.
+MU_EXPORT int mu_attention_prefill_tc(const void* q, long long ldq, int n_tokens, void* out, long long ldo,
+                                      const void* kv, long long n_cache_pages, const int* block_table,
+                                      int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
+                                      const int* tiles, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
+                                      float scale, int window, int* status, void* stream) {
+    if (n_tiles <= 0) return MU_OK;
+    if (page_tokens != mu::PT_K || head_dim != mu::PT_D) return MU_ERR_UNSUPPORTED_SIZE;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0 || n_tokens <= 0 || !(scale > 0.0f))
+        return MU_ERR_BAD_ARGUMENT;                  // (the row maximum is taken before the scores are scaled)
+    if (!q || !out || !kv || !block_table || !tok_pos || !tok_seq || !tiles || !status) return MU_ERR_BAD_ARGUMENT;
+    if (ldq % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)kv & 15) || ldo % 8 != 0 || ((uintptr_t)out & 15))
+        return MU_ERR_ALIGNMENT;
+    const long long kv_rows = n_cache_pages * 2 * n_kv_heads * mu::PT_K;
+    const long long items = (long long)n_tiles * n_heads;
+    if (kv_rows > 2147483647ll || items > 2147483647ll) return MU_ERR_UNSUPPORTED_SIZE;
+    CUtensorMap map_q, map_kv;
+    if (!mu::tensor_map_bf16(&map_q, q, n_tokens, n_heads * mu::PT_D, ldq, mu::PT_Q) ||
+        !mu::tensor_map_bf16(&map_kv, kv, kv_rows, mu::PT_D, mu::PT_D, mu::PT_K))
+        return MU_ERR_LAUNCH;
+    auto kernel = mu::attention_prefill_tc_kernel;
+    const size_t smem = sizeof(mu::PtSmem) + 1024;
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return MU_ERR_LAUNCH;
+        raised = true;
+    }
+    return mu::launch_pdl(kernel, dim3((unsigned)items), dim3(mu::PT_THREADS), smem, (cudaStream_t)stream, 1, map_q,
+                          map_kv, (__nv_bfloat16*)out, ldo, block_table, max_pages, tok_pos, tok_seq, tiles, n_heads,
+                          n_kv_heads, scale, window, status);
+}

@@ -20,16 +20,14 @@
 // memory and returns, so a wrong phase shows up as an error and not as a hang.
 //
 // The reference's counterpart is matmulTiled (include/ai/Kernels.hpp:315-430).
-#include "common.cuh"
+#include "tcgen05.cuh"
 
-#include <cuda.h>
 #include <cstdlib>
 #include <mutex>
 
 namespace mu {
 
 constexpr int TC_BM = 128, TC_BK = 64, TC_EPI_WARPS = 8, TC_THREADS = 64 + 32 * TC_EPI_WARPS;
-constexpr unsigned long long TC_WAIT_NS = 2000000000ull;      // a wait gives up after two seconds
 constexpr int TC_PATCH_PITCH = 33;               // floats per row of an epilogue patch: odd, so columns and rows both spread over the banks
 
 // Optional time stamps for measurements (mu_gemm_tc_trace): per block TC_TRACE_WORDS words of
@@ -45,89 +43,6 @@ __device__ __forceinline__ void tc_stamp(unsigned long long* trace, int word) {
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
         trace[(long long)blockIdx.x * TC_TRACE_WORDS + word] = now;
     }
-}
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false if it never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    unsigned long long start = 0;
-    for (unsigned int spin = 0;; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if ((spin & 255u) == 255u) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (start == 0) start = now;
-            else if (now - start > TC_WAIT_NS) return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile with rows of 128 bytes, 128-byte swizzle, groups of
-// 8 rows 1024 bytes apart (bits: address >> 4 at 0, leading offset at 16, stride offset at 32,
-// descriptor version 1 at 46, swizzle mode 2 = 128 B at 61).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-// Instruction descriptor of kind::f16: float32 accumulator (bit 4), bfloat16 A and B (bits 7, 10),
-// both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
-        "%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 template <int BN, int STAGES>
@@ -365,7 +280,7 @@ static EncodeTiledFn encode_tiled() {
 // model asks for the same ones step after step (weights always, activations whenever the allocator hands
 // the same buffer back).
 struct MapKey {
-    const void* base; int rows, cols, box_rows; long long ld;
+    const void* base; long long rows; int cols, box_rows; long long ld;
     bool operator==(const MapKey& o) const {
         return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && ld == o.ld;
     }
@@ -374,9 +289,9 @@ struct MapSlot { MapKey key; CUtensorMap map; bool used; };
 static MapSlot map_cache[512];
 static std::mutex map_mutex;
 
-static bool make_map_uncached(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows);
+static bool make_map_uncached(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows);
 
-static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
+bool tensor_map_bf16(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
     const MapKey key = {base, rows, cols, box_rows, ld};
     const size_t h = ((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)rows * 31 + (size_t)cols * 131 + box_rows;
     MapSlot& slot = map_cache[(h >> 20) & 511];
@@ -388,7 +303,7 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, lon
 }
 
 // A [rows, cols] bfloat16 matrix with `ld` elements between rows, cut into boxes of box_rows x 64.
-static bool make_map_uncached(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
+static bool make_map_uncached(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -417,7 +332,7 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
                      int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int* status,
                      cudaStream_t s) {
     CUtensorMap map_a, map_w;
-    if (!make_map(&map_a, A, M, K, lda, TC_BM) || !make_map(&map_w, W, N, K, ldw, BN)) return MU_ERR_LAUNCH;
+    if (!tensor_map_bf16(&map_a, A, M, K, lda, TC_BM) || !tensor_map_bf16(&map_w, W, N, K, ldw, BN)) return MU_ERR_LAUNCH;
     auto kernel = gemm_tc_kernel<BN, STAGES, TC>;
     const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
     static bool raised = false;

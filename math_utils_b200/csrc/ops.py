@@ -53,6 +53,8 @@ _SIGNATURES = {
     "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
     "mu_attention_prefill": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int,
                              _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p],
+    "mu_attention_prefill_tc": [_c_p, _c_ll, _c_int, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_p, _c_p,
+                                _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p],
     "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
@@ -562,6 +564,34 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv_pages), _ptr(block_table), block_table.shape[1],
         page_tokens, _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles), tiles.shape[0], n_heads, n_kv_heads, head_dim,
         float(scale), int(window), _ptr(counter), _stream()), ("attention_prefill(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
+    return out
+
+
+def prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_tokens: int) -> bool:
+    """Whether the tcgen05 prompt attention takes this case: bfloat16, head size
+    64, pages of 64, query and output rows 16-byte aligned.  MU_B200_PREFILL_TC=0
+    switches it off (the mma.sync kernel then runs)."""
+    if os.environ.get("MU_B200_PREFILL_TC", "1") == "0":
+        return False
+    return (q.dtype == torch.bfloat16 and head_dim == 64 and page_tokens == 64 and q.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)
+
+
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor,
+                         page_tokens: int, tok_pos, tok_seq, tiles: torch.Tensor, n_heads: int, n_kv_heads: int,
+                         head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of prompt tokens on the tcgen05 tensor cores (TMA loads,
+    scores and outputs in tensor memory).  ``tiles`` int32 [n, 2]: first flat
+    query index and query count (<= 128) of each tile, longest tiles first."""
+    _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, tiles)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table"), (tiles, "tiles")):
+        _i32(t, name)
+    _check(library().mu_attention_prefill_tc(
+        _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kv_pages), kv_pages.shape[0],
+        _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles),
+        tiles.shape[0], n_heads, n_kv_heads, head_dim, float(scale), int(window),
+        _ptr(status_word(q.device)), _stream()),
+        ("attention_prefill_tc(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
     return out
 
 

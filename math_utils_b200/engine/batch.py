@@ -77,6 +77,7 @@ class StepContext:
     workspace: dict = field(default_factory=dict)
     split_target_warps: int = 148 * 8
     q_tiles: Optional[torch.Tensor] = None  # [n, 2] int32: (first flat token, count <= 64) of each query tile
+    q_tiles_wide: Optional[torch.Tensor] = None  # the same in tiles of up to 128 queries
 
     @property
     def is_decode(self) -> bool:
@@ -137,17 +138,21 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     n_tokens, n_seqs = sum(q_lens), len(entries)
     n_want = sum(len(e.want) for e in entries)
     tables = [cache.block_table_rows(g.index, [e.slot for e in entries]) for g in cache.kv_groups]
-    tiles = []                            # query tiles of 64 for the prompt attention kernel
-    if max(q_lens) > 1:
-        flat, ends = 0, []
+    def cut(width):
+        """Query tiles of `width` tokens, none across two sequences, those with the most keys first
+        (the attention kernels' blocks take them in this order)."""
+        found, ends, flat = [], [], 0
         for n, start in zip(q_lens, starts):
-            for o in range(0, n, TILE_QUERIES):
-                tiles.append((flat + o, min(TILE_QUERIES, n - o)))
-                ends.append(start + o + tiles[-1][1])
+            for o in range(0, n, width):
+                found.append((flat + o, min(width, n - o)))
+                ends.append(start + o + found[-1][1])
             flat += n
-        # the tiles with the most keys first: the attention kernel's blocks take them in this order
-        tiles = [tiles[i] for i in sorted(range(len(tiles)), key=lambda i: -ends[i])]
-    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * len(tiles)] + [t.size for t in tables]
+        return [found[i] for i in sorted(range(len(found)), key=lambda i: -ends[i])]
+
+    tiles, wide = [], []                  # query tiles for the prompt attention kernels
+    if max(q_lens) > 1:
+        tiles, wide = cut(TILE_QUERIES), cut(2 * TILE_QUERIES)
+    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * len(tiles), 2 * len(wide)] + [t.size for t in tables]
     offsets = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])])   # 16-byte aligned parts
     total = int(offsets[-1])
     host = ring.next(total)
@@ -168,8 +173,9 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     h[offsets[4]: offsets[4] + n_seqs] = np.asarray([e.slot for e in entries], dtype=np.int32)
     if tiles:
         h[offsets[5]: offsets[5] + 2 * len(tiles)] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        h[offsets[6]: offsets[6] + 2 * len(wide)] = np.asarray(wide, dtype=np.int32).reshape(-1)
     for i, t in enumerate(tables):
-        h[offsets[6 + i]: offsets[6 + i] + t.size] = t.reshape(-1)
+        h[offsets[7 + i]: offsets[7 + i] + t.size] = t.reshape(-1)
     dev = torch.empty(total, dtype=torch.int32, device=runtime.device)
     dev.copy_(host[:total], non_blocking=True)
     ring.mark()
@@ -181,9 +187,10 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
         runtime=runtime, position=position, n_tokens=n_tokens, n_seqs=n_seqs,
         token_ids=part(0, n_tokens), tok_pos=part(1, n_tokens), tok_seq=part(2, n_tokens),
         want_rows=part(3, n_want) if n_want else None,
-        block_tables=[part(6 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
+        block_tables=[part(7 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
         seq_slots=part(4, n_seqs),
         q_tiles=part(5, 2 * len(tiles)).view(len(tiles), 2) if tiles else None,
+        q_tiles_wide=part(6, 2 * len(wide)).view(len(wide), 2) if wide else None,
         slots=[e.slot for e in entries], starts=list(starts), q_lens=q_lens,
         max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
         workspace=workspace)

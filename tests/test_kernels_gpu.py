@@ -473,3 +473,53 @@ def test_append_by_tiles_writes_the_same_cache(n_kv_heads, head_dim, dtype):
     want_k = ks[4][128:192].reshape(64, n_kv_heads, head_dim).permute(1, 0, 2)
     want_v = vs[4][128:192].reshape(64, n_kv_heads, head_dim).permute(1, 2, 0)
     assert torch.equal(flat_k, want_k) and torch.equal(flat_v, want_v)
+
+
+@pytest.mark.parametrize("n_heads,n_kv_heads,window", [(12, 12, 0), (4, 2, 0), (6, 2, 100), (3, 1, 64), (2, 2, 1)])
+def test_prompt_attention_on_tcgen05(n_heads, n_kv_heads, window):
+    """The tcgen05 prompt kernel (head size 64): whole prompts and prompts
+    continued from a filled cache, tiles of up to 128 queries that start and end
+    inside pages, several sequences in one launch, grouped heads and windows;
+    in the longest sequence one key far back answers one head's last queries, so
+    a misplaced page or column shows."""
+    from math_utils_b200.csrc import ops
+    head_dim = 64
+    rng = np.random.default_rng(17 * n_heads + window)
+    totals = [1, 64, 65, 200, 333, 1000]
+    starts = [0, 0, 0, 70, 128, 0]                 # tokens the cache already holds
+    kv, table, ks, vs = paged_setup(rng, totals, n_kv_heads, head_dim, "bfloat16")
+    flat_total = sum(n - s for n, s in zip(totals, starts))
+    q_all = dev(rng.standard_normal((flat_total, n_heads * head_dim + 16)), torch.bfloat16)[:, :n_heads * head_dim]
+    # sequence 5, head 1: the key at `far` is six times the last query of the head
+    far = 1000 - window if window and window < 900 else 37
+    off5 = flat_total - 1000
+    g = 1 // (n_heads // n_kv_heads) if n_heads > 1 else 0
+    hq = 1 if n_heads > 1 else 0
+    ks[5][far, g * head_dim:(g + 1) * head_dim] = (6.0 * q_all[off5 + 999, hq * head_dim:(hq + 1) * head_dim].float()).to(torch.bfloat16)
+    all_pos = torch.tensor([p for n in totals for p in range(n)], dtype=torch.int32, device="cuda")
+    all_seq = torch.tensor([s for s, n in enumerate(totals) for _ in range(n)], dtype=torch.int32, device="cuda")
+    ops.kv_append(torch.cat(ks), torch.cat(vs), all_pos, all_seq, table, 64, n_kv_heads, head_dim, kv)
+    tok_pos = torch.tensor([p for n, s in zip(totals, starts) for p in range(s, n)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([i for i, (n, s) in enumerate(zip(totals, starts)) for _ in range(s, n)],
+                           dtype=torch.int32, device="cuda")
+    tiles, flat = [], 0
+    for n, s in zip(totals, starts):
+        for o in range(0, n - s, 128):
+            tiles.append((flat + o, min(128, n - s - o)))
+        flat += n - s
+    tiles.sort(key=lambda t: -t[1])
+    tiles_t = torch.tensor(tiles, dtype=torch.int32, device="cuda")
+    out = torch.full((flat, n_heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / math.sqrt(head_dim)
+    assert ops.prefill_tc_ok(q_all, out, head_dim, 64)
+    ops.attention_prefill_tc(q_all, out, kv, table, 64, tok_pos, tok_seq, tiles_t, n_heads, n_kv_heads, head_dim,
+                             scale, window)
+    ops.check_status()
+    o = 0
+    for i, (n, s) in enumerate(zip(totals, starts)):
+        want = plain_gpt2.causal_attention(q_all[o:o + n - s].double().cpu().numpy(), ks[i].double().cpu().numpy(),
+                                           vs[i].double().cpu().numpy(), n_heads, n_kv_heads, scale, window, start=s)
+        vmax = float(vs[i].abs().max())
+        assert_close(out[o:o + n - s].float().cpu().numpy(), want, "bfloat16", f"sequence {i}",
+                     extra_abs=2.0 ** -8 * vmax)
+        o += n - s

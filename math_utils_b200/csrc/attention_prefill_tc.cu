@@ -366,12 +366,27 @@ MU_EXPORT int mu_attention_prefill_tc_trace(void* buffer) {
 // n_cache_pages pages; tiles: int32 [n_tiles][2] = (flat index of the tile's first query token, number of
 // queries <= 128), a tile's queries belonging to one sequence and following one another, longest tiles
 // first (blocks start in this order).  out rows ldo apart, 16-byte aligned.  head_dim 64, pages of 64.
+// k_new, v_new (optional, both or neither): this step's keys and values, rows ldk / ldv apart, appended to
+// the cache first (mu_kv_append with append_tiles: tiles of up to 64 tokens) - one call for both launches.
+extern "C" int mu_kv_append(const void* k, long long ldk, const void* v, long long ldv, const int* tok_pos,
+                            const int* tok_seq, const int* block_table, int max_pages, int page_tokens,
+                            int n_tokens, int n_kv_heads, int head_dim, void* kv, int is_bf16, const int* tiles,
+                            int n_tiles, void* stream);
+
 MU_EXPORT int mu_attention_prefill_tc(const void* q, long long ldq, int n_tokens, void* out, long long ldo,
-                                      const void* kv, long long n_cache_pages, const int* block_table,
+                                      void* kv, long long n_cache_pages, const int* block_table,
                                       int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
                                       const int* tiles, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
-                                      float scale, int window, int* status, void* stream) {
+                                      float scale, int window, const void* k_new, long long ldk,
+                                      const void* v_new, long long ldv, const int* append_tiles,
+                                      int n_append_tiles, int* status, void* stream) {
     if (n_tiles <= 0) return MU_OK;
+    if ((k_new == nullptr) != (v_new == nullptr)) return MU_ERR_BAD_ARGUMENT;
+    if (k_new) {
+        if (int e = mu_kv_append(k_new, ldk, v_new, ldv, tok_pos, tok_seq, block_table, max_pages, page_tokens,
+                                 n_tokens, n_kv_heads, head_dim, kv, 1, append_tiles, n_append_tiles, stream))
+            return e;
+    }
     if (page_tokens != mu::PT_K || head_dim != mu::PT_D) return MU_ERR_UNSUPPORTED_SIZE;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0 || n_tokens <= 0 || !(scale > 0.0f))
         return MU_ERR_BAD_ARGUMENT;                  // (the row maximum is taken before the scores are scaled)

@@ -401,3 +401,19 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
     return MU_TC(256, 4);
 #undef MU_TC
 }
+
+extern "C" int mu_layernorm(const float* x, const int* rows, const float* gamma, const float* beta, void* y,
+                            int n_rows, int hidden, float eps, int out_bf16, void* stream);
+
+// LayerNorm of float32 rows of x (contiguous, K wide; optionally the rows that `rows` picks) into the
+// bfloat16 buffer `normed` [M, K], then the product of it: two launches from one call, for the prompt
+// step, whose host side would otherwise spend as long on the two calls as the device on the kernels.
+MU_EXPORT int mu_layernorm_gemm_tc(const float* x, const int* rows, const float* gamma, const float* beta,
+                                   float eps, void* normed, const void* W, const float* bias,
+                                   const float* residual, void* C, int M, int N, int K, long long ldw,
+                                   long long ldc, long long ldr, int act, int out_bf16, int* status,
+                                   void* stream) {
+    if (!normed) return MU_ERR_BAD_ARGUMENT;
+    if (int e = mu_layernorm(x, rows, gamma, beta, normed, M, K, eps, 1, stream)) return e;
+    return mu_gemm_tc(normed, W, bias, residual, C, M, N, K, K, ldw, ldc, ldr, act, out_bf16, status, stream);
+}

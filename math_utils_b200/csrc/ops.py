@@ -54,7 +54,10 @@ _SIGNATURES = {
     "mu_attention_prefill": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int,
                              _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p],
     "mu_attention_prefill_tc": [_c_p, _c_ll, _c_int, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_p, _c_p,
-                                _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p],
+                                _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_ll, _c_p, _c_ll,
+                                _c_p, _c_int, _c_p, _c_p],
+    "mu_layernorm_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
+                             _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_p],
     "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
@@ -579,19 +582,78 @@ def prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_tokens
 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor,
                          page_tokens: int, tok_pos, tok_seq, tiles: torch.Tensor, n_heads: int, n_kv_heads: int,
-                         head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+                         head_dim: int, scale: float, window: int = 0, k_new: Optional[torch.Tensor] = None,
+                         v_new: Optional[torch.Tensor] = None, append_tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of prompt tokens on the tcgen05 tensor cores (TMA loads,
     scores and outputs in tensor memory).  ``tiles`` int32 [n, 2]: first flat
-    query index and query count (<= 128) of each tile, longest tiles first."""
-    _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, tiles)
-    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table"), (tiles, "tiles")):
+    query index and query count (<= 128) of each tile, longest tiles first.
+    With ``k_new`` / ``v_new`` the step's keys and values are appended to the
+    cache first, in the same call (``append_tiles``: tiles of <= 64 tokens)."""
+    _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, tiles, k_new, v_new, append_tiles)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table"), (tiles, "tiles"),
+                    (append_tiles, "append_tiles")):
         _i32(t, name)
+    if k_new is not None and (k_new.dtype != kv_pages.dtype or v_new is None or v_new.dtype != kv_pages.dtype
+                              or k_new.stride(1) != 1 or v_new.stride(1) != 1):
+        raise KernelError("keys, values and the cache must share a dtype; unit stride within a row")
     _check(library().mu_attention_prefill_tc(
         _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kv_pages), kv_pages.shape[0],
         _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles),
         tiles.shape[0], n_heads, n_kv_heads, head_dim, float(scale), int(window),
+        _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
+        v_new.stride(0) if v_new is not None else 0, _ptr(append_tiles),
+        append_tiles.shape[0] if append_tiles is not None else 0,
         _ptr(status_word(q.device)), _stream()),
-        ("attention_prefill_tc(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
+        ("attention_prefill_tc(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim),
+        launches=2 if k_new is not None else 1)
+    return out
+
+
+_scratch = {}
+
+
+def scratch(name: str, device, numel: int, dtype) -> torch.Tensor:
+    """A device buffer kept per purpose, device and dtype that only ever grows
+    (a buffer it outgrows is kept alive: a recorded graph may still point at it)."""
+    key = (name, device, dtype)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < numel:
+        if buf is not None:
+            _retired.append(buf)
+        buf = _scratch[key] = torch.empty(max(numel, 1), dtype=dtype, device=device)
+    return buf
+
+
+def _layernorm_gemm_tc(x: "NormedInput", weight, bias, act, residual, out, out_dtype):
+    """The norm and the tensor-core product of it from one call into the library
+    (two launches), for more than 64 rows of bfloat16; None if the case is not its."""
+    m, k = x.n_rows, x.x.shape[1]
+    n = weight.shape[0]
+    if (m <= 64 or x._value is not None or weight.dtype != torch.bfloat16 or x.out_dtype != torch.bfloat16
+            or x.x.dtype != torch.float32 or not x.x.is_contiguous() or weight.dim() != 2 or weight.shape[1] != k
+            or weight.stride(1) != 1 or k % 8 != 0 or weight.stride(0) % 8 != 0 or weight.data_ptr() % 16 != 0):
+        return None
+    if not (x.x.is_cuda and weight.is_cuda and x.gamma.dtype == torch.float32
+            and (x.beta is None or x.beta.dtype == torch.float32)):
+        return None
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or torch.bfloat16, device=weight.device)
+    elif out.shape != (m, n) or out.stride(1) != 1 or not out.is_cuda:
+        raise KernelError("gemm output has the wrong shape, stride or device")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != n or not bias.is_cuda):
+        raise KernelError("gemm bias must be float32 of length n on the device")
+    ldr = 0
+    if residual is not None:
+        if residual.dtype != torch.float32 or residual.shape != (m, n) or residual.stride(1) != 1 or not residual.is_cuda:
+            raise KernelError("gemm residual must be float32 [m, n] on the device")
+        ldr = residual.stride(0)
+    _i32(x.rows, "rows")
+    normed = scratch("layernorm_out", weight.device, m * k, torch.bfloat16)
+    _check(library().mu_layernorm_gemm_tc(
+        x.x.data_ptr(), _ptr(x.rows), x.gamma.data_ptr(), _ptr(x.beta), float(x.eps), normed.data_ptr(),
+        weight.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), m, n, k, weight.stride(0), out.stride(0),
+        ldr, ACT_CODES[act], _is_bf16(out), status_word(weight.device).data_ptr(), _stream()),
+        ("layernorm_gemm_tc({}x{}x{})", m, n, k), launches=2)
     return out
 
 
@@ -616,6 +678,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
                 and x.x.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
             return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
+        fused = _layernorm_gemm_tc(x, weight, bias, act, residual, out, out_dtype)
+        if fused is not None:
+            return fused
         x = x.materialize()
     # One pass over what the kernels need, then straight to the library (this is the call a prompt
     # step makes a hundred times): the shapes must agree here; alignment, strides and sizes that a

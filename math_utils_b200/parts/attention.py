@@ -72,15 +72,17 @@ class CausalSelfAttention(Mixer):
                                  self.n_kv_heads, self.head_dim, self.scale, self.window,
                                  ctx.decode_pages(cache.page_tokens))
         else:
+            if ctx.q_tiles_wide is not None and ops.prefill_tc_ok(q, attn, self.head_dim, cache.page_tokens):
+                # the append and the attention from one call into the library
+                ops.attention_prefill_tc(q, attn, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq,
+                                         ctx.q_tiles_wide, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                         self.window, k_new=k if owns_cache else None,
+                                         v_new=v if owns_cache else None, append_tiles=ctx.q_tiles)
+                self.out(attn, residual=residual, out=residual)
+                return
             if owns_cache:
                 ops.kv_append(k, v, ctx.tok_pos, ctx.tok_seq, table, cache.page_tokens,
                               self.n_kv_heads, self.head_dim, cache.pages, tiles=ctx.q_tiles)
-            if ctx.q_tiles_wide is not None and ops.prefill_tc_ok(q, attn, self.head_dim, cache.page_tokens):
-                ops.attention_prefill_tc(q, attn, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq,
-                                         ctx.q_tiles_wide, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
-                                         self.window)
-                self.out(attn, residual=residual, out=residual)
-                return
             if ctx.q_tiles is not None and ops.prefill_ok(q, self.head_dim, cache.page_tokens):
                 ops.attention_prefill(q, attn, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq,
                                       ctx.q_tiles, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,

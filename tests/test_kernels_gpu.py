@@ -376,10 +376,14 @@ def test_product_with_the_norm_inside(m, n, k, act):
 
 @pytest.mark.parametrize("m,n,k", [(65, 64, 64), (128, 128, 64), (129, 130, 72), (257, 200, 328), (1000, 520, 768),
                                    (2048, 2304, 768), (2048, 768, 3072), (300, 1031, 96), (70, 50257, 64)])
-def test_tensor_core_product(m, n, k):
+@pytest.mark.parametrize("tile", [0, 64, 128, 256])
+def test_tensor_core_product(m, n, k, tile, monkeypatch):
     """The tcgen05 / TMA kernel at ragged sizes: more than one k-block ring turn,
-    edges in m, n and k, both tile widths, every epilogue."""
+    edges in m, n and k, every tile width (0: the kernel's own choice), every
+    epilogue."""
     from math_utils_b200.csrc import ops
+    if tile:
+        monkeypatch.setenv("MU_B200_TC_TILE", str(tile))
     rng = np.random.default_rng(m + n + k)
     a = dev(rng.standard_normal((m, k)), torch.bfloat16)
     w = dev(rng.standard_normal((n, k)) / math.sqrt(k), torch.bfloat16)

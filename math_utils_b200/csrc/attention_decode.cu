@@ -28,7 +28,6 @@
 
 namespace mu {
 
-constexpr int AD_WARPS = 4;
 constexpr int AD_PAGE = 64;
 
 __device__ __forceinline__ float dot_head(const float* qs, const float* krow, int head_dim) {

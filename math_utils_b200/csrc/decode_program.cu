@@ -30,7 +30,7 @@
 namespace mu {
 
 constexpr int DP_THREADS = 256, DP_WARPS = 8;
-constexpr int OP_END = 0, OP_EMBED = 1, OP_GEMM = 2, OP_ATTENTION = 3;
+constexpr int OP_EMBED = 1, OP_GEMM = 2, OP_ATTENTION = 3;
 constexpr int DP_MAX_ROWS = 16;            // activation rows (sequences) a program may carry
 constexpr int DP_PAGE = 64;
 

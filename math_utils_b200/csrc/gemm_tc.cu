@@ -45,6 +45,72 @@ __device__ __forceinline__ void tc_stamp(unsigned long long* trace, int word) {
     }
 }
 
+template <int ACT> __device__ __forceinline__ float tc_act(float x, bool to_bf16) {
+    if (ACT == ACT_GELU_NEW) return to_bf16 ? gelu_new_fast(x) : gelu_new(x);
+    if (ACT == ACT_GELU_ERF) return gelu_erf(x);
+    return x;
+}
+
+// One 32 x 32 block of the accumulator (thread = row, r = its 32 columns) to C, with bias, activation and
+// residual.  tcgen05.ld hands every thread one row; stored like that, a warp's instruction would touch 32
+// rows at once (measured: some 450 cycles per 16-byte store instruction).  So the block is turned in the
+// warp's patch of shared memory and written so that an instruction covers whole runs of a row:
+//   packed (bfloat16, no residual, 16-byte aligned rows): four lanes write a row's 64 bytes, eight rows per
+//     instruction;
+//   otherwise: a lane per column, row after row (128 bytes of float32 per instruction); all of the residual
+//     is asked for before any of it is used (it may be C itself: every element is read and written by the
+//     same lane).
+template <int ACT, typename TC>
+__device__ __forceinline__ void tc_finish_block(const uint32_t (&r)[32], float* patch, int lane,
+                                                const float* __restrict__ bias, const float* bias_lane,
+                                                const float* residual, TC* C, int M, int N, int row0, int nb,
+                                                long long ldc, long long ldr, bool packed) {
+    const int n_rows = min(32, M - row0);
+    __syncwarp();                                                   // the patch's last readers are done
+#pragma unroll
+    for (int i = 0; i < 32; ++i) patch[lane * TC_PATCH_PITCH + i] = __uint_as_float(r[i]);
+    __syncwarp();
+    if (packed) {
+        // four lanes write a row's 64 bytes, eight rows per instruction; a lane's eight columns are the same
+        // in every row, so their bias (bias_lane[0..7]) was fetched long before
+        __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row0 * ldc + nb;
+        const int part = lane & 3;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int row = 8 * it + (lane >> 2);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = tc_act<ACT>(patch[row * TC_PATCH_PITCH + 8 * part + e] + bias_lane[e], true);
+            uint4 piece;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+            piece.x = *reinterpret_cast<uint32_t*>(&h0);
+            piece.y = *reinterpret_cast<uint32_t*>(&h1);
+            piece.z = *reinterpret_cast<uint32_t*>(&h2);
+            piece.w = *reinterpret_cast<uint32_t*>(&h3);
+            if (row < n_rows) *reinterpret_cast<uint4*>(cb + (long long)row * ldc + 8 * part) = piece;
+        }
+        return;
+    }
+    const int n = nb + lane;
+    const bool live = n < N;
+    const float bv = bias_lane[0];
+    TC* cc = C + (long long)row0 * ldc + n;
+    const float* rr = (residual && live) ? residual + (long long)row0 * ldr + n : nullptr;
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = (rr && i < n_rows) ? rr[(long long)i * ldr] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] += tc_act<ACT>(patch[i * TC_PATCH_PITCH + lane] + bv, sizeof(TC) == 2);
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < n_rows) cc[(long long)i * ldc] = from_float<TC>(x[i]);
+    }
+}
+
 template <int BN, int STAGES>
 struct TcSmem {
     __nv_bfloat16 a[STAGES][TC_BM * TC_BK];      // each tile 1024-byte aligned: 128 x 128 B
@@ -54,7 +120,8 @@ struct TcSmem {
     uint64_t acc_full[2];                        // an accumulator is complete (tensor cores -> epilogue)
     uint64_t acc_empty[2];                       // an accumulator has been read out (epilogue -> tensor cores)
     uint32_t tmem_base;
-    float patch[TC_EPI_WARPS][32 * TC_PATCH_PITCH];   // where each epilogue warp turns a 32 x 32 block
+    alignas(16) float patch[TC_EPI_WARPS][32 * TC_PATCH_PITCH + 8];   // where each epilogue warp turns a 32 x 32 block
+                                                     // (a multiple of 16 bytes each: packed rows go in 16-byte pieces)
 };
 
 // Persistent: a block per SM walks over the tiles of C (tile = block, block + grid, ...); the ring of
@@ -163,18 +230,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         constexpr int COLS = BN / (TC_EPI_WARPS / 4);
         float* patch = sm.patch[warp - 2];
         constexpr int CHUNKS = COLS / 32;
-        const bool vec_ok = sizeof(TC) == 2 && ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) && !residual;
+        const bool vec_ok = sizeof(TC) == 2 && ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) && !residual &&
+                            (((uintptr_t)bias) % 16 == 0);
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
             const int row0 = m0 + quad * 32;
             // float32 path: the bias of this lane's columns, fetched while the tensor cores are still at work
-            float bias_col[CHUNKS];
+            // lane-per-column path: one value per block; packed path: the lane's eight columns of every block
+            float bias_col[CHUNKS][8];
 #pragma unroll
             for (int q = 0; q < CHUNKS; ++q) {
-                const int n = n0 + half * COLS + 32 * q + lane;
-                bias_col[q] = (bias && !vec_ok && n < N) ? bias[n] : 0.0f;
+                const int nq = n0 + half * COLS + 32 * q;
+                if (vec_ok && nq + 32 <= N) {
+                    const float4* b4 = reinterpret_cast<const float4*>(bias + nq + 8 * (lane & 3));
+                    const float4 lo = bias ? b4[0] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    const float4 hi = bias ? b4[1] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    bias_col[q][0] = lo.x; bias_col[q][1] = lo.y; bias_col[q][2] = lo.z; bias_col[q][3] = lo.w;
+                    bias_col[q][4] = hi.x; bias_col[q][5] = hi.y; bias_col[q][6] = hi.z; bias_col[q][7] = hi.w;
+                } else {
+                    bias_col[q][0] = (bias && nq + lane < N) ? bias[nq + lane] : 0.0f;
+                }
             }
             ok = mbar_wait(&sm.acc_full[buf], (uint32_t)((local >> 1) & 1));
             if (!ok) {
@@ -195,58 +272,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 const int nb = n0 + c0;
                 if (row0 >= M || nb >= N) continue;                   // the same for the whole warp
-                if (vec_ok && nb + 32 <= N) {
-                    // bfloat16 without a residual: every thread packs its row of the block and stores it in
-                    // 16-byte pieces (measured faster here than turning the block for row-wise stores)
-                    if (row0 + lane < M) {
-                        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(C) + (long long)(row0 + lane) * ldc + nb;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            float v[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                v[e] = apply_act_bf16(__uint_as_float(r[i + e]) + (bias ? bias[nb + i + e] : 0.0f), act);
-                            uint4 packed;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
-                            packed.x = *reinterpret_cast<uint32_t*>(&h0);
-                            packed.y = *reinterpret_cast<uint32_t*>(&h1);
-                            packed.z = *reinterpret_cast<uint32_t*>(&h2);
-                            packed.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(crow + i) = packed;
-                        }
-                    }
-                    continue;
-                }
-                // otherwise the block is turned in the warp's patch of shared memory and handled a row per
-                // instruction, a lane per column: whole 128-byte runs of float32.  All of the residual is
-                // asked for before any of it is used (it may be C itself: every element is read and written
-                // by the same lane).
-                __syncwarp();                                         // the patch's last readers are done
-#pragma unroll
-                for (int i = 0; i < 32; ++i) patch[lane * TC_PATCH_PITCH + i] = __uint_as_float(r[i]);
-                __syncwarp();
-                const int n_rows = min(32, M - row0);
-                const int n = nb + lane;
-                const bool live = n < N;
-                const float bv = vec_ok ? ((bias && live) ? bias[n] : 0.0f) : bias_col[q];
-                TC* cc = C + (long long)row0 * ldc + n;
-                const float* rr = (residual && live) ? residual + (long long)row0 * ldr + n : nullptr;
-                float x[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) x[i] = (rr && i < n_rows) ? rr[(long long)i * ldr] : 0.0f;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float y = patch[i * TC_PATCH_PITCH + lane] + bv;
-                    x[i] += sizeof(TC) == 2 ? apply_act_bf16(y, act) : apply_act(y, act);
-                }
-                if (live) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (i < n_rows) cc[(long long)i * ldc] = from_float<TC>(x[i]);
-                }
+                // the activation is the same for the whole launch: chosen here, outside the loops over the
+                // elements (inside them the compiler evaluated every activation for every element)
+                if (act == ACT_GELU_NEW)
+                    tc_finish_block<ACT_GELU_NEW, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N,
+                                                      row0, nb, ldc, ldr, vec_ok && nb + 32 <= N);
+                else if (act == ACT_GELU_ERF)
+                    tc_finish_block<ACT_GELU_ERF, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N,
+                                                      row0, nb, ldc, ldr, vec_ok && nb + 32 <= N);
+                else
+                    tc_finish_block<0, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N, row0, nb,
+                                           ldc, ldr, vec_ok && nb + 32 <= N);
             }
             if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 5);
         }

@@ -270,7 +270,6 @@ attention_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
 
 // One query token per sequence.  n_splits: warps per block, each taking every n_splits-th page of
 // its sequence (1, 2, 4, 8 or 16; more pages than warps are folded by the warps in turn).
-// part_o, part_ml and tickets are not used (the merge happens in shared memory) and may be null.
 // tok_seq may be null when token t belongs to sequence t.  k_new / v_new: this step's keys and
 // values ([n_tokens, n_kv_heads * head_dim] views) to be appended, or null if the cache holds them
 // already.  The cache must have pages of 64 positions.
@@ -279,8 +278,7 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
                                   const int* block_table, int max_pages, int page_tokens,
                                   const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads,
                                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
-                                  float* part_o, float* part_ml, int* tickets, int is_bf16, void* stream) {
-    (void)part_o; (void)part_ml; (void)tickets;
+                                  int is_bf16, void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (page_tokens != mu::AD_PAGE) return MU_ERR_UNSUPPORTED_SIZE;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;

@@ -62,8 +62,7 @@ _SIGNATURES = {
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
     "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
-                            _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p,
-                            _c_int, _c_p],
+                            _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p],
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                                _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p,
                                _c_p],
@@ -505,13 +504,11 @@ def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv
 def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
                      out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, page_tokens: int,
                      tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                     window: int, n_splits: int, part_o: Optional[torch.Tensor] = None,
-                     part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     window: int, n_splits: int) -> torch.Tensor:
     """Single-token attention, one launch: appends ``k_new`` / ``v_new`` (if
     given), attends page by page, merges in shared memory.  ``n_splits``: how
     many warps share a sequence's pages (its page count is a good choice; at most
-    16 are used).  ``tok_seq`` None: token t is sequence t.  The scratch
-    arguments are accepted for older callers and ignored."""
+    16 are used).  ``tok_seq`` None: token t is sequence t."""
     if _recorder is not None:
         _recorder.add_attention(q, k_new, v_new, out, kv_pages, block_table, page_tokens, tok_pos, tok_seq,
                                 n_heads, n_kv_heads, head_dim, scale, window)
@@ -540,8 +537,7 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
         v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
         _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
-        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), None, None, None,
-        _is_bf16(kv_pages), _stream()),
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), _is_bf16(kv_pages), _stream()),
         ("attention_decode(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
     return out
 

@@ -83,12 +83,14 @@ class StepContext:
     def is_decode(self) -> bool:
         return self.max_q_len == 1
 
-    def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+    def buffer(self, name: str, shape, dtype, columns=None):
         """An activation buffer of this shape that lives from step to step and is
         shared by every layer that asks under the same name: layers run one after
         another on one stream, so a layer's intermediate results are dead when the
-        next layer writes them.  Only the last shape asked for is kept."""
-        key = ("buffer", name, dtype)
+        next layer writes them.  Only the last shape asked for is kept.  With
+        ``columns`` (widths that add up to the row) the buffer comes with its
+        column blocks as views, made once: ``(buffer, block, block, ...)``."""
+        key = ("buffer", name, dtype, columns)
         held = self.workspace.get(key)
         if held is not None and held[0] == shape:
             return held[1]
@@ -96,6 +98,11 @@ class StepContext:
         for n in shape:
             numel *= n
         view = self.scratch(name, numel, dtype)[:numel].view(shape)
+        if columns is not None:
+            edges = [0]
+            for w in columns:
+                edges.append(edges[-1] + w)
+            view = (view,) + tuple(view[:, a:b] for a, b in zip(edges, edges[1:]))
         self.workspace[key] = (shape, view)
         return view
 

@@ -57,11 +57,9 @@ class CausalSelfAttention(Mixer):
 
     def forward(self, h, residual, ctx, cache, owns_cache: bool) -> None:
         ops = self.runtime.ops
-        qkv = self.qkv(h, out=ctx.buffer("attention.qkv", (ctx.n_tokens, self.q_width + 2 * self.kv_width),
-                                         self.runtime.dtype))
-        q = qkv[:, :self.q_width]
-        k = qkv[:, self.q_width:self.q_width + self.kv_width]
-        v = qkv[:, self.q_width + self.kv_width:]
+        qkv, q, k, v = ctx.buffer("attention.qkv", (ctx.n_tokens, self.q_width + 2 * self.kv_width),
+                                  self.runtime.dtype, columns=(self.q_width, self.kv_width, self.kv_width))
+        self.qkv(h, out=qkv)
         ctx.position.rotate(q, k, ctx)
         table = ctx.block_tables[cache.group]
         attn = ctx.buffer("attention.out", (ctx.n_tokens, self.q_width), qkv.dtype)

@@ -111,10 +111,12 @@ __device__ __forceinline__ void tc_finish_block(const uint32_t (&r)[32], float* 
     }
 }
 
-template <int BN, int STAGES>
+// KSUB: 64-deep sub-tiles per stage (a stage is 64 * KSUB deep: with two, the issuing thread waits and
+// commits half as often, which pays where the products are narrow and issuing them sets the pace).
+template <int BN, int STAGES, int KSUB>
 struct TcSmem {
-    __nv_bfloat16 a[STAGES][TC_BM * TC_BK];      // each tile 1024-byte aligned: 128 x 128 B
-    __nv_bfloat16 b[STAGES][BN * TC_BK];
+    __nv_bfloat16 a[STAGES][KSUB][TC_BM * TC_BK];      // each sub-tile 1024-byte aligned: rows of 128 bytes
+    __nv_bfloat16 b[STAGES][KSUB][BN * TC_BK];
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];                        // an accumulator is complete (tensor cores -> epilogue)
@@ -127,19 +129,19 @@ struct TcSmem {
 // Persistent: a block per SM walks over the tiles of C (tile = block, block + grid, ...); the ring of
 // shared-memory stages runs on across tiles, and two accumulators in tensor memory take turns, so the
 // read-out and the stores of one tile overlap the products of the next.
-template <int BN, int STAGES, typename TC>
+template <int BN, int STAGES, int KSUB, typename TC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
                long long ldc, long long ldr, int act, int* status) {
     extern __shared__ unsigned char tc_raw[];
-    TcSmem<BN, STAGES>& sm =
-        *reinterpret_cast<TcSmem<BN, STAGES>*>(((uintptr_t)tc_raw + 1023) & ~(uintptr_t)1023);
+    TcSmem<BN, STAGES, KSUB>& sm =
+        *reinterpret_cast<TcSmem<BN, STAGES, KSUB>*>(((uintptr_t)tc_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int num_kb = (K + KSUB * TC_BK - 1) / (KSUB * TC_BK);          // a sub-tile past K is zero-filled
     const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
     const int tiles = m_tiles * n_tiles;
-    constexpr uint32_t STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16);
+    constexpr uint32_t STAGE_BYTES = KSUB * (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16);
     constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     bool ok = true;
 
@@ -176,8 +178,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbar_wait(&sm.empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1));   // passes at once the first time round
                     if (!ok) break;
                     mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-                    tma_load_2d(sm.a[s], &map_a, kb * TC_BK, m0, &sm.full[s]);
-                    tma_load_2d(sm.b[s], &map_w, kb * TC_BK, n0, &sm.full[s]);
+#pragma unroll
+                    for (int u = 0; u < KSUB; ++u) {
+                        tma_load_2d(sm.a[s][u], &map_a, (kb * KSUB + u) * TC_BK, m0, &sm.full[s]);
+                        tma_load_2d(sm.b[s][u], &map_w, (kb * KSUB + u) * TC_BK, n0, &sm.full[s]);
+                    }
                     issued = it + 1;
                     if (local < TC_TRACE_TILES && (kb == 0 || kb == num_kb - 1)) tc_stamp(trace, 2 + 6 * local + (kb == 0 ? 0 : 1));
                 }
@@ -206,12 +211,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (!ok) break;
                     if (kb == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k) {
-                        // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
-                        umma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int u = 0; u < KSUB; ++u) {
+                        const uint32_t a_addr = smem_u32(sm.a[s][u]), b_addr = smem_u32(sm.b[s][u]);
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k) {
+                            // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
+                            umma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                      (kb > 0 || u > 0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(&sm.empty[s]);            // the stage is free once these have read it
                 }
@@ -368,14 +376,14 @@ static int sm_count() {
     return sms;
 }
 
-template <int BN, int STAGES, typename TC>
+template <int BN, int STAGES, int KSUB, typename TC>
 static int launch_tc(const void* A, const void* W, const float* bias, const float* residual, TC* C, int M, int N,
                      int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int* status,
                      cudaStream_t s) {
     CUtensorMap map_a, map_w;
     if (!tensor_map_bf16(&map_a, A, M, K, lda, TC_BM) || !tensor_map_bf16(&map_w, W, N, K, ldw, BN)) return MU_ERR_LAUNCH;
-    auto kernel = gemm_tc_kernel<BN, STAGES, TC>;
-    const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
+    auto kernel = gemm_tc_kernel<BN, STAGES, KSUB, TC>;
+    const size_t smem = sizeof(TcSmem<BN, STAGES, KSUB>) + 1024;
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -428,18 +436,20 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
         const double score = (double)tiles / (double)(rounds * sms) * worth[i];
         if (score > best) { best = score; best_bn = widths[i]; }
     }
-#define MU_TC(BN, ST)                                                                                           \
-    (out_bf16 ? mu::launch_tc<BN, ST, __nv_bfloat16>(A, W, bias, residual, (__nv_bfloat16*)C, M, N, K, lda, ldw, \
-                                                     ldc, ldr, act, status, s)                                  \
-              : mu::launch_tc<BN, ST, float>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc, ldr, act,  \
-                                             status, s))
+#define MU_TC(BN, ST, KS)                                                                                       \
+    (out_bf16 ? mu::launch_tc<BN, ST, KS, __nv_bfloat16>(A, W, bias, residual, (__nv_bfloat16*)C, M, N, K, lda,  \
+                                                         ldw, ldc, ldr, act, status, s)                         \
+              : mu::launch_tc<BN, ST, KS, float>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc, ldr,   \
+                                                 act, status, s))
     if (const char* forced = getenv("MU_B200_TC_TILE")) {       // for measurements: 64, 128 or 256
         const int f = atoi(forced);
         if (f == 64 || f == 128 || f == 256) best_bn = f;
     }
-    if (best_bn == 64) return MU_TC(64, 6);
-    if (best_bn == 128) return MU_TC(128, 5);
-    return MU_TC(256, 4);
+    // narrow tiles: 128-deep stages (issuing, not multiplying, sets their pace); K of a single 64 keeps 64
+    static const bool deep = !(getenv("MU_B200_TC_DEEP") && atoi(getenv("MU_B200_TC_DEEP")) == 0);
+    if (best_bn == 64) return (deep && K > 64) ? MU_TC(64, 4, 2) : MU_TC(64, 6, 1);
+    if (best_bn == 128) return (deep && K > 64) ? MU_TC(128, 3, 2) : MU_TC(128, 5, 1);
+    return MU_TC(256, 4, 1);
 #undef MU_TC
 }
 

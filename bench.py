@@ -341,8 +341,8 @@ def run_product_trace(args):
 
 
 def run_reference(args):
-    # The reference is a header-only C++ project with a makefile and no Python packaging, so the
-    # offline `pip install --target baseline/_ref /root/reference` has nothing to install.
+    # The reference is a header-only C++ project with a makefile and no Python packaging, so an
+    # offline `pip install --target baseline/_ref` of its checkout has nothing to install.
     print(json.dumps({"impl": "reference",
                       "unavailable": "hday200202/math-utils is a C++ header library without setup.py or "
                                      "pyproject.toml: pip cannot install it offline, and it has no CUDA path"}),

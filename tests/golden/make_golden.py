@@ -126,7 +126,9 @@ def run_local_model(folder, ids, vocab):
 
 
 if __name__ == "__main__":
-    REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py PATH_TO_A_CHECKOUT_OF_hday200202/math-utils")
+    REFERENCE = sys.argv[1]
     with_cpp = os.path.exists(os.path.join(HERE, "local_model_probe.cpp"))
     for k, (name, cfg) in enumerate(GOLDEN_CONFIGS.items()):
         weights = make_weights(cfg, seed=1234 + k)
@@ -145,4 +147,4 @@ if __name__ == "__main__":
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
         print(name, {k2: v.shape for k2, v in arrays.items()})
 else:
-    REFERENCE = "/root/reference"
+    REFERENCE = os.environ.get("MATH_UTILS_REFERENCE", "")      # only needed to regenerate the files

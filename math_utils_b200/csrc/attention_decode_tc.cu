@@ -25,10 +25,10 @@
 // attention_decode.cu.  Softmax in float32; probabilities rounded to bfloat16
 // for the second product, as in the prompt kernel.
 //
-// Formulas: include/ai/Kernels.hpp:132-161.  Head sizes 32 and 64 (a page's
+// Formulas: include/ai/Kernels.hpp:132-161.  Head sizes 32 and 64 here (a page's
 // fragments of both operands stay in registers, which larger heads would not
-// allow; those go to the CUDA-core kernel); up to 16 query heads per kv head;
-// pages of 64 positions.
+// allow) and 32, 64, 96, 128 in the variant below that stages pages in shared
+// memory; up to 16 query heads per kv head; pages of 64 positions.
 #include "common.cuh"
 
 #include <math.h>
@@ -598,7 +598,8 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
                                      int ring, int* status, void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (page_tokens != mu::TD_PAGE) return MU_ERR_UNSUPPORTED_SIZE;
-    if (head_dim != 32 && head_dim != 64) return MU_ERR_UNSUPPORTED_SIZE;
+    // staged in shared memory: head sizes 32, 64, 96, 128; straight into registers: 32 and 64
+    if (head_dim != 32 && head_dim != 64 && !(ring && (head_dim == 96 || head_dim == 128))) return MU_ERR_UNSUPPORTED_SIZE;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0) return MU_ERR_BAD_ARGUMENT;
     if (n_heads / n_kv_heads > 16) return MU_ERR_UNSUPPORTED_SIZE;
     if (!q || !out || !kv || !block_table || !tok_pos) return MU_ERR_BAD_ARGUMENT;
@@ -635,7 +636,9 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
                            (size_t)6 * rows * (head_dim + 1) * sizeof(float);
         const bool wide = n_warps >= 6 && six <= 200 * 1024;
         if (head_dim == 32) { if (wide) MU_TR(2, 6); else MU_TR(2, 2); }
-        else { if (wide) MU_TR(4, 6); else MU_TR(4, 2); }
+        else if (head_dim == 64) { if (wide) MU_TR(4, 6); else MU_TR(4, 2); }
+        else if (head_dim == 96) MU_TR(6, 2);
+        else MU_TR(8, 2);
 #undef MU_TR
         return rc;
     }

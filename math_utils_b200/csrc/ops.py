@@ -487,11 +487,12 @@ def _sm_count(device) -> int:
 def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv_heads: int,
                  head_dim: int) -> bool:
     """Whether the tensor-core single-token attention takes this case (else the
-    CUDA-core kernel does): bfloat16, head sizes 32 and 64, at most 16 query
+    CUDA-core kernel does): bfloat16, head sizes 32, 64, 96 and 128 (96 and 128 only staged in shared memory), at most 16 query
     heads per kv head, 16-byte aligned rows.  MU_B200_ATT_TC=0 switches it off."""
     if os.environ.get("MU_B200_ATT_TC", "1") == "0":
         return False
-    if kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim not in (32, 64):
+    staged = os.environ.get("MU_B200_ATT_RING", "1") != "0"
+    if kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim not in ((32, 64, 96, 128) if staged else (32, 64)):
         return False
     if n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 16:
         return False

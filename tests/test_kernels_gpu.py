@@ -298,7 +298,8 @@ def test_single_token_attention_kernel(n_heads, n_kv_heads, head_dim, window, dt
 
 @pytest.mark.parametrize("staged,warps", [(0, 1), (0, 2), (0, 8), (1, 2), (1, 6)])
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
-    (5, 5, 64, 0), (16, 1, 64, 0), (12, 4, 32, 0), (9, 3, 64, 100), (6, 3, 32, 64), (22, 2, 64, 0), (34, 2, 32, 0)])
+    (5, 5, 64, 0), (16, 1, 64, 0), (12, 4, 32, 0), (9, 3, 64, 100), (6, 3, 32, 64), (22, 2, 64, 0), (34, 2, 32, 0),
+    (4, 2, 128, 0), (6, 1, 96, 70), (3, 3, 128, 200)])
 def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window, staged, warps, monkeypatch):
     """The tensor-core kernels of single-token steps (pages straight into
     registers, or staged in shared memory by bulk copies) at every number of
@@ -327,7 +328,8 @@ def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, w
     k_new = torch.stack([k[-1] for k in ks]).contiguous()
     v_new = torch.stack([v[-1] for v in vs]).contiguous()
     pos1 = torch.tensor([n - 1 for n in seq_lens], dtype=torch.int32, device="cuda")
-    assert ops.decode_tc_ok(q, k_new, v_new, kv, 64, n_heads, n_kv_heads, head_dim) == (n_heads // n_kv_heads <= 16)
+    assert ops.decode_tc_ok(q, k_new, v_new, kv, 64, n_heads, n_kv_heads, head_dim) == (
+        n_heads // n_kv_heads <= 16 and (head_dim <= 64 or staged == 1))    # the larger heads only staged
     want = np.stack([plain_gpt2.causal_attention(
         np.repeat(q[s:s + 1].double().cpu().numpy(), n, axis=0), ks[s].double().cpu().numpy(),
         vs[s].double().cpu().numpy(), n_heads, n_kv_heads, scale, window)[-1] for s, n in enumerate(seq_lens)])

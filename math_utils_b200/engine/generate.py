@@ -157,9 +157,11 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
             positions = [cache.length(slots[k]) for k in members]
             parked = set()
             dirty = True
+            page = cache.page_tokens
             while live and (len(live) * 2 > len(members) or len(members) == 1):
                 for k in live:
-                    dirty |= cache.reserve_one(slots[k])
+                    if positions[place[k]] % page == 0:     # the token of this step opens a page
+                        dirty |= cache.reserve_one(slots[k])
                 if dirty:
                     session.sync_block_tables()
                     dirty = False

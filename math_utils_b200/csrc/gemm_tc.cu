@@ -268,16 +268,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 4);
-            // the next block's load from tensor memory is under way while this block is finished
+            // (asking for the next block before this one is finished measured slower)
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + half * COLS);
-            uint32_t rr[2][32];
-            tmem_ld_32x32_nowait(acc_addr, rr[0]);
 #pragma unroll
             for (int q = 0; q < CHUNKS; ++q) {
                 const int c0 = half * COLS + 32 * q;
-                uint32_t (&r)[32] = rr[q & 1];
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (q + 1 < CHUNKS) tmem_ld_32x32_nowait(acc_addr + 32 * (q + 1), rr[(q + 1) & 1]);
+                uint32_t r[32];
+                tmem_ld_32x32(acc_addr + 32 * q, r);
                 if (q == CHUNKS - 1) {
                     // this warp has read all it needs of the accumulator: the tensor cores may have it back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

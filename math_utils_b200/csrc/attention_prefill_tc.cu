@@ -85,6 +85,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr uint32_t PAGE_BYTES = PT_K * PT_D * sizeof(__nv_bfloat16);
 
     if (threadIdx.x == 0) {
+        tma_prefetch_map(&map_q);
+        tma_prefetch_map(&map_kv);
         mbar_init(&sm.q_full, 1);
         // (a stage is declared free by the four softmax warps that have seen the product that read it complete:
         // an arrival of theirs is cheaper than another commit of the issuing thread)

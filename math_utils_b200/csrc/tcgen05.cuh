@@ -70,6 +70,11 @@ __device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity) {
     }
 }
 
+// Asks for a tensor map (a kernel parameter) ahead of its first use by a copy.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

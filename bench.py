@@ -62,7 +62,7 @@ def peaks():
             with open(path) as f:
                 p = json.load(f)
             return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
-        except (OSError, KeyError, ValueError):
+        except (OSError, KeyError, ValueError, TypeError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
 

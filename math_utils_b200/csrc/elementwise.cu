@@ -196,3 +196,12 @@ MU_EXPORT int mu_set_pdl(int enabled) {
     mu::pdl_enabled() = enabled ? 1 : 0;
     return MU_OK;
 }
+
+// A plain asynchronous copy on the stream (either direction; host memory should be pinned).  For copies
+// that are recorded into a CUDA graph together with the kernels.
+MU_EXPORT int mu_copy_async(void* dst, const void* src, long long n_bytes, void* stream) {
+    if (n_bytes <= 0) return MU_OK;
+    if (!dst || !src) return MU_ERR_BAD_ARGUMENT;
+    return cudaMemcpyAsync(dst, src, (size_t)n_bytes, cudaMemcpyDefault, (cudaStream_t)stream) == cudaSuccess
+               ? MU_OK : MU_ERR_LAUNCH;
+}

@@ -37,6 +37,7 @@ _lock = threading.Lock()
 _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
 
 _SIGNATURES = {
+    "mu_copy_async": [_c_p, _c_p, _c_ll, _c_p],
     "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p],
     "mu_layernorm": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p],
     "mu_gemm_simt": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
@@ -161,6 +162,19 @@ def set_pdl(enabled: bool) -> None:
     kernel of the step writes, while the kernel before it ends.  Launches
     already recorded in a CUDA graph keep the mode they were recorded with."""
     library().mu_set_pdl(1 if enabled else 0)
+
+
+def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst <- src (same size and dtype, contiguous; host tensors pinned) as a
+    plain asynchronous copy on the current stream.  For copies recorded into a
+    CUDA graph: the caller keeps both tensors alive as long as the graph."""
+    if dst.dtype != src.dtype or dst.numel() != src.numel() or not dst.is_contiguous() or not src.is_contiguous():
+        raise KernelError("copy_async needs contiguous tensors of one dtype and size")
+    for t in (dst, src):
+        if not t.is_cuda and not t.is_pinned():
+            raise KernelError("copy_async needs pinned host memory")
+    _check(library().mu_copy_async(dst.data_ptr(), src.data_ptr(), dst.numel() * dst.element_size(), _stream()),
+           "copy_async", launches=0)
 
 
 _workspaces = {}

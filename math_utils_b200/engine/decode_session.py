@@ -28,8 +28,15 @@ from .batch import StepContext
 
 class DecodeSession:
     def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
-                 request_ids: Sequence[int], kv_bound: Optional[int] = None, use_program: Optional[bool] = None):
+                 request_ids: Sequence[int], kv_bound: Optional[int] = None, use_program: Optional[bool] = None,
+                 copies_in_graph: bool = False):
+        """``copies_in_graph``: the recorded graph starts with the copy of the fed
+        tokens and positions from pinned memory and ends with the copy of the
+        sampled tokens to pinned memory, so a step of the generation loop is one
+        launch instead of three.  Without it a launch leaves the inputs alone,
+        and each step's samples feed the next on the device."""
         self.model, self.cache = model, cache
+        self.copies_in_graph = copies_in_graph
         self.slots = list(slots)
         self.n = len(self.slots)
         self.params = params
@@ -65,6 +72,7 @@ class DecodeSession:
             q_lens=[1] * n, max_q_len=1, max_kv_len=self.kv_bound, workspace={})
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._feed_views = None
+        self._replayed = False
         self._stream = None
         self.program = None
         # One persistent kernel for the whole step instead of a graph of ~60 launches.  Measured on
@@ -115,7 +123,8 @@ class DecodeSession:
         tok_view, pos_view, dev_part, host_part, n_bytes = self._feed_views
         tok_view[:] = tokens
         pos_view[:] = positions
-        dev_part.copy_(host_part, non_blocking=True)
+        if not (self.copies_in_graph and self.graph is not None):
+            dev_part.copy_(host_part, non_blocking=True)       # else the graph's first node does it
         self._fed = True
         return n_bytes
 
@@ -171,7 +180,14 @@ class DecodeSession:
         before = ops.launch_count
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
+            # (the library's own copy: a torch copy from or to pinned memory would leave the host allocator
+            # with an event recorded during a capture)
+            if self.copies_in_graph:
+                _, _, dev_part, host_part, _ = self._feed_views
+                ops.copy_async(dev_part, host_part)
             self._run_once()
+            if self.copies_in_graph:
+                ops.copy_async(self.next_host, self.next_tokens)
         self.launches_per_step = ops.launch_count - before
         self.graph = graph
         self.token_ids.copy_(saved[0]); self.tok_pos.copy_(saved[1]); self.draws.copy_(saved[2])
@@ -180,11 +196,13 @@ class DecodeSession:
         if self.graph is None:
             self.capture()
         self.graph.replay()
+        self._replayed = True
         self.model.runtime.ops.launch_count += self.launches_per_step
 
     def read_tokens(self) -> List[int]:
         """The tokens the last launched step sampled (waits for it)."""
-        self.next_host.copy_(self.next_tokens, non_blocking=True)
+        if not (self.copies_in_graph and self._replayed):
+            self.next_host.copy_(self.next_tokens, non_blocking=True)
         if self._stream is None:
             self._stream = torch.cuda.current_stream()
         self._stream.synchronize()
@@ -194,14 +212,15 @@ class DecodeSession:
 _SESSIONS_KEPT = 6
 
 
-def session_for(model, cache, params: SamplingParams, n: int) -> DecodeSession:
+def session_for(model, cache, params: SamplingParams, n: int, copies_in_graph: bool = True) -> DecodeSession:
     """A session of ``n`` sequences for this model, cache and sampling rule; the
     last few are kept so that batch after batch replays the same graphs."""
     kept = model.__dict__.setdefault("_decode_sessions", {})
-    key = (id(cache), n, params)
+    key = (id(cache), n, params, copies_in_graph)
     session = kept.pop(key, None)
     if session is None or session.cache is not cache:
-        session = DecodeSession(model, cache, [0] * n, params, [0] * n, kv_bound=model.max_positions)
+        session = DecodeSession(model, cache, [0] * n, params, [0] * n, kv_bound=model.max_positions,
+                                copies_in_graph=copies_in_graph)
     kept[key] = session                                  # most recently used last
     while len(kept) > _SESSIONS_KEPT:
         kept.pop(next(iter(kept)))

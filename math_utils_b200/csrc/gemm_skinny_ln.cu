@@ -1,0 +1,6 @@
+// The few-row product (see gemm_skinny.cuh): bfloat16 output, activations made as a LayerNorm inside the kernel.
+#include "gemm_skinny.cuh"
+
+namespace mu {
+MU_SKINNY_ROWS(__nv_bfloat16, true, 2)
+}  // namespace mu

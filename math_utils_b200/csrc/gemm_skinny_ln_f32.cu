@@ -1,0 +1,6 @@
+// The few-row product (see gemm_skinny.cuh): float32 output, activations made as a LayerNorm inside the kernel.
+#include "gemm_skinny.cuh"
+
+namespace mu {
+MU_SKINNY_ROWS(float, true, 2)
+}  // namespace mu

@@ -1,312 +1,20 @@
-// C[M, N] = act(A[M, K] . W[N, K]^T + bias) (+ residual) on the 5th-generation tensor cores.
-//
-// The product kernel of whole prompts (bfloat16 in, float32 accumulate).  A
-// block per SM walks over the 128 x BN tiles of C; in each block:
-//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
-//            of 128 x 64 tiles of A and BN x 64 tiles of W into a ring of
-//            shared-memory stages and arms each stage's "full" mbarrier;
-//   warp 1   allocates 2 x BN columns of tensor memory (two accumulators that take turns, so
-//            that one tile is read out while the next is being computed); one lane issues
-//            tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per
-//            stage with shared-memory descriptors, the accumulator staying in
-//            tensor memory, and commits each stage back to the producer
-//            ("empty" mbarrier) and at the end the accumulator to the epilogue;
-//   warps 2-9  read the accumulator with tcgen05.ld (each warp 32 rows and half the columns
-//            of the tile), add bias, apply the activation, add the
-//            float32 residual and store bfloat16 or float32.
-// Rows of A and W beyond M, N and K are zero-filled by TMA; the epilogue
-// predicates its stores.  Every wait on an mbarrier is bounded: if it runs out
-// the block records a code in `status`, lets its copies land, frees its tensor
-// memory and returns, so a wrong phase shows up as an error and not as a hang.
-//
-// The reference's counterpart is matmulTiled (include/ai/Kernels.hpp:315-430).
-#include "tcgen05.cuh"
+// Host side of the tensor-core product (the kernel: gemm_tc_kernel.cuh): tensor maps, the choice of the
+// tile width and of a cut along K, and the library's entry points.  The kernels of cut products are
+// compiled in gemm_tc_split.cu.
+#include "gemm_tc_kernel.cuh"
 
-#include <cstdlib>
 #include <mutex>
 
 namespace mu {
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_EPI_WARPS = 8, TC_THREADS = 64 + 32 * TC_EPI_WARPS;
-constexpr int TC_PATCH_PITCH = 33;               // floats per row of an epilogue patch: odd, so columns and rows both spread over the banks
+SplitWorkspace g_split;
 
-// Optional time stamps for measurements (mu_gemm_tc_trace): per block TC_TRACE_WORDS words of
-// %globaltimer: [0] set-up done, [1] the kernel before has ended, then for each of the block's first
-// TC_TRACE_TILES tiles: first and last load issued, first stage arrived, last product issued,
-// accumulator seen complete by the epilogue, epilogue's stores issued.
-constexpr int TC_TRACE_TILES = 4, TC_TRACE_WORDS = 2 + 6 * TC_TRACE_TILES;
-__device__ unsigned long long* g_tc_trace = nullptr;
+// the variants for products cut along K (gemm_tc_split.cu); bn: 64, 128 or 256
+int launch_tc_split(int bn, const void* A, const void* W, const float* bias, const float* residual, void* C, int M,
+                    int N, int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int out_bf16,
+                    int* status, int splits, cudaStream_t s);
+int set_tc_trace_split(unsigned long long* buffer);
 
-__device__ __forceinline__ void tc_stamp(unsigned long long* trace, int word) {
-    if (trace) {
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        trace[(long long)blockIdx.x * TC_TRACE_WORDS + word] = now;
-    }
-}
-
-template <int ACT> __device__ __forceinline__ float tc_act(float x, bool to_bf16) {
-    if (ACT == ACT_GELU_NEW) return to_bf16 ? gelu_new_fast(x) : gelu_new(x);
-    if (ACT == ACT_GELU_ERF) return gelu_erf(x);
-    return x;
-}
-
-// One 32 x 32 block of the accumulator (thread = row, r = its 32 columns) to C, with bias, activation and
-// residual.  tcgen05.ld hands every thread one row; stored like that, a warp's instruction would touch 32
-// rows at once (measured: some 450 cycles per 16-byte store instruction).  So the block is turned in the
-// warp's patch of shared memory and written so that an instruction covers whole runs of a row:
-//   packed (bfloat16, no residual, 16-byte aligned rows): four lanes write a row's 64 bytes, eight rows per
-//     instruction;
-//   otherwise: a lane per column, row after row (128 bytes of float32 per instruction); all of the residual
-//     is asked for before any of it is used (it may be C itself: every element is read and written by the
-//     same lane).
-template <int ACT, typename TC>
-__device__ __forceinline__ void tc_finish_block(const uint32_t (&r)[32], float* patch, int lane,
-                                                const float* __restrict__ bias, const float* bias_lane,
-                                                const float* residual, TC* C, int M, int N, int row0, int nb,
-                                                long long ldc, long long ldr, bool packed) {
-    const int n_rows = min(32, M - row0);
-    __syncwarp();                                                   // the patch's last readers are done
-#pragma unroll
-    for (int i = 0; i < 32; ++i) patch[lane * TC_PATCH_PITCH + i] = __uint_as_float(r[i]);
-    __syncwarp();
-    if (packed) {
-        // four lanes write a row's 64 bytes, eight rows per instruction; a lane's eight columns are the same
-        // in every row, so their bias (bias_lane[0..7]) was fetched long before
-        __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row0 * ldc + nb;
-        const int part = lane & 3;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-            const int row = 8 * it + (lane >> 2);
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = tc_act<ACT>(patch[row * TC_PATCH_PITCH + 8 * part + e] + bias_lane[e], true);
-            uint4 piece;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
-            piece.x = *reinterpret_cast<uint32_t*>(&h0);
-            piece.y = *reinterpret_cast<uint32_t*>(&h1);
-            piece.z = *reinterpret_cast<uint32_t*>(&h2);
-            piece.w = *reinterpret_cast<uint32_t*>(&h3);
-            if (row < n_rows) *reinterpret_cast<uint4*>(cb + (long long)row * ldc + 8 * part) = piece;
-        }
-        return;
-    }
-    const int n = nb + lane;
-    const bool live = n < N;
-    const float bv = bias_lane[0];
-    TC* cc = C + (long long)row0 * ldc + n;
-    const float* rr = (residual && live) ? residual + (long long)row0 * ldr + n : nullptr;
-    float x[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = (rr && i < n_rows) ? rr[(long long)i * ldr] : 0.0f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] += tc_act<ACT>(patch[i * TC_PATCH_PITCH + lane] + bv, sizeof(TC) == 2);
-    if (live) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (i < n_rows) cc[(long long)i * ldc] = from_float<TC>(x[i]);
-    }
-}
-
-// KSUB: 64-deep sub-tiles per stage (a stage is 64 * KSUB deep: with two, the issuing thread waits and
-// commits half as often, which pays where the products are narrow and issuing them sets the pace).
-template <int BN, int STAGES, int KSUB>
-struct TcSmem {
-    __nv_bfloat16 a[STAGES][KSUB][TC_BM * TC_BK];      // each sub-tile 1024-byte aligned: rows of 128 bytes
-    __nv_bfloat16 b[STAGES][KSUB][BN * TC_BK];
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
-    uint64_t acc_full[2];                        // an accumulator is complete (tensor cores -> epilogue)
-    uint64_t acc_empty[2];                       // an accumulator has been read out (epilogue -> tensor cores)
-    uint32_t tmem_base;
-    alignas(16) float patch[TC_EPI_WARPS][32 * TC_PATCH_PITCH + 8];   // where each epilogue warp turns a 32 x 32 block
-                                                     // (a multiple of 16 bytes each: packed rows go in 16-byte pieces)
-};
-
-// Persistent: a block per SM walks over the tiles of C (tile = block, block + grid, ...); the ring of
-// shared-memory stages runs on across tiles, and two accumulators in tensor memory take turns, so the
-// read-out and the stores of one tile overlap the products of the next.
-template <int BN, int STAGES, int KSUB, typename TC>
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
-               long long ldc, long long ldr, int act, int* status) {
-    extern __shared__ unsigned char tc_raw[];
-    TcSmem<BN, STAGES, KSUB>& sm =
-        *reinterpret_cast<TcSmem<BN, STAGES, KSUB>*>(((uintptr_t)tc_raw + 1023) & ~(uintptr_t)1023);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (K + KSUB * TC_BK - 1) / (KSUB * TC_BK);          // a sub-tile past K is zero-filled
-    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-    const int tiles = m_tiles * n_tiles;
-    constexpr uint32_t STAGE_BYTES = KSUB * (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16);
-    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    bool ok = true;
-
-    if (threadIdx.x == 0) {
-        tma_prefetch_map(&map_a);
-        tma_prefetch_map(&map_w);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], TC_EPI_WARPS); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = sm.tmem_base;
-    unsigned long long* const trace = g_tc_trace;
-    if (threadIdx.x == 0) tc_stamp(trace, 0);
-    pdl_trigger();
-    pdl_wait();                                  // barriers and tensor memory are set up while the kernel before ends
-    if (threadIdx.x == 0) tc_stamp(trace, 1);
-
-    // consecutive tiles share a column block of W and differ in their rows of A, so the blocks that
-    // run at the same time read few distinct tiles of either operand
-    if (warp == 0) {
-        if (lane == 0) {
-            long long it = 0, issued = 0;
-            int local = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-                const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = (int)(it % STAGES);
-                    ok = mbar_wait(&sm.empty[s], (uint32_t)(((it / STAGES) & 1) ^ 1));   // passes at once the first time round
-                    if (!ok) break;
-                    mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-#pragma unroll
-                    for (int u = 0; u < KSUB; ++u) {
-                        tma_load_2d(sm.a[s][u], &map_a, (kb * KSUB + u) * TC_BK, m0, &sm.full[s]);
-                        tma_load_2d(sm.b[s][u], &map_w, (kb * KSUB + u) * TC_BK, n0, &sm.full[s]);
-                    }
-                    issued = it + 1;
-                    if (local < TC_TRACE_TILES && (kb == 0 || kb == num_kb - 1)) tc_stamp(trace, 2 + 6 * local + (kb == 0 ? 0 : 1));
-                }
-            }
-            if (!ok) {
-                atomicExch(status, 1);
-                // let the copies already under way land before the block goes away
-                for (long long j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j)
-                    mbar_wait(&sm.full[j % STAGES], (uint32_t)((j / STAGES) & 1));
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
-            long long it = 0;
-            int local = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-                const int buf = local & 1;
-                ok = mbar_wait(&sm.acc_empty[buf], (uint32_t)(((local >> 1) & 1) ^ 1));
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = (int)(it % STAGES);
-                    ok = mbar_wait(&sm.full[s], (uint32_t)((it / STAGES) & 1));
-                    if (!ok) break;
-                    if (kb == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 2);
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (int u = 0; u < KSUB; ++u) {
-                        const uint32_t a_addr = smem_u32(sm.a[s][u]), b_addr = smem_u32(sm.b[s][u]);
-#pragma unroll
-                        for (int k = 0; k < TC_BK / 16; ++k) {
-                            // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
-                            umma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                                      (kb > 0 || u > 0 || k > 0) ? 1u : 0u);
-                        }
-                    }
-                    umma_commit(&sm.empty[s]);            // the stage is free once these have read it
-                }
-                if (ok) umma_commit(&sm.acc_full[buf]);   // the accumulator is complete
-                if (local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 3);
-            }
-            if (!ok) atomicExch(status, 2);
-        }
-    } else {
-        // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31; two warps share each
-        // quarter of the rows and take half of the columns each, so that every scheduler of the SM
-        // has two epilogue warps to switch between.  tcgen05.ld hands every thread one row of a 32 x 32
-        // block.
-        const int quad = warp & 3;
-        const int half = (warp - 2) / 4;
-        constexpr int COLS = BN / (TC_EPI_WARPS / 4);
-        float* patch = sm.patch[warp - 2];
-        constexpr int CHUNKS = COLS / 32;
-        const bool vec_ok = sizeof(TC) == 2 && ((ldc * sizeof(TC)) % 16 == 0) && (((uintptr_t)C) % 16 == 0) && !residual &&
-                            (((uintptr_t)bias) % 16 == 0);
-        int local = 0;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
-            const int buf = local & 1;
-            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-            const int row0 = m0 + quad * 32;
-            // float32 path: the bias of this lane's columns, fetched while the tensor cores are still at work
-            // lane-per-column path: one value per block; packed path: the lane's eight columns of every block
-            float bias_col[CHUNKS][8];
-#pragma unroll
-            for (int q = 0; q < CHUNKS; ++q) {
-                const int nq = n0 + half * COLS + 32 * q;
-                if (vec_ok && nq + 32 <= N) {
-                    const float4* b4 = reinterpret_cast<const float4*>(bias + nq + 8 * (lane & 3));
-                    const float4 lo = bias ? b4[0] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    const float4 hi = bias ? b4[1] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    bias_col[q][0] = lo.x; bias_col[q][1] = lo.y; bias_col[q][2] = lo.z; bias_col[q][3] = lo.w;
-                    bias_col[q][4] = hi.x; bias_col[q][5] = hi.y; bias_col[q][6] = hi.z; bias_col[q][7] = hi.w;
-                } else {
-                    bias_col[q][0] = (bias && nq + lane < N) ? bias[nq + lane] : 0.0f;
-                }
-            }
-            ok = mbar_wait(&sm.acc_full[buf], (uint32_t)((local >> 1) & 1));
-            if (!ok) {
-                if (lane == 0) atomicExch(status, 3);
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 4);
-            // (asking for the next block before this one is finished measured slower)
-            const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + half * COLS);
-#pragma unroll
-            for (int q = 0; q < CHUNKS; ++q) {
-                const int c0 = half * COLS + 32 * q;
-                uint32_t r[32];
-                tmem_ld_32x32(acc_addr + 32 * q, r);
-                if (q == CHUNKS - 1) {
-                    // this warp has read all it needs of the accumulator: the tensor cores may have it back
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
-                }
-                const int nb = n0 + c0;
-                if (row0 >= M || nb >= N) continue;                   // the same for the whole warp
-                // the activation is the same for the whole launch: chosen here, outside the loops over the
-                // elements (inside them the compiler evaluated every activation for every element)
-                if (act == ACT_GELU_NEW)
-                    tc_finish_block<ACT_GELU_NEW, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N,
-                                                      row0, nb, ldc, ldr, vec_ok && nb + 32 <= N);
-                else if (act == ACT_GELU_ERF)
-                    tc_finish_block<ACT_GELU_ERF, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N,
-                                                      row0, nb, ldc, ldr, vec_ok && nb + 32 <= N);
-                else
-                    tc_finish_block<0, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N, row0, nb,
-                                           ldc, ldr, vec_ok && nb + 32 <= N);
-            }
-            if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 5);
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
-    }
-}
-
-// ---------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -363,40 +71,6 @@ static bool make_map_uncached(CUtensorMap* map, const void* base, long long rows
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// SMs of the current device (asked once: this library drives one device per process).
-static int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-            sms = 0;
-    }
-    return sms;
-}
-
-template <int BN, int STAGES, int KSUB, typename TC>
-static int launch_tc(const void* A, const void* W, const float* bias, const float* residual, TC* C, int M, int N,
-                     int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int* status,
-                     cudaStream_t s) {
-    CUtensorMap map_a, map_w;
-    if (!tensor_map_bf16(&map_a, A, M, K, lda, TC_BM) || !tensor_map_bf16(&map_w, W, N, K, ldw, BN)) return MU_ERR_LAUNCH;
-    auto kernel = gemm_tc_kernel<BN, STAGES, KSUB, TC>;
-    const size_t smem = sizeof(TcSmem<BN, STAGES, KSUB>) + 1024;
-    static bool raised = false;
-    if (!raised) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return MU_ERR_LAUNCH;
-        raised = true;
-    }
-    const int sms = sm_count();
-    if (sms <= 0) return MU_ERR_LAUNCH;
-    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
-    dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-    return launch_pdl(kernel, grid, dim3(TC_THREADS), smem, s, 1, map_a, map_w, bias, residual, C, M, N, K, ldc, ldr,
-                      act, status);
-}
-
 }  // namespace mu
 
 // For measurements: a device buffer of (blocks x TC_TRACE_WORDS) 64-bit words that the kernel's roles
@@ -404,7 +78,20 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
 MU_EXPORT int mu_gemm_tc_trace(void* buffer) {
     unsigned long long* p = (unsigned long long*)buffer;
     if (cudaMemcpyToSymbol(mu::g_tc_trace, &p, sizeof(p)) != cudaSuccess) return -1;
+    if (mu::set_tc_trace_split(p) != 0) return -1;
     return mu::TC_TRACE_WORDS;
+}
+
+// Gives the product kernel room for products that are cut along K (few tiles of C, long K): `parts` takes
+// the partial tiles (float32, 16-byte aligned), `tickets` n_tickets counters that are zero now and are left
+// zero by every launch.  Without it, or where it is too small, such products run uncut.
+MU_EXPORT int mu_gemm_tc_split_workspace(void* parts, long long parts_bytes, int* tickets, int n_tickets) {
+    if (((uintptr_t)parts & 15) || parts_bytes < 0 || n_tickets < 0) return MU_ERR_BAD_ARGUMENT;
+    mu::g_split.parts = (float*)parts;
+    mu::g_split.parts_bytes = parts ? parts_bytes : 0;
+    mu::g_split.tickets = tickets;
+    mu::g_split.n_tickets = tickets ? n_tickets : 0;
+    return MU_OK;
 }
 
 // bfloat16 A [M, K] (lda) and W [N, K] (ldw): K, lda, ldw multiples of 8, bases 16-byte aligned.
@@ -436,14 +123,35 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
         if (score > best) { best = score; best_bn = widths[i]; }
     }
 #define MU_TC(BN, ST, KS)                                                                                       \
-    (out_bf16 ? mu::launch_tc<BN, ST, KS, __nv_bfloat16>(A, W, bias, residual, (__nv_bfloat16*)C, M, N, K, lda,  \
-                                                         ldw, ldc, ldr, act, status, s)                         \
-              : mu::launch_tc<BN, ST, KS, float>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc, ldr,   \
-                                                 act, status, s))
+    (out_bf16 ? mu::launch_tc<BN, ST, KS, __nv_bfloat16, false>(A, W, bias, residual, (__nv_bfloat16*)C, M, N, K, \
+                                                                lda, ldw, ldc, ldr, act, status, 1, s)           \
+              : mu::launch_tc<BN, ST, KS, float, false>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc,   \
+                                                        ldr, act, status, 1, s))
     if (const char* forced = getenv("MU_B200_TC_TILE")) {       // for measurements: 64, 128 or 256
         const int f = atoi(forced);
         if (f == 64 || f == 128 || f == 256) best_bn = f;
     }
+    // Few tiles and a long K can be cut along K so that (tiles x parts) fill the SMs: MU_B200_TC_SPLIT=n asks
+    // for n parts wherever K allows.  It is off unless asked for: handing the parts over (stores, a fence, a
+    // ticket, the sum) measured slower than what it replaces at GPT-2 small's sizes (64 rows: k = 768 in 4
+    // parts 16.4 instead of 10 us per product; k = 3,072 in 8 parts 20.7 us instead of the few-rows kernel's
+    // 14.4 us).
+    int splits = 1;
+    {
+        const long long tiles = m_tiles * ((N + best_bn - 1) / best_bn);
+        const int kb64 = (K + 63) / 64;
+        if (const char* forced = getenv("MU_B200_TC_SPLIT")) {
+            const int f = atoi(forced);
+            splits = f <= 0 ? 1 : (f < kb64 ? f : kb64);
+        }
+        // the workspace must hold a partial tile per (tile, part) and a ticket per tile
+        if (!mu::g_split.parts || tiles > mu::g_split.n_tickets ||
+            tiles * splits * (long long)(mu::TC_BM * best_bn * sizeof(float)) > mu::g_split.parts_bytes)
+            splits = 1;
+    }
+    if (splits > 1)
+        return mu::launch_tc_split(best_bn, A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act, out_bf16, status,
+                                   splits, s);
     // narrow tiles: 128-deep stages (issuing, not multiplying, sets their pace); K of a single 64 keeps 64
     static const bool deep = !(getenv("MU_B200_TC_DEEP") && atoi(getenv("MU_B200_TC_DEEP")) == 0);
     if (best_bn == 64) return (deep && K > 64) ? MU_TC(64, 4, 2) : MU_TC(64, 6, 1);

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "mu_gemm_skinny": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                        _c_int, _c_int, _c_p],
     "mu_gemm_tc_trace": [_c_p],
+    "mu_gemm_tc_split_workspace": [_c_p, _c_ll, _c_p, _c_int],
     "mu_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                    _c_int, _c_int, _c_p, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
@@ -292,7 +293,22 @@ def status_word(device) -> torch.Tensor:
     word = _status.get(device)
     if word is None:
         word = _status[device] = _status[str(device)] = torch.zeros(1, dtype=torch.int32, device=device)
+        _split_workspace(device)
     return word
+
+
+_TC_SPLIT = os.environ.get("MU_B200_TC_SPLIT", "0") not in ("0", "")    # products cut along k: only when asked for
+
+
+def _split_workspace(device) -> None:
+    """Room for tensor-core products that are cut along k (few output tiles,
+    long k: a batch of 33 to 128 single tokens): partial tiles for one tile per
+    SM at the widest tile, and a ticket per tile.  Set once per device, at the
+    first use of a kernel with a status word, hence never inside a capture."""
+    parts = scratch("gemm_tc_parts", device, _sm_count(device) * 128 * 256, torch.float32)
+    tickets = zeroed_workspace("gemm_tc_tickets", device, 4 * 1024)
+    _check(library().mu_gemm_tc_split_workspace(parts.data_ptr(), parts.numel() * 4, tickets.data_ptr(),
+                                                tickets.numel() // 4), "gemm_tc_split_workspace", launches=0)
 
 
 def check_status(device="cuda:0") -> None:
@@ -728,7 +744,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     # up to 32 rows the few-rows kernel; up to 64 too where the weight is deeper than wide (its split
     # along k fills the SMs); wider weights go to the tcgen05 kernel from 33 rows on, whose TMA
     # pipeline streams them faster once every block has to read that many rows of activations anyway
-    if tensor_cores and m <= 64 and (m <= 32 or n < k):
+    if tensor_cores and m <= 64 and (m <= 32 or (n < k and not _TC_SPLIT)):
         _check(lib.mu_gemm_skinny(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
                                   _is_bf16(out), _stream()), ("gemm_skinny({}x{}x{})", m, n, k))
     elif tensor_cores:

@@ -402,6 +402,40 @@ def test_tensor_core_product(m, n, k, tile, monkeypatch):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 2304, 768), (64, 768, 3072), (40, 770, 1600), (128, 264, 2048), (200, 72, 520),
+                                   (33, 50, 256)])
+@pytest.mark.parametrize("parts", [None, 2, 5, 64])
+def test_tensor_core_product_cut_along_k(m, n, k, parts, monkeypatch):
+    """Few output tiles and a long k: the kernel cuts k over several blocks, which leave their parts in a
+    workspace; the block with a tile's last ticket adds them in the order of k.  The kernel's own choice of
+    parts and forced ones (64: as many as k has 64-deep stages), ragged edges, every epilogue; run twice,
+    since a launch must leave the tickets as it found them, and bit for bit the same, since the order of
+    the sum is fixed."""
+    from math_utils_b200.csrc import ops
+    if parts:
+        monkeypatch.setenv("MU_B200_TC_SPLIT", str(parts))
+    rng = np.random.default_rng(m + n + k)
+    a = dev(rng.standard_normal((m, k)), torch.bfloat16)
+    w = dev(rng.standard_normal((n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.standard_normal(n))
+    res = dev(rng.standard_normal((m, n)))
+    z = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    zb = z + bias.double().cpu().numpy()
+    runs = []
+    for _ in range(2):
+        got = ops.gemm_tc(a, w, None, out_dtype=torch.float32)
+        assert_close(got.cpu().numpy(), z, "float32", "plain product", k=k)
+        act = ops.gemm_tc(a, w, bias, act="gelu")
+        assert_close(act.float().cpu().numpy(), plain_gpt2.gelu_erf(zb), "bfloat16", "bias, gelu, bfloat16 out")
+        x = res.clone()
+        ops.gemm_tc(a, w, bias, residual=x, out=x)
+        assert_close(x.cpu().numpy(), zb + res.double().cpu().numpy(), "float32", "residual in place", k=k)
+        ops.check_status()
+        runs.append((got, act, x))
+    for first, second in zip(*runs):
+        assert torch.equal(first, second)
+
+
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
     (4, 4, 16, 0), (6, 2, 48, 0), (3, 3, 80, 0), (8, 2, 128, 70), (12, 12, 64, 0), (4, 2, 32, 1), (2, 1, 112, 130)])
 def test_prompt_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window):

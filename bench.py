@@ -10,8 +10,10 @@ context of 1,024.  One JSON line is printed:
               around K graph replays (each step's samples feed the next step
               on the device);
   e2e         the same through the Python entry point ``LLM.generate``: host
-              token lists in, host token lists out, every step's tokens copied
-              to the device from pinned memory and its samples read back;
+              token lists in, host token lists out; every step's positions are
+              copied to the device from pinned memory (the host decides which
+              sequences move on) and its samples read back, the host reading
+              one step behind the device;
   prefill     one step of 2 x 1,024 prompt tokens;
   roofline    bytes a decode step must read (every weight once, the live cache)
               over its time, against the measured copy bandwidth;
@@ -241,7 +243,7 @@ def run_ours(args):
                    "sampling": "greedy", "decode": "cuda graph replay",
                    "l2": "inputs larger than L2 (weights 247 MB + cache per step)",
                    "peaks": pk["source"]},
-        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * 4,
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": batch * 4,
                 "d2h_bytes_per_step": batch * 4},
         "gpu_launches": launches,
         "prefill": {"value": round(pre_tokens / (pre_ms / 1e3), 1), "tokens": pre_tokens, "ms": round(pre_ms, 3),

@@ -7,12 +7,17 @@ sampling and the hand-over of the sampled tokens to the next step in a CUDA
 graph once, and replays it: one launch per step instead of a hundred.  The
 kernels are the ones the eager step runs; only the launching differs.
 
-Two ways to drive it:
+Three ways to drive it:
   * ``feed(tokens, positions)`` then ``launch()`` then ``read_tokens()``: the
-    host supplies every step's inputs and reads every step's tokens (the
-    generation loop, which has to see stop tokens);
+    host supplies every step's inputs and reads every step's tokens;
   * ``launch()`` repeatedly: each step's samples are the next step's inputs on
-    the device (``advance``), with no host round trip between steps.
+    the device (``advance``), with no host round trip between steps;
+  * ``pipelined``: ``start(tokens)`` once, then ``launch_step(positions)`` and
+    ``read_step(ticket)``: the samples feed the next step on the device, the
+    host supplies every step's positions (it alone knows which sequences have
+    ended and stay where they are) and reads every step's samples, one step
+    behind: while it looks at step s, step s + 1 already runs (the generation
+    loop, which has to see stop tokens but should not hold the device up).
 """
 from __future__ import annotations
 
@@ -29,14 +34,15 @@ from .batch import StepContext
 class DecodeSession:
     def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
                  request_ids: Sequence[int], kv_bound: Optional[int] = None, use_program: Optional[bool] = None,
-                 copies_in_graph: bool = False):
-        """``copies_in_graph``: the recorded graph starts with the copy of the fed
-        tokens and positions from pinned memory and ends with the copy of the
-        sampled tokens to pinned memory, so a step of the generation loop is one
-        launch instead of three.  Without it a launch leaves the inputs alone,
-        and each step's samples feed the next on the device."""
+                 pipelined: bool = False):
+        """``pipelined``: two graphs that take turns; each starts with the copy of
+        the step's positions from a pinned buffer of its own and ends with the
+        copy of the sampled tokens to a pinned buffer of its own, so a step is
+        one launch, and the host may fill the buffers of the next step while
+        this one runs.  Without it a launch leaves the inputs alone, and each
+        step's samples feed the next on the device."""
         self.model, self.cache = model, cache
-        self.copies_in_graph = copies_in_graph
+        self.pipelined = pipelined
         self.slots = list(slots)
         self.n = len(self.slots)
         self.params = params
@@ -72,8 +78,16 @@ class DecodeSession:
             q_lens=[1] * n, max_q_len=1, max_kv_len=self.kv_bound, workspace={})
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._feed_views = None
-        self._replayed = False
         self._stream = None
+        if pipelined:
+            self._turn_graphs = None
+            self._turn = 0
+            self._pos_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._pos_views = [t.numpy() for t in self._pos_host]
+            self._out_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._done = [torch.cuda.Event() for _ in range(2)]
+            self._unread = [False, False]
+            self._first_tokens = torch.zeros(n, dtype=torch.int32, pin_memory=True)
         self.program = None
         # One persistent kernel for the whole step instead of a graph of ~60 launches.  Measured on
         # GPT-2 small at batch 8 it is the slower of the two (0.65 ms against 0.41 ms: its 61
@@ -123,10 +137,44 @@ class DecodeSession:
         tok_view, pos_view, dev_part, host_part, n_bytes = self._feed_views
         tok_view[:] = tokens
         pos_view[:] = positions
-        if not (self.copies_in_graph and self.graph is not None):
-            dev_part.copy_(host_part, non_blocking=True)       # else the graph's first node does it
+        dev_part.copy_(host_part, non_blocking=True)
         self._fed = True
         return n_bytes
+
+    # ------------------------------------------------ pipelined: one step behind
+    def start(self, tokens: Sequence[int], positions: Sequence[int]) -> None:
+        """The tokens the first step of these sequences takes (later steps take
+        the samples of the step before, on the device) and its positions."""
+        torch.cuda.current_stream().synchronize()          # no copy from the staging buffer is still under way
+        self._unread = [False, False]
+        self._first_tokens.numpy()[:] = tokens
+        self.token_ids.copy_(self._first_tokens, non_blocking=True)
+        self._pos_views[self._turn][:] = positions
+        self.tok_pos.copy_(self._pos_host[self._turn], non_blocking=True)
+        self._fed = True
+
+    def launch_step(self, positions: Sequence[int]) -> int:
+        """Launches a step at these positions; returns the ticket to read its
+        samples with.  At most two steps may be unread at any time."""
+        turn = self._turn
+        if self._unread[turn]:
+            raise RuntimeError("two steps are launched and unread: read the older one first (its buffers come next)")
+        self._unread[turn] = True
+        self._pos_views[turn][:] = positions
+        if self._turn_graphs is None:
+            self.capture()
+        self._turn_graphs[turn].replay()
+        self._done[turn].record()
+        self.model.runtime.ops.launch_count += self.launches_per_step
+        self._turn = turn ^ 1
+        return turn
+
+    def read_step(self, ticket: int) -> List[int]:
+        """The samples of the step launched with this ticket (waits for that
+        step only)."""
+        self._done[ticket].synchronize()
+        self._unread[ticket] = False
+        return self._out_host[ticket].tolist()
 
     # ------------------------------------------------------------------- steps
     def _record(self) -> None:
@@ -177,32 +225,38 @@ class DecodeSession:
             self._run_once()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        before = ops.launch_count
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            # (the library's own copy: a torch copy from or to pinned memory would leave the host allocator
-            # with an event recorded during a capture)
-            if self.copies_in_graph:
-                _, _, dev_part, host_part, _ = self._feed_views
-                ops.copy_async(dev_part, host_part)
-            self._run_once()
-            if self.copies_in_graph:
-                ops.copy_async(self.next_host, self.next_tokens)
-        self.launches_per_step = ops.launch_count - before
-        self.graph = graph
+        if self.pipelined:
+            graphs = []
+            for turn in range(2):
+                before = ops.launch_count
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    # (the library's own copy: a torch copy from or to pinned memory would leave the host
+                    # allocator with an event recorded during a capture)
+                    ops.copy_async(self.tok_pos, self._pos_host[turn])
+                    self._run_once()
+                    ops.copy_async(self._out_host[turn], self.next_tokens)
+                self.launches_per_step = ops.launch_count - before
+                graphs.append(graph)
+            self._turn_graphs = graphs
+        else:
+            before = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._run_once()
+            self.launches_per_step = ops.launch_count - before
+            self.graph = graph
         self.token_ids.copy_(saved[0]); self.tok_pos.copy_(saved[1]); self.draws.copy_(saved[2])
 
     def launch(self) -> None:
         if self.graph is None:
             self.capture()
         self.graph.replay()
-        self._replayed = True
         self.model.runtime.ops.launch_count += self.launches_per_step
 
     def read_tokens(self) -> List[int]:
         """The tokens the last launched step sampled (waits for it)."""
-        if not (self.copies_in_graph and self._replayed):
-            self.next_host.copy_(self.next_tokens, non_blocking=True)
+        self.next_host.copy_(self.next_tokens, non_blocking=True)
         if self._stream is None:
             self._stream = torch.cuda.current_stream()
         self._stream.synchronize()
@@ -212,15 +266,15 @@ class DecodeSession:
 _SESSIONS_KEPT = 6
 
 
-def session_for(model, cache, params: SamplingParams, n: int, copies_in_graph: bool = True) -> DecodeSession:
+def session_for(model, cache, params: SamplingParams, n: int, pipelined: bool = True) -> DecodeSession:
     """A session of ``n`` sequences for this model, cache and sampling rule; the
     last few are kept so that batch after batch replays the same graphs."""
     kept = model.__dict__.setdefault("_decode_sessions", {})
-    key = (id(cache), n, params, copies_in_graph)
+    key = (id(cache), n, params, pipelined)
     session = kept.pop(key, None)
     if session is None or session.cache is not cache:
         session = DecodeSession(model, cache, [0] * n, params, [0] * n, kv_bound=model.max_positions,
-                                copies_in_graph=copies_in_graph)
+                                pipelined=pipelined)
     kept[key] = session                                  # most recently used last
     while len(kept) > _SESSIONS_KEPT:
         kept.pop(next(iter(kept)))

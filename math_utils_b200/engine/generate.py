@@ -117,10 +117,21 @@ def run_batch(step: Callable, sample: Callable, acquire: Callable, release: Call
 def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[RequestState], stop_ids,
                       max_tokens: int, context: int) -> None:
     """The same batch as ``run_batch``, with the single-token steps replayed
-    from a CUDA graph (``DecodeSession``).  The prompts run as one eager step.
-    A finished request stays parked in the graph's batch (its last token at its
-    last position, so nothing of another sequence is touched) and keeps its slot
-    until the batch has halved, when the rest moves to a smaller graph."""
+    from CUDA graphs (``DecodeSession``, pipelined).  The prompts run as one
+    eager step.  Then the host stays one step behind the device: each step's
+    samples feed the next step on the device, and while the host reads the
+    samples of step s, step s + 1 already runs.  A request that samples a stop
+    token has by then been stepped once more; that step's sample is dropped and
+    its key and value lie past the request's end, in a page the request held
+    anyway.  Ends that do not depend on the sample (``max_tokens``, the context)
+    are known before the launch, and no such extra step is made.  A finished
+    request stays parked in the graph's batch (at its last position, so nothing
+    of another sequence is touched) and keeps its slot until the batch has
+    halved, when the rest moves to a smaller graph.  With a windowed cache group
+    the host does not run behind (pages are given back as a sequence moves on,
+    and the page lists on the device must match the step that reads them)."""
+    from collections import deque
+
     from .decode_session import session_for
     ops = model.runtime.ops
     slots = {}
@@ -147,49 +158,78 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
                 live.remove(k)
                 cache.release(slots.pop(k))
         windowed = any(g.spec.window > 0 for g in cache.kv_groups)
+        depth = 1 if windowed else 2                     # steps launched and not yet read
+        page = cache.page_tokens
         while live:
             members = list(live)                         # the graph's batch; some may park later
             session = session_for(model, cache, params, len(members))
             session.rebind([slots[k] for k in members], [states[k].index for k in members],
                            [draws[k] for k in members])
             place = {k: i for i, k in enumerate(members)}
-            tokens_in = [feed[k] for k in members]
-            positions = [cache.length(slots[k]) for k in members]
+            positions = [cache.length(slots[k]) for k in members]      # of each member's next step
+            stepped_at = list(positions)                                # of each member's last launched step
+            session.start([feed[k] for k in members], positions)
+            running = list(live)        # stepped for real by the next launch, as far as the host knows
+            unread = {k: 0 for k in members}                            # launched steps whose samples are unread
+            in_flight = deque()                                         # (ticket, sequences stepped for real)
             parked = set()
             dirty = True
-            page = cache.page_tokens
             while live and (len(live) * 2 > len(members) or len(members) == 1):
-                for k in live:
-                    if positions[place[k]] % page == 0:     # the token of this step opens a page
-                        dirty |= cache.reserve_one(slots[k])
-                if dirty:
-                    session.sync_block_tables()
-                    dirty = False
-                session.feed(tokens_in, positions)
-                session.launch()
-                tokens = session.read_tokens()
-                still = []
-                for k in live:
-                    slot, i = slots[k], place[k]
-                    cache.lengths[slot] += 1             # what commit(slot, 1) does without a window
-                    if windowed:
-                        cache.commit(slot, 0)
-                    draws[k] += 1
-                    tok = tokens[i]
-                    if take_token(states[k], tok, stop_ids, max_tokens, context):
-                        tokens_in[i] = tok
-                        positions[i] += 1
-                        still.append(k)
-                    else:
-                        parked.add(k)                    # keeps feeding its last token at its last position
-                live = still
-            for k in live:                               # what a smaller graph goes on with
-                feed[k] = tokens_in[place[k]]
+                while running and len(in_flight) < depth:
+                    for k in running:
+                        if positions[place[k]] % page == 0:            # the token of this step opens a page
+                            dirty |= cache.reserve_one(slots[k])
+                    if dirty:
+                        session.sync_block_tables()
+                        dirty = False
+                    in_flight.append((session.launch_step(positions), list(running)))
+                    goes_on = []
+                    for k in running:
+                        i, st = place[k], states[k]
+                        cache.lengths[slots[k]] += 1                   # what commit(slot, 1) does without a window
+                        stepped_at[i] = positions[i]
+                        unread[k] += 1
+                        made = len(st.produced) + unread[k]            # if none of the unread samples is a stop token
+                        if made < max_tokens and len(st.prompt) + made < context:
+                            positions[i] += 1
+                            goes_on.append(k)
+                        # else this step's sample is its last, whatever it is: it stays where it is
+                    running = goes_on
+                if not in_flight:                        # cannot be: a live request is running or has a step unread
+                    raise RuntimeError("the generation loop has live requests and nothing to wait for")
+                _read_step(session, in_flight.popleft(), states, place, live, running, parked, unread, draws, feed,
+                           positions, stepped_at, slots, cache, windowed, stop_ids, max_tokens, context)
+            while in_flight:                             # steps launched before the batch halved or ended
+                _read_step(session, in_flight.popleft(), states, place, live, running, parked, unread, draws, feed,
+                           positions, stepped_at, slots, cache, windowed, stop_ids, max_tokens, context)
             for k in parked:
                 cache.release(slots.pop(k))
     finally:
         for slot in slots.values():
             cache.release(slot)
+
+
+def _read_step(session, launched, states, place, live, running, parked, unread, draws, feed, positions, stepped_at,
+               slots, cache, windowed, stop_ids, max_tokens, context) -> None:
+    """Reads the samples of one launched step and applies them to its requests."""
+    ticket, stepped = launched
+    tokens = session.read_step(ticket)
+    for k in stepped:
+        unread[k] -= 1
+        if states[k].finished:                           # the step ran ahead of the news of its end
+            continue
+        if windowed:
+            cache.commit(slots[k], 0)
+        draws[k] += 1
+        tok = tokens[place[k]]
+        if take_token(states[k], tok, stop_ids, max_tokens, context):
+            feed[k] = tok                                # what a smaller graph would go on with
+        else:
+            live.remove(k)
+            parked.add(k)                                # keeps being stepped at its last position
+            if k in running:
+                running.remove(k)
+                positions[place[k]] = stepped_at[place[k]]
 
 
 def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams,

@@ -1,5 +1,7 @@
 """The generation loop's decisions, with a fake model: no device needed."""
+import numpy as np
 import pytest
+import torch
 
 from math_utils_b200.engine.generate import (RequestState, most_positions, plan_batches, run_batch,
                                              take_token)
@@ -109,3 +111,140 @@ def test_slots_come_back_when_the_model_fails():
         run_batch(bad_step, m.sample, m.acquire, m.release, [RequestState(0, [1]), RequestState(1, [2])],
                   set(), 3, 10)
     assert m.seqs == {}
+
+
+# ------------------------------------------------------------------ the loop that runs one step behind the device
+class FakeDevice:
+    """What the graphed loop drives, without a device: a model whose next token is
+    (sum of the tokens its window sees) % 50, keys kept in numbered pages that are found through
+    the page lists the host has SENT (not the ones it holds), so a missing hand-over of the
+    lists, a page used by two sequences or a step past a sequence's pages shows as a wrong
+    token or an assertion.  Sessions behave like ``DecodeSession(pipelined=True)``: samples feed
+    the next step on the device, positions come from the host, two steps at most are unread."""
+
+    def __init__(self, cache, window=0, limit=10 ** 9):
+        self.cache, self.window, self.limit = cache, window, limit
+        self.page = cache.page_tokens
+        self.pages = {}                                    # (page number, offset) -> token
+        self.steps_launched = 0
+        self.most_unread = 0
+        self.runtime = type("R", (), {"ops": None, "device": "cpu"})()
+        self.graph_safe = True
+
+    def visible(self, table_row, pos):
+        first = 0 if self.window <= 0 else max(0, pos - self.window + 1)
+        total = 0
+        for p in range(first, pos + 1):
+            page = int(table_row[p // self.page])
+            assert page >= 0, f"position {p} has no page"
+            total += self.pages[(page, p % self.page)]
+        return total % 50
+
+    def step(self, cache, entries):                        # the eager prompt step
+        out = []
+        for e in entries:
+            start = cache.reserve(e.slot, len(e.tokens))
+            row = cache.kv_groups[0].table[e.slot]
+            for i, t in enumerate(e.tokens):
+                self.pages[(int(row[(start + i) // self.page]), (start + i) % self.page)] = t
+            out.append(self.visible(row, start + len(e.tokens) - 1))
+            cache.commit(e.slot, len(e.tokens))
+        return torch.tensor(out)
+
+    def session(self, n):
+        dev = self
+
+        class Session:
+            def __init__(self):
+                self.tokens, self.unread, self.turn, self.out = [0] * n, [False, False], 0, [None, None]
+
+            def rebind(self, slots, request_ids, draws):
+                self.slots, self.table = list(slots), None
+
+            def sync_block_tables(self):
+                self.table = dev.cache.kv_groups[0].table[self.slots].copy()
+
+            def start(self, tokens, positions):
+                self.tokens, self.unread = list(tokens), [False, False]
+
+            def launch_step(self, positions):
+                assert not self.unread[self.turn], "a third step launched with two unread"
+                rows_now = dev.cache.kv_groups[0].table[self.slots]
+                nxt = []
+                for i, (tok, pos) in enumerate(zip(self.tokens, positions)):
+                    assert pos < dev.limit, f"member {i} steps at position {pos}: the context ends at {dev.limit}"
+                    page = int(self.table[i][pos // dev.page])
+                    if page < 0 or page != int(rows_now[i][pos // dev.page]):
+                        # only a parked sequence may step without a page of its own: it must not write
+                        raise AssertionError(f"member {i} steps at position {pos} without a page it holds")
+                    dev.pages[(page, pos % dev.page)] = tok
+                    nxt.append(dev.visible(self.table[i], pos))
+                self.tokens = nxt
+                ticket, self.turn = self.turn, self.turn ^ 1
+                self.unread[ticket], self.out[ticket] = True, list(nxt)
+                dev.steps_launched += 1
+                dev.most_unread = max(dev.most_unread, sum(self.unread))
+                return ticket
+
+            def read_step(self, ticket):
+                assert self.unread[ticket]
+                self.unread[ticket] = False
+                return self.out[ticket]
+
+        return Session()
+
+
+def expected_windowed(prompt, max_tokens, stop, context, window):
+    ids, out = list(prompt), []
+    for _ in range(max_tokens):
+        if len(ids) >= context:
+            break
+        t = sum(ids if window <= 0 else ids[-window:]) % 50
+        if t in stop:
+            break
+        out.append(t); ids.append(t)
+    return out
+
+
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("max_tokens,context,stop", [(40, 200, {13, 33}), (5, 200, set()), (150, 140, {7}), (1, 200, set()),
+                                                     (2, 200, set()), (66, 200, {49}),
+                                                     (90, 200, {1, 2, 3, 4, 5, 6, 7, 8, 9})])
+def test_loop_one_step_behind_the_device(monkeypatch, window, max_tokens, context, stop):
+    """``run_batch_graphed`` against the plain recurrence: unequal prompts that cross page borders,
+    stop tokens found one step late, ends known in advance, parked requests, the move to a
+    smaller graph, batch after batch on the same slots; with a window the loop must not run
+    behind."""
+    from math_utils_b200.cache import SequenceCache
+    from math_utils_b200.engine import decode_session, generate as gen
+    from math_utils_b200.parts.base import KVCacheSpec
+    from math_utils_b200.sampling import SamplingParams
+    all_lens = [1, 63, 64, 65, 127, 30]
+    # exactly the pages the first (largest) batch is planned with: a step past a request's planned end finds none
+    room = sum(-(-max(most_positions(n, max_tokens, context), 1) // 64) * 64 for n in all_lens)
+    cache = SequenceCache([KVCacheSpec(1, 16, window)], room, 200, torch.float32, "cpu", n_slots=6)
+    dev = FakeDevice(cache, window, limit=context)
+    sessions = {}
+    monkeypatch.setattr(decode_session, "session_for",
+                        lambda model, c, params, n, pipelined=True: sessions.setdefault(n, dev.session(n)))
+
+    class FakeSampler:
+        def __init__(self, *a):
+            pass
+
+        def sample(self, logits):
+            return logits
+    monkeypatch.setattr(gen, "Sampler", FakeSampler)
+    rng = np.random.default_rng(max_tokens + context)
+    for round_ in range(3):                                # the same slots again and again
+        lens = all_lens[: 6 - round_]
+        prompts = [rng.integers(0, 50, size=n).tolist() for n in lens]
+        states = [RequestState(i, p) for i, p in enumerate(prompts)]
+        gen.run_batch_graphed(dev, cache, SamplingParams(temperature=0.0), states, stop, max_tokens, context)
+        for st, p in zip(states, prompts):
+            assert st.finished
+            assert st.produced == expected_windowed(p, max_tokens, stop, context, window), (round_, len(p), st.reason)
+        assert cache.slots.n_free == 6 and cache.free_pages(0) == cache.n_pages
+    assert dev.most_unread <= (1 if window else 2)
+    if max_tokens > 2 and not window:
+        assert dev.most_unread == 2                        # the loop did run behind

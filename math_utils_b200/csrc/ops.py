@@ -96,15 +96,6 @@ def library() -> ctypes.CDLL:
     return _lib
 
 
-def declare(name: str, argtypes) -> None:
-    """Registers the signature of one more launcher of the library."""
-    _SIGNATURES[name] = argtypes
-    if _lib is not None and hasattr(_lib, name):
-        fn = getattr(_lib, name)
-        fn.argtypes = argtypes
-        fn.restype = _c_int
-
-
 launch_count = 0      # kernels of this library launched so far (a merge after a split counts too)
 
 
@@ -352,14 +343,6 @@ def gemm_tc_trace(buffer: Optional[torch.Tensor]) -> int:
     if words < 0:
         raise KernelError("gemm_tc_trace: the trace pointer could not be set")
     return words
-
-
-def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether gemm_skinny takes this product: bfloat16, at most 64 rows, k and
-    both row strides multiples of 8 elements, 16-byte aligned bases."""
-    return (a.dtype == torch.bfloat16 and a.shape[0] <= 64 and a.shape[1] % 8 == 0
-            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,

@@ -226,27 +226,34 @@ class DecodeSession:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         if self.pipelined:
-            graphs = []
-            for turn in range(2):
-                before = ops.launch_count
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    # (the library's own copy: a torch copy from or to pinned memory would leave the host
-                    # allocator with an event recorded during a capture)
-                    ops.copy_async(self.tok_pos, self._pos_host[turn])
-                    self._run_once()
-                    ops.copy_async(self._out_host[turn], self.next_tokens)
-                self.launches_per_step = ops.launch_count - before
-                graphs.append(graph)
-            self._turn_graphs = graphs
-        else:
-            before = ops.launch_count
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            def turn_body(turn):
+                # (the library's own copy: a torch copy from or to pinned memory would leave the host
+                # allocator with an event recorded during a capture)
+                ops.copy_async(self.tok_pos, self._pos_host[turn])
                 self._run_once()
-            self.launches_per_step = ops.launch_count - before
-            self.graph = graph
+                ops.copy_async(self._out_host[turn], self.next_tokens)
+            self._turn_graphs = [self._record_graph(lambda turn=turn: turn_body(turn), side) for turn in range(2)]
+        else:
+            self.graph = self._record_graph(self._run_once, side)
         self.token_ids.copy_(saved[0]); self.tok_pos.copy_(saved[1]); self.draws.copy_(saved[2])
+
+    def _record_graph(self, body, side: torch.cuda.Stream) -> torch.cuda.CUDAGraph:
+        """Records what ``body`` launches on the side stream.  ``torch.cuda.graph`` would do the same
+        after a garbage collection and after emptying the allocator's cache, which costs a batch that
+        thins out (a smaller graph every time it halves) tens of milliseconds per graph."""
+        ops = self.model.runtime.ops
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            try:
+                body()
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
+        self.launches_per_step = ops.launch_count - before
+        return graph
 
     def launch(self) -> None:
         if self.graph is None:

@@ -15,6 +15,8 @@ int launch_tc_split(int bn, const void* A, const void* W, const float* bias, con
                     int* status, int splits, cudaStream_t s);
 int set_tc_trace_split(unsigned long long* buffer);
 
+constexpr bool TC_SPLIT_AUTO_DEFAULT = true;    // what an unset MU_B200_TC_SPLIT means (ops.py holds the same)
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -131,18 +133,24 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
         const int f = atoi(forced);
         if (f == 64 || f == 128 || f == 256) best_bn = f;
     }
-    // Few tiles and a long K can be cut along K so that (tiles x parts) fill the SMs: MU_B200_TC_SPLIT=n asks
-    // for n parts wherever K allows.  It is off unless asked for: handing the parts over (stores, a fence, a
-    // ticket, the sum) measured slower than what it replaces at GPT-2 small's sizes (64 rows: k = 768 in 4
-    // parts 16.4 instead of 10 us per product; k = 3,072 in 8 parts 20.7 us instead of the few-rows kernel's
-    // 14.4 us).
+    // Few tiles and a long K can be cut along K so that (tiles x parts) fill the SMs.  Handing the parts over
+    // (stores, a fence, a ticket, the sum) costs some microseconds, as much as a dozen 64-deep stages of
+    // products.  MU_B200_TC_SPLIT: "auto" cuts a K of 2,048 or more into parts of six stages or more,
+    // "0" never cuts, n cuts into n parts wherever K allows; unset: TC_SPLIT_AUTO_DEFAULT.
     int splits = 1;
     {
         const long long tiles = m_tiles * ((N + best_bn - 1) / best_bn);
         const int kb64 = (K + 63) / 64;
-        if (const char* forced = getenv("MU_B200_TC_SPLIT")) {
-            const int f = atoi(forced);
+        const char* asked = getenv("MU_B200_TC_SPLIT");
+        const bool automatic = asked ? (asked[0] == 'a') : mu::TC_SPLIT_AUTO_DEFAULT;
+        if (asked && !automatic) {
+            const int f = atoi(asked);
             splits = f <= 0 ? 1 : (f < kb64 ? f : kb64);
+        } else if (automatic && tiles * 2 <= sms && kb64 >= 32) {
+            long long want = sms / tiles;
+            if (want > kb64 / 6) want = kb64 / 6;
+            if (want > 8) want = 8;
+            splits = (int)want;
         }
         // the workspace must hold a partial tile per (tile, part) and a ticket per tile
         if (!mu::g_split.parts || tiles > mu::g_split.n_tickets ||

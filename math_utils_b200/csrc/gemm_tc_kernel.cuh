@@ -16,8 +16,8 @@
 //            float32 residual and store bfloat16 or float32.
 // Rows of A and W beyond M, N and K are zero-filled by TMA; the epilogue
 // predicates its stores.  When C has far fewer tiles than there are SMs (a
-// batch of single tokens: one row of tiles), K can be cut into `splits` parts
-// (the SPLIT variant, only when asked for: see mu_gemm_tc), and
+// batch of single tokens: one row of tiles) and K is long, K is cut into
+// `splits` parts (the SPLIT variant; mu_gemm_tc decides), and
 // every (tile, part) is a work item of its own: a block leaves its partial
 // tile in a float32 workspace and takes a ticket; the block that draws a
 // tile's last ticket adds the parts in the order of K (so the sum does not
@@ -131,34 +131,59 @@ __device__ __forceinline__ void tc_store_partial(const uint32_t (&r)[32], float*
         if (i < n_rows) __stcg(ws_block + (long long)i * bn + lane, patch[i * TC_PATCH_PITCH + lane]);
 }
 
-// The same block of C from the parts: a lane per column; the parts of an element are added in the order of
-// K, whoever wrote them when.  part_stride: floats between one part of the tile and the next.
-template <int ACT, typename TC>
-__device__ __forceinline__ void tc_finish_split(const float* ws_block, long long part_stride, int splits, int bn,
-                                                int lane, const float* __restrict__ bias, const float* residual,
-                                                TC* C, int N, int row0, int nb, int n_rows, long long ldc,
-                                                long long ldr) {
-    const int n = nb + lane;
-    if (n >= N) return;
-    const float bv = bias ? bias[n] : 0.0f;
-    for (int i0 = 0; i0 < n_rows; i0 += 8) {
-        float acc[8], res[8];
+// A tile of C from its parts, by all the epilogue threads together (`who` of `n_threads`): a thread takes
+// four neighbouring columns of a row at a time and asks for up to eight parts of them at once (one round
+// trip to the L2 instead of one per part), then adds them in the order of K, whoever wrote them when.
+// ws_tile: the tile's parts, each [128][BN] float32; rows: the tile's real rows.
+template <int ACT, typename TC, int BN>
+__device__ __forceinline__ void tc_finish_split(const float* ws_tile, int splits, int who, int n_threads,
+                                                const float* __restrict__ bias, const float* residual, TC* C,
+                                                int N, int m0, int n0, int rows, long long ldc, long long ldr) {
+    constexpr int QUADS = BN / 4;                         // groups of four columns in a row of the tile
+    constexpr long long PART = (long long)TC_BM * BN;
+    const bool wide_ok = (ldc % 4 == 0) && (((uintptr_t)C) % 16 == 0);
+    for (int f = who; f < rows * QUADS; f += n_threads) {
+        const int row = f / QUADS, col = 4 * (f % QUADS);
+        const int n = n0 + col;
+        if (n >= N) continue;
+        const float* src = ws_tile + (long long)row * BN + col;
+        float4 part[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            acc[j] = 0.0f;
-            res[j] = (residual && i0 + j < n_rows) ? residual[(long long)(row0 + i0 + j) * ldr + n] : 0.0f;
+        for (int sp = 0; sp < 8; ++sp)
+            part[sp] = sp < splits ? __ldcg(reinterpret_cast<const float4*>(src + sp * PART))
+                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float v[4] = {part[0].x, part[0].y, part[0].z, part[0].w};
+#pragma unroll
+        for (int sp = 1; sp < 8; ++sp)
+            if (sp < splits) { v[0] += part[sp].x; v[1] += part[sp].y; v[2] += part[sp].z; v[3] += part[sp].w; }
+        for (int sp = 8; sp < splits; ++sp) {
+            const float4 more = __ldcg(reinterpret_cast<const float4*>(src + sp * PART));
+            v[0] += more.x; v[1] += more.y; v[2] += more.z; v[3] += more.w;
         }
-        for (int sp = 0; sp < splits; ++sp) {
-            const float* src = ws_block + sp * part_stride + (long long)i0 * bn + lane;
+        const long long m = m0 + row;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (i0 + j < n_rows) acc[j] += __ldcg(src + (long long)j * bn);
+        for (int e = 0; e < 4; ++e) {
+            const bool live = n + e < N;
+            const float b = (bias && live) ? bias[n + e] : 0.0f;
+            const float r = (residual && live) ? residual[m * ldr + n + e] : 0.0f;
+            v[e] = r + tc_act<ACT>(v[e] + b, sizeof(TC) == 2);
         }
+        TC* dst = C + m * ldc + n;
+        if (wide_ok && n + 3 < N) {
+            if (sizeof(TC) == 2) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = packed;
+            } else {
+                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (i0 + j < n_rows)
-                C[(long long)(row0 + i0 + j) * ldc + n] =
-                    from_float<TC>(res[j] + tc_act<ACT>(acc[j] + bv, sizeof(TC) == 2));
+            for (int e = 0; e < 4; ++e)
+                if (n + e < N) dst[e] = from_float<TC>(v[e]);
+        }
     }
 }
 
@@ -381,29 +406,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (lane == 0) atomicExch(status, 3);
                     break;
                 }
-                if (last && n_rows > 0) {
+                if (last) {
                     __threadfence();
-                    const float* ws_read = ws_tile + (quad * 32) * BN + half * COLS;
-#pragma unroll
-                    for (int q = 0; q < CHUNKS; ++q) {
-                        const int nb = n0 + half * COLS + 32 * q;
-                        if (nb >= N) continue;
-                        if (act == ACT_GELU_NEW)
-                            tc_finish_split<ACT_GELU_NEW, TC>(ws_read + 32 * q, TC_BM * BN, splits, BN, lane, bias,
-                                                              residual, C, N, row0, nb, n_rows, ldc, ldr);
-                        else if (act == ACT_GELU_ERF)
-                            tc_finish_split<ACT_GELU_ERF, TC>(ws_read + 32 * q, TC_BM * BN, splits, BN, lane, bias,
-                                                              residual, C, N, row0, nb, n_rows, ldc, ldr);
-                        else
-                            tc_finish_split<0, TC>(ws_read + 32 * q, TC_BM * BN, splits, BN, lane, bias, residual, C, N,
-                                                   row0, nb, n_rows, ldc, ldr);
-                    }
+                    const int who = (int)threadIdx.x - 64, rows = min(TC_BM, M - m0);
+                    if (act == ACT_GELU_NEW)
+                        tc_finish_split<ACT_GELU_NEW, TC, BN>(ws_tile, splits, who, TC_EPI_WARPS * 32, bias, residual, C, N,
+                                                              m0, n0, rows, ldc, ldr);
+                    else if (act == ACT_GELU_ERF)
+                        tc_finish_split<ACT_GELU_ERF, TC, BN>(ws_tile, splits, who, TC_EPI_WARPS * 32, bias, residual, C, N,
+                                                              m0, n0, rows, ldc, ldr);
+                    else
+                        tc_finish_split<0, TC, BN>(ws_tile, splits, who, TC_EPI_WARPS * 32, bias, residual, C, N, m0, n0,
+                                                   rows, ldc, ldr);
                 }
-                if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 5);
-                continue;
-            }
+            } else {
 #pragma unroll
-            for (int q = 0; !SPLIT && q < CHUNKS; ++q) {
+            for (int q = 0; q < CHUNKS; ++q) {
                 const int c0 = half * COLS + 32 * q;
                 uint32_t r[32];
                 tmem_ld_32x32(acc_addr + 32 * q, r);
@@ -425,6 +443,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else
                     tc_finish_block<0, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N, row0, nb,
                                            ldc, ldr, vec_ok && nb + 32 <= N);
+            }
             }
             if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 5);
         }

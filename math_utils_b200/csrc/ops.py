@@ -288,7 +288,19 @@ def status_word(device) -> torch.Tensor:
     return word
 
 
-_TC_SPLIT = os.environ.get("MU_B200_TC_SPLIT", "0") not in ("0", "")    # products cut along k: only when asked for
+# Products of few tiles cut along k (mu_gemm_tc): "auto", "0" or a number of parts; the default is the
+# library's (TC_SPLIT_AUTO_DEFAULT in gemm_tc.cu).
+_TC_SPLIT = os.environ.get("MU_B200_TC_SPLIT", "auto")
+
+
+def _deep_to_tensor_cores(n: int, k: int) -> bool:
+    """Whether a product of 33 to 64 rows whose weight is deeper than wide goes to the tensor-core
+    kernel (which then cuts k) instead of the few-rows kernel.  Measured at 64 rows: 768 x 3,072
+    11.0 us few-rows against 13.8 cut; 1,024 x 4,096 11.8 against 14.6; 1,600 x 6,400 30.5 against
+    17.9: the cut pays from some six million weights on."""
+    if _TC_SPLIT.startswith("a"):
+        return n * k >= 6_000_000
+    return _TC_SPLIT not in ("0", "")
 
 
 def _split_workspace(device) -> None:
@@ -727,7 +739,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     # up to 32 rows the few-rows kernel; up to 64 too where the weight is deeper than wide (its split
     # along k fills the SMs); wider weights go to the tcgen05 kernel from 33 rows on, whose TMA
     # pipeline streams them faster once every block has to read that many rows of activations anyway
-    if tensor_cores and m <= 64 and (m <= 32 or (n < k and not _TC_SPLIT)):
+    if tensor_cores and m <= 64 and (m <= 32 or (n < k and not _deep_to_tensor_cores(n, k))):
         _check(lib.mu_gemm_skinny(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
                                   _is_bf16(out), _stream()), ("gemm_skinny({}x{}x{})", m, n, k))
     elif tensor_cores:

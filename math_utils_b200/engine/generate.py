@@ -16,6 +16,7 @@ without a device.
 """
 from __future__ import annotations
 
+from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
@@ -130,8 +131,6 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
     halved, when the rest moves to a smaller graph.  With a windowed cache group
     the host does not run behind (pages are given back as a sequence moves on,
     and the page lists on the device must match the step that reads them)."""
-    from collections import deque
-
     from .decode_session import session_for
     ops = model.runtime.ops
     slots = {}
@@ -159,77 +158,94 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
                 cache.release(slots.pop(k))
         windowed = any(g.spec.window > 0 for g in cache.kv_groups)
         depth = 1 if windowed else 2                     # steps launched and not yet read
-        page = cache.page_tokens
         while live:
             members = list(live)                         # the graph's batch; some may park later
             session = session_for(model, cache, params, len(members))
-            session.rebind([slots[k] for k in members], [states[k].index for k in members],
-                           [draws[k] for k in members])
-            place = {k: i for i, k in enumerate(members)}
-            positions = [cache.length(slots[k]) for k in members]      # of each member's next step
-            stepped_at = list(positions)                                # of each member's last launched step
-            session.start([feed[k] for k in members], positions)
-            running = list(live)        # stepped for real by the next launch, as far as the host knows
-            unread = {k: 0 for k in members}                            # launched steps whose samples are unread
-            in_flight = deque()                                         # (ticket, sequences stepped for real)
-            parked = set()
-            dirty = True
+            run = _GraphedStretch(session, cache, states, slots, members, live, feed, draws, windowed,
+                                  stop_ids, max_tokens, context)
             while live and (len(live) * 2 > len(members) or len(members) == 1):
-                while running and len(in_flight) < depth:
-                    for k in running:
-                        if positions[place[k]] % page == 0:            # the token of this step opens a page
-                            dirty |= cache.reserve_one(slots[k])
-                    if dirty:
-                        session.sync_block_tables()
-                        dirty = False
-                    in_flight.append((session.launch_step(positions), list(running)))
-                    goes_on = []
-                    for k in running:
-                        i, st = place[k], states[k]
-                        cache.lengths[slots[k]] += 1                   # what commit(slot, 1) does without a window
-                        stepped_at[i] = positions[i]
-                        unread[k] += 1
-                        made = len(st.produced) + unread[k]            # if none of the unread samples is a stop token
-                        if made < max_tokens and len(st.prompt) + made < context:
-                            positions[i] += 1
-                            goes_on.append(k)
-                        # else this step's sample is its last, whatever it is: it stays where it is
-                    running = goes_on
-                if not in_flight:                        # cannot be: a live request is running or has a step unread
-                    raise RuntimeError("the generation loop has live requests and nothing to wait for")
-                _read_step(session, in_flight.popleft(), states, place, live, running, parked, unread, draws, feed,
-                           positions, stepped_at, slots, cache, windowed, stop_ids, max_tokens, context)
-            while in_flight:                             # steps launched before the batch halved or ended
-                _read_step(session, in_flight.popleft(), states, place, live, running, parked, unread, draws, feed,
-                           positions, stepped_at, slots, cache, windowed, stop_ids, max_tokens, context)
-            for k in parked:
+                while run.running and len(run.in_flight) < depth:
+                    run.launch()
+                run.read()
+            while run.in_flight:                         # steps launched before the batch halved or ended
+                run.read()
+            for k in run.parked:
                 cache.release(slots.pop(k))
     finally:
         for slot in slots.values():
             cache.release(slot)
 
 
-def _read_step(session, launched, states, place, live, running, parked, unread, draws, feed, positions, stepped_at,
-               slots, cache, windowed, stop_ids, max_tokens, context) -> None:
-    """Reads the samples of one launched step and applies them to its requests."""
-    ticket, stepped = launched
-    tokens = session.read_step(ticket)
-    for k in stepped:
-        unread[k] -= 1
-        if states[k].finished:                           # the step ran ahead of the news of its end
-            continue
-        if windowed:
-            cache.commit(slots[k], 0)
-        draws[k] += 1
-        tok = tokens[place[k]]
-        if take_token(states[k], tok, stop_ids, max_tokens, context):
-            feed[k] = tok                                # what a smaller graph would go on with
-        else:
-            live.remove(k)
-            parked.add(k)                                # keeps being stepped at its last position
-            if k in running:
-                running.remove(k)
-                positions[place[k]] = stepped_at[place[k]]
+class _GraphedStretch:
+    """A batch's steps on one graph: from the binding of its live requests
+    (``members``) to a session until half of them have ended.  ``live``, ``feed``
+    (the token each live request is fed next) and ``draws`` (how far each
+    sampling stream has run) are the batch's and are updated in place."""
+
+    def __init__(self, session, cache, states, slots, members, live, feed, draws, windowed, stop_ids,
+                 max_tokens, context):
+        self.session, self.cache, self.states, self.slots = session, cache, states, slots
+        self.live, self.feed, self.draws, self.windowed = live, feed, draws, windowed
+        self.stop_ids, self.max_tokens, self.context = stop_ids, max_tokens, context
+        self.place = {k: i for i, k in enumerate(members)}
+        self.positions = [cache.length(slots[k]) for k in members]     # of each member's next step
+        self.stepped_at = list(self.positions)                          # of each member's last launched step
+        self.running = list(live)          # stepped for real by the next launch, as far as the host knows
+        self.unread = {k: 0 for k in members}                           # launched steps whose samples are unread
+        self.in_flight = deque()                                        # (ticket, requests stepped for real)
+        self.parked = set()
+        self.dirty = True                                               # the page lists on the device are out of date
+        session.rebind([slots[k] for k in members], [states[k].index for k in members],
+                       [draws[k] for k in members])
+        session.start([feed[k] for k in members], self.positions)
+
+    def launch(self) -> None:
+        """Launches the next step and works out who goes on after it if no sample
+        of an unread step is a stop token."""
+        cache, positions, place = self.cache, self.positions, self.place
+        for k in self.running:
+            if positions[place[k]] % cache.page_tokens == 0:            # the token of this step opens a page
+                self.dirty |= cache.reserve_one(self.slots[k])
+        if self.dirty:
+            self.session.sync_block_tables()
+            self.dirty = False
+        self.in_flight.append((self.session.launch_step(positions), list(self.running)))
+        goes_on = []
+        for k in self.running:
+            i, st = place[k], self.states[k]
+            cache.lengths[self.slots[k]] += 1                           # what commit(slot, 1) does without a window
+            self.stepped_at[i] = positions[i]
+            self.unread[k] += 1
+            made = len(st.produced) + self.unread[k]                    # if none of the unread samples is a stop token
+            if made < self.max_tokens and len(st.prompt) + made < self.context:
+                positions[i] += 1
+                goes_on.append(k)
+            # else this step's sample is its last, whatever it is: it stays where it is
+        self.running = goes_on
+
+    def read(self) -> None:
+        """Reads the samples of the oldest launched step and applies them to its
+        requests."""
+        if not self.in_flight:                           # cannot be: a live request is running or has a step unread
+            raise RuntimeError("the generation loop has live requests and nothing to wait for")
+        ticket, stepped = self.in_flight.popleft()
+        tokens = self.session.read_step(ticket)
+        for k in stepped:
+            self.unread[k] -= 1
+            if self.states[k].finished:                  # the step ran ahead of the news of its end
+                continue
+            if self.windowed:
+                self.cache.commit(self.slots[k], 0)
+            self.draws[k] += 1
+            tok = tokens[self.place[k]]
+            if take_token(self.states[k], tok, self.stop_ids, self.max_tokens, self.context):
+                self.feed[k] = tok                       # what a smaller graph would go on with
+            else:
+                self.live.remove(k)
+                self.parked.add(k)                       # keeps being stepped at its last position
+                if k in self.running:
+                    self.running.remove(k)
+                    self.positions[self.place[k]] = self.stepped_at[self.place[k]]
 
 
 def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams,

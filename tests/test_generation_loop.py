@@ -248,3 +248,48 @@ def test_loop_one_step_behind_the_device(monkeypatch, window, max_tokens, contex
     assert dev.most_unread <= (1 if window else 2)
     if max_tokens > 2 and not window:
         assert dev.most_unread == 2                        # the loop did run behind
+
+
+def test_loop_one_step_behind_on_drawn_cases(monkeypatch):
+    """The same comparison on drawn cases: prompt lengths, token budget, context, stop tokens and
+    window at random, the cache exactly as large as ``plan_batches`` counts."""
+    from math_utils_b200.cache import SequenceCache
+    from math_utils_b200.engine import decode_session, generate as gen
+    from math_utils_b200.parts.base import KVCacheSpec
+    from math_utils_b200.sampling import SamplingParams
+
+    class FakeSampler:
+        def __init__(self, *a):
+            pass
+
+        def sample(self, logits):
+            return logits
+    monkeypatch.setattr(gen, "Sampler", FakeSampler)
+    rng = np.random.default_rng(2024)
+    reasons = set()
+    for case in range(60):
+        n_req = int(rng.integers(1, 7))
+        context = int(rng.integers(2, 200))
+        lens = [int(rng.integers(1, context + 1)) for _ in range(n_req)]
+        max_tokens = int(rng.choice([0, 1, 2, 3, 17, 64, 65, 300]))
+        stop = set(rng.integers(0, 50, size=int(rng.integers(0, 6))).tolist())
+        window = int(rng.choice([0, 0, 1, 40, 64, 130]))
+        room = sum(-(-max(most_positions(n, max_tokens, context), 1) // 64) * 64 for n in lens)
+        cache = SequenceCache([KVCacheSpec(1, 16, window)], room, 200, torch.float32, "cpu", n_slots=n_req)
+        dev = FakeDevice(cache, window, limit=context)
+        sessions = {}
+        monkeypatch.setattr(decode_session, "session_for",
+                            lambda model, c, params, n, pipelined=True, dev=dev, sessions=sessions:
+                            sessions.setdefault(n, dev.session(n)))
+        for round_ in range(2):
+            prompts = [rng.integers(0, 50, size=n).tolist() for n in lens]
+            states = [RequestState(i, p) for i, p in enumerate(prompts)]
+            gen.run_batch_graphed(dev, cache, SamplingParams(temperature=0.0), states, stop, max_tokens, context)
+            for st, p in zip(states, prompts):
+                assert st.finished
+                assert st.produced == expected_windowed(p, max_tokens, stop, context, window), \
+                    (case, round_, lens, max_tokens, context, sorted(stop), window, len(p), st.reason)
+                reasons.add(st.reason)
+            assert cache.slots.n_free == n_req and cache.free_pages(0) == cache.n_pages
+        assert dev.most_unread <= (1 if window else 2)
+    assert reasons == {"stop", "max_tokens", "context"}

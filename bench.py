@@ -298,95 +298,6 @@ def run_part(args):
     return 0
 
 
-def run_product_sweep(args):
-    """Products of 64 and 128 rows at the shapes of GPT-2 small, medium and XL: the tensor-core kernel
-    uncut, cut along k (its own choice and fixed numbers of parts) and the few-rows kernel, microseconds
-    a call with the weights rotating through more than the L2 holds.  Not a bench record."""
-    import torch
-    from math_utils_b200.csrc import ops
-    dev = "cuda:0"
-
-    def timed(fn, copies, reps=3):
-        for w in copies[:2]:
-            fn(w)
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(reps):
-            for w in copies:
-                fn(w)
-        end.record()
-        torch.cuda.synchronize()
-        return start.elapsed_time(end) * 1e3 / (reps * len(copies))
-
-    before = os.environ.get("MU_B200_TC_SPLIT")
-    for name, m, n, k in [("small proj", 64, 768, 3072), ("small qkv", 64, 2304, 768), ("medium proj", 64, 1024, 4096),
-                          ("xl proj", 64, 1600, 6400), ("xl out", 64, 1600, 1600), ("xl qkv", 64, 4800, 1600),
-                          ("xl proj", 128, 1600, 6400)]:
-        copies = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02
-                  for _ in range(max(2, int(200e6 // (n * k * 2)) + 1))]
-        a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
-        x = torch.zeros(m, n, device=dev, dtype=torch.float32)
-        bias = torch.zeros(n, device=dev)
-        row = {"part": "product_sweep", "shape": name, "m": m, "n": n, "k": k}
-        for mode in ("0", "auto", "2", "4", "8"):
-            os.environ["MU_B200_TC_SPLIT"] = mode
-            row["tc_" + mode + "_us"] = round(timed(lambda w: ops.gemm_tc(a, w, bias, residual=x, out=x), copies), 2)
-        if m <= 64:
-            row["few_rows_us"] = round(timed(lambda w: ops.gemm_skinny(a, w, bias, residual=x, out=x), copies), 2)
-        print(json.dumps(row), flush=True)
-    if before is None:
-        os.environ.pop("MU_B200_TC_SPLIT", None)
-    else:
-        os.environ["MU_B200_TC_SPLIT"] = before
-    ops.check_status()
-    return 0
-
-
-def run_product_trace(args):
-    """The tensor-core product kernel on the four products of a layer (and two
-    large ones) with its time stamps switched on: prints, per shape, when the
-    blocks' loads, products and stores happened (median over the blocks, in
-    microseconds after the first block's set-up).  Not a bench record."""
-    import numpy as np
-    import torch
-    from math_utils_b200.csrc import ops
-    cfg = baseline_config()
-    e, inner, rows = cfg["n_embd"], cfg["n_inner"], PREFILL_SEQS * CONTEXT
-    shapes = [("qkv", rows, 3 * e, e, None, False), ("out", rows, e, e, None, True),
-              ("fc", rows, inner, e, cfg["activation_function"], False), ("proj", rows, e, inner, None, True),
-              ("4096^3", 4096, 4096, 4096, None, False), ("8192^3", 8192, 8192, 8192, None, False)]
-    torch.manual_seed(0)
-    names = ["set-up", "wait over"] + [f"tile{i} {w}" for i in range(4) for w in
-                                       ("first load", "last load", "first stage in", "last product", "accumulator", "stores")]
-    for name, m, n, k, act, res in shapes:
-        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-        w = (torch.randn(n, k, device="cuda") / k ** 0.5).to(torch.bfloat16)
-        bias = torch.randn(n, device="cuda")
-        x = torch.randn(m, n, device="cuda") if res else None
-        out = x if res else torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
-        for _ in range(3):
-            ops.gemm_tc(a, w, bias, act=act, residual=x, out=out)
-        buf = torch.zeros(148 * 64, dtype=torch.int64, device="cuda")
-        words = ops.gemm_tc_trace(buf)
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        ops.gemm_tc(a, w, bias, act=act, residual=x, out=out)
-        end.record()
-        torch.cuda.synchronize()
-        ops.gemm_tc_trace(None)
-        t = buf.cpu().numpy()[:148 * words].reshape(148, words).astype(np.float64)
-        t = t[t[:, 0] > 0]
-        rel = np.where(t > 0, (t - t[:, 0].min()) / 1e3, np.nan)
-        stamps = {nm: round(float(np.nanmedian(rel[:, i])), 1) for i, nm in enumerate(names[:words])
-                  if not np.isnan(rel[:, i]).all()}
-        print(json.dumps({"part": "product_trace", "shape": name, "m": m, "n": n, "k": k, "blocks": int(t.shape[0]),
-                          "event_us": round(start.elapsed_time(end) * 1e3, 1), "us": stamps}), flush=True)
-    ops.check_status()
-    return 0
-
-
 def run_reference(args):
     # The reference is a header-only C++ project with a makefile and no Python packaging, so an
     # offline `pip install --target baseline/_ref` of its checkout has nothing to install.
@@ -404,7 +315,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "product_trace", "product_sweep"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only and print a short line (for profiling a small case)")
     ap.add_argument("--layers", type=int, default=0, help="with --only: fewer layers than the model has")
     args = ap.parse_args()
@@ -414,10 +325,6 @@ def main():
         print(f"bench.py measures one GPU only: this library has no multi-GPU path (asked for {args.gpus})",
               flush=True)
         return 2
-    if args.only == "product_trace":
-        return run_product_trace(args)
-    if args.only == "product_sweep":
-        return run_product_sweep(args)
     if args.only != "all":
         return run_part(args)
     return run_ours(args)

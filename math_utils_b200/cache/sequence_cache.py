@@ -282,6 +282,18 @@ class SequenceCache:
         for g in self.kv_groups:
             g.trim(slot, int(self.lengths[slot]))
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forgets the slot's positions from ``length`` on (a step that ran ahead
+        of the news that its sequence had ended).  The pages stay with the slot.
+        Not for windowed groups, which have given pages back as the sequence
+        moved on, nor for fixed-size state, which cannot be wound back."""
+        self._check(slot)
+        if not 0 <= length <= int(self.lengths[slot]):
+            raise CacheError(f"slot {slot} holds {int(self.lengths[slot])} positions, cannot cut it to {length}")
+        if length < int(self.lengths[slot]) and (self.state_groups or any(g.spec.window > 0 for g in self.kv_groups)):
+            raise CacheError("a cache with a windowed group or with fixed-size state cannot be cut back")
+        self.lengths[slot] = length
+
     def entry(self, index: int):
         """The view of schedule entry ``index``'s cache, or None if it owns none."""
         return self._entry_view.get(index)

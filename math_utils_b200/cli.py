@@ -39,7 +39,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--model", dest="model_opt", help="same as the positional model folder")
     ap.add_argument("--tokens", type=int, default=256, help="most new tokens per answer")
     ap.add_argument("--temp", type=float, default=0.7, help="temperature; 0 is greedy")
-    ap.add_argument("--topk", type=int, default=20, help="keep the k likeliest tokens; 1 is greedy, 0 keeps all")
+    ap.add_argument("--topk", type=int, default=20, help="keep the k likeliest tokens; 0 or 1 is greedy, a negative number keeps all")
     ap.add_argument("--seed", type=int, default=0, help="seed of sampling and of --random weights")
     ap.add_argument("--ctx", type=int, default=4096, help="cache positions, clamped to the model's maximum")
     ap.add_argument("--prompt", help="one shot: answer these token ids and exit")

@@ -8,6 +8,7 @@ reference dispatches on ``model_type`` alone through ``specRegistry`` /
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 from dataclasses import dataclass
@@ -71,9 +72,30 @@ def read_config_json(model_dir: str) -> dict:
     return raw
 
 
+def generation_stop_ids(model_dir: str) -> tuple:
+    """``eos_token_id`` of the folder's generation_config.json (an id or a list),
+    empty if there is no such file or it cannot be read: the reference adds these
+    to config.json's own (include/ai/LocalModel.hpp:1788-1792)."""
+    from .base import KeyReader
+    path = os.path.join(model_dir, "generation_config.json")
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            raw = json.load(f)
+    except (OSError, json.JSONDecodeError):
+        return ()
+    if not isinstance(raw, dict):
+        return ()
+    return KeyReader(raw, "generation_config.json").id_list("eos_token_id")
+
+
 def load_config(model_dir: str):
-    """(architecture entry, typed configuration, plan) of a model folder."""
+    """(architecture entry, typed configuration, plan) of a model folder.  The
+    plan's stop ids are config.json's followed by generation_config.json's."""
     raw = read_config_json(model_dir)
     arch = architecture_for(raw)
     config = arch.config_class.from_json(raw)
-    return arch, config, config.plan()
+    plan = config.plan()
+    more = tuple(t for t in generation_stop_ids(model_dir) if t not in plan.stop_ids)
+    if more:
+        plan = dataclasses.replace(plan, stop_ids=tuple(plan.stop_ids) + more)
+    return arch, config, plan

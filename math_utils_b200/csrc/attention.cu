@@ -185,9 +185,18 @@ __device__ __forceinline__ void load_run32(const __nv_bfloat16* p, float (&v)[32
     }
 }
 
+// The same for a head size whose rows are not whole 16-byte pieces: one element at a time.
+template <typename TE>
+__device__ __forceinline__ float dot_row_any(const float* qs, const TE* krow, int head_dim) {
+    float s = 0.0f;
+    for (int d = 0; d < head_dim; ++d) s = fmaf(qs[d], to_float(krow[d]), s);
+    return s;
+}
+
 constexpr int ATT_WARPS = 4;
 
-template <typename TE, int DPL>
+// DPL: dimensions per lane (head_dim <= 32 * DPL).  VEC: key rows are whole 16-byte pieces.
+template <typename TE, int DPL, bool VEC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_kernel(const TE* __restrict__ q, long long ldq, TE* __restrict__ out, long long ldo,
                  const TE* __restrict__ kv, const int* __restrict__ block_table, int max_pages,
@@ -207,8 +216,10 @@ attention_kernel(const TE* __restrict__ q, long long ldq, TE* __restrict__ out, 
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     int lo = first, hi = pos + 1;
     if (n_splits > 1) {
+        // the last split takes whatever the others leave, so no key is dropped when
+        // n_splits * split_keys falls short of a sequence
         lo = max(first, split * split_keys);
-        hi = min(pos + 1, (split + 1) * split_keys);
+        hi = split == n_splits - 1 ? pos + 1 : min(pos + 1, (split + 1) * split_keys);
     }
     float* qs = q_smem[warp];
     for (int d = lane; d < head_dim; d += 32) qs[d] = to_float(q[(long long)t * ldq + h * head_dim + d]);
@@ -230,7 +241,10 @@ attention_kernel(const TE* __restrict__ q, long long ldq, TE* __restrict__ out, 
         const bool valid = j >= lo && j < hi;
         const long long page_off = (long long)pages[base / page_tokens] * page_stride;
         float s = -INFINITY;
-        if (valid) s = dot_row(qs, kv + page_off + k_base + (long long)(j % page_tokens) * head_dim, head_dim) * scale;
+        if (valid) {
+            const TE* krow = kv + page_off + k_base + (long long)(j % page_tokens) * head_dim;
+            s = (VEC ? dot_row(qs, krow, head_dim) : dot_row_any(qs, krow, head_dim)) * scale;
+        }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.0f;   // the run holds at least one visible key
         const float corr = expf(m - m_new);               // 0 on the first run (m = -inf)
@@ -305,7 +319,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 static int check_paged(int page_tokens, int n_kv_heads, int head_dim, int max_pages) {
     if (page_tokens <= 0 || n_kv_heads <= 0 || max_pages <= 0) return MU_ERR_BAD_ARGUMENT;
     if (page_tokens % 32 != 0) return MU_ERR_UNSUPPORTED_SIZE;       // values are read in aligned runs of 32 positions
-    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;
+    if (head_dim <= 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;
     return MU_OK;
 }
 
@@ -322,7 +336,8 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = n_kv_heads * head_dim >= 256 ? 256 : 128;
     const int e = is_bf16 ? 8 : 4;
-    if (ldk % e == 0 && ldv % e == 0 && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) && !((uintptr_t)kv & 15)) {
+    if (head_dim % e == 0 && ldk % e == 0 && ldv % e == 0 && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) &&
+        !((uintptr_t)kv & 15)) {
         const int vthreads = n_kv_heads * head_dim / e >= 128 ? 128 : 64;
         const bool tiled = tiles != nullptr && n_tiles > 0 && n_kv_heads <= 65535 && page_tokens % 8 == 0;
         if (tiled) {
@@ -373,7 +388,8 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
 
 // n_splits > 1 needs part_o [n_tokens * n_heads * n_splits * head_dim] and
 // part_ml [n_tokens * n_heads * n_splits * 2] floats of scratch, and split s takes
-// the keys [s * split_keys, (s + 1) * split_keys).
+// the keys [s * split_keys, (s + 1) * split_keys); the last split goes on to the
+// token's own position.  Any head size up to 256.
 MU_EXPORT int mu_attention(const void* q, long long ldq, void* out, long long ldo, const void* kv,
                            const int* block_table, int max_pages, int page_tokens,
                            const int* tok_pos, const int* tok_seq, int n_tokens,
@@ -390,17 +406,22 @@ MU_EXPORT int mu_attention(const void* q, long long ldq, void* out, long long ld
     dim3 grid((unsigned)((items + mu::ATT_WARPS - 1) / mu::ATT_WARPS), n_splits);
     cudaStream_t s = (cudaStream_t)stream;
     const int dpl = (head_dim + 31) / 32;
-#define MU_ATT(TE, DPL)                                                                          \
-    mu::attention_kernel<TE, DPL><<<grid, mu::ATT_WARPS * 32, 0, s>>>(                            \
+    // key rows in 16-byte pieces where the head size and the cache's address allow it
+    const bool vec = head_dim % (is_bf16 ? 8 : 4) == 0 && !((uintptr_t)kv & 15);
+#define MU_ATT(TE, DPL, VEC)                                                                     \
+    mu::attention_kernel<TE, DPL, VEC><<<grid, mu::ATT_WARPS * 32, 0, s>>>(                       \
         (const TE*)q, ldq, (TE*)out, ldo, (const TE*)kv, block_table, max_pages, page_tokens,    \
         tok_pos, tok_seq, n_tokens, n_heads, n_kv_heads, head_dim, scale, window,      \
         n_splits, split_keys, part_o, part_ml)
-#define MU_ATT_T(TE)                     \
-    do {                                 \
-        if (dpl <= 1) MU_ATT(TE, 1);     \
-        else if (dpl <= 2) MU_ATT(TE, 2);\
-        else if (dpl <= 4) MU_ATT(TE, 4);\
-        else MU_ATT(TE, 8);              \
+#define MU_ATT_T(TE)                                     \
+    do {                                                 \
+        if (!vec) {                                      \
+            if (dpl <= 2) MU_ATT(TE, 2, false);          \
+            else MU_ATT(TE, 8, false);                   \
+        } else if (dpl <= 1) MU_ATT(TE, 1, true);        \
+        else if (dpl <= 2) MU_ATT(TE, 2, true);          \
+        else if (dpl <= 4) MU_ATT(TE, 4, true);          \
+        else MU_ATT(TE, 8, true);                        \
     } while (0)
     if (is_bf16) MU_ATT_T(__nv_bfloat16);
     else MU_ATT_T(float);
@@ -458,12 +479,18 @@ MU_EXPORT int mu_attention_static_scratch(const void* q, long long ldq, void* ou
                                           float scale, int window, int n_splits, int split_keys,
                                           int is_bf16, void* stream) {
     if (n_tokens <= 0) return MU_OK;
-    if (n_heads <= 0 || head_dim <= 0 || n_splits < 1) return MU_ERR_BAD_ARGUMENT;
+    // everything the size below is made of is checked first, so that the product cannot overflow
+    if (int e = check_paged(page_tokens, n_kv_heads, head_dim, max_pages)) return e;
+    if (n_heads <= 0 || n_heads > 65535 || n_splits < 1 || n_splits > 65535) return MU_ERR_BAD_ARGUMENT;
+    if (n_splits > 1 && split_keys <= 0) return MU_ERR_BAD_ARGUMENT;
     float* part_o = nullptr;
     float* part_ml = nullptr;
     if (n_splits > 1) {
+        const long long per_token = (long long)n_heads * n_splits * (head_dim + 2);     // < 2^41 after the checks above
+        if (per_token > (long long)MU_STATIC_SCRATCH_FLOATS ||
+            (long long)n_tokens * per_token > (long long)MU_STATIC_SCRATCH_FLOATS)
+            return MU_ERR_STATIC_SCRATCH;
         const long long units = (long long)n_tokens * n_heads * n_splits;
-        if (units * (head_dim + 2) > (long long)MU_STATIC_SCRATCH_FLOATS) return MU_ERR_STATIC_SCRATCH;
         float* base = nullptr;
         if (int e = static_scratch_for_current_device(&base)) return e;
         part_o = base;

@@ -24,7 +24,6 @@
 #include "common.cuh"
 
 #include <math.h>
-#include <cstdlib>
 
 namespace mu {
 
@@ -278,7 +277,7 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
                                   const int* block_table, int max_pages, int page_tokens,
                                   const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads,
                                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
-                                  int is_bf16, void* stream) {
+                                  int max_warps, int is_bf16, void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (page_tokens != mu::AD_PAGE) return MU_ERR_UNSUPPORTED_SIZE;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return MU_ERR_UNSUPPORTED_SIZE;
@@ -293,14 +292,14 @@ MU_EXPORT int mu_attention_decode(const void* q, long long ldq, const void* k_ne
     const int dp = (head_dim + 63) / 64;
     // a warp per page while the GPU has room for them; with many sequences fewer warps per block,
     // each folding several pages, so that several blocks share an SM and overlap their waits
-    long long room = (148ll * 16 * 2) / items;
+    const int sms = mu::sm_count();
+    if (sms <= 0) return MU_ERR_LAUNCH;
+    long long room = ((long long)sms * 16 * 2) / items;
     if (room < 1) room = 1;
     const int want = n_splits < room ? n_splits : (int)room;
     int nw = want >= 16 ? 16 : want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
-    if (const char* cap = getenv("MU_B200_ATT_WARPS")) {       // for measurements: at most this many warps per block
-        const int c = atoi(cap);
-        while (nw > 1 && nw > c) nw /= 2;
-    }
+    if (max_warps > 0)
+        while (nw > 1 && nw > max_warps) nw /= 2;
     int rc = MU_OK;
 #define MU_AD(TE, DP, NW)                                                                               \
     rc = mu::launch_pdl(mu::attention_decode_kernel<TE, DP, NW>, grid, dim3(NW * 32), 0, s, 1,          \

@@ -5,7 +5,7 @@
 // bfloat16 and multiplying one pair at a time.  Here a warp does a page with
 // some two hundred: both products of the page are mma.sync.m16n8k16, and the
 // fragments are loaded straight from the cache in the layout the instruction
-// wants, 16 bytes at a time, with no shared memory and no shuffles:
+// wants, 16 bytes at a time, with no shuffles:
 //   * S = Q K^T.  The 16 rows of the left operand are the query heads that
 //     share one kv head (one row for plain multi-head attention; the rest are
 //     zero).  A key is one contiguous row of the page; thread (g, t) of the
@@ -25,10 +25,8 @@
 // attention_decode.cu.  Softmax in float32; probabilities rounded to bfloat16
 // for the second product, as in the prompt kernel.
 //
-// Formulas: include/ai/Kernels.hpp:132-161.  Head sizes 32 and 64 here (a page's
-// fragments of both operands stay in registers, which larger heads would not
-// allow) and 32, 64, 96, 128 in the variant below that stages pages in shared
-// memory; up to 16 query heads per kv head; pages of 64 positions.
+// Formulas: include/ai/Kernels.hpp:132-161.  Head sizes 32, 64, 96 and 128; up
+// to 16 query heads per kv head; pages of 64 positions.
 #include "common.cuh"
 
 #include <math.h>
@@ -49,268 +47,13 @@ __device__ __forceinline__ uint32_t td_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// KD = head_dim / 16 (even).  NW = warps per block.
-template <int KD, int NW>
-__global__ void __launch_bounds__(NW * 32)
-attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
-                           const __nv_bfloat16* __restrict__ k_new, long long ldk,
-                           const __nv_bfloat16* __restrict__ v_new, long long ldv,
-                           __nv_bfloat16* __restrict__ out, long long ldo, __nv_bfloat16* kv,
-                           const int* __restrict__ block_table, int max_pages,
-                           const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
-                           int n_kv_heads, float scale, int window) {
-    constexpr int DH = 16 * KD;
-    constexpr int KW = 2 * KD;                     // 32-bit words of a key row that a thread holds (dh/4 dims)
-    constexpr int KV4 = KW / 4;                    // ... as 16-byte pieces
-    extern __shared__ float part_o[];              // [NW][rows][DH + 1]
-    __shared__ float part_m[NW][16], part_l[NW][16];
-    __shared__ float weight[NW][16];
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int tk = blockIdx.x / n_kv_heads, kvh = blockIdx.x % n_kv_heads;
-    const int rows = n_heads / n_kv_heads;         // query heads of this kv head: rows of the left operand
-    pdl_trigger();
-    const int* pages = block_table + (long long)(tok_seq ? tok_seq[tk] : tk) * max_pages;
-    const int guess = pages[min(warp, max_pages - 1)];
-    const int pos = tok_pos[tk];
-    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-    const int first_page = first / TD_PAGE, last_page = pos / TD_PAGE;
-    const long long head_stride = (long long)TD_PAGE * DH;
-
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};      // rows g and g + 8
-    float o_acc[2 * KD][4];
-#pragma unroll
-    for (int j = 0; j < 2 * KD; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o_acc[j][i] = 0.0f;
-
-    uint4 kf[8][KV4];                              // key fragments: tile j -> the thread's dims of key(j, g)
-    uint4 vf[2 * KD][2];                           // value fragments: dimension tile j -> positions [16 t, 16 t + 16)
-    struct PageView { __nv_bfloat16* kpage; __nv_bfloat16* vpage; int lo, hi; bool has_new; };
-    auto view_of = [&](int page_idx) {
-        PageView pv;
-        const int page = (page_idx == warp) ? guess : pages[page_idx];
-        pv.kpage = kv + ((long long)page * 2 * n_kv_heads + kvh) * head_stride;
-        pv.vpage = pv.kpage + (long long)n_kv_heads * head_stride;
-        const int base = page_idx * TD_PAGE;
-        pv.lo = max(first - base, 0);
-        pv.hi = min(pos + 1 - base, TD_PAGE);
-        pv.has_new = (k_new != nullptr) && page_idx == last_page;
-        return pv;
-    };
-    // Everything of the page that the cache holds: rows written by earlier steps, which no kernel of
-    // this step touches.  (The position of the step's own token is read too and weighs nothing.)
-    auto fetch = [&](const PageView& pv) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int key = 16 * (g >> 1) + 2 * j + (g & 1);
-            const uint4* src = reinterpret_cast<const uint4*>(pv.kpage + (long long)key * DH + (DH / 4) * t);
-#pragma unroll
-            for (int c = 0; c < KV4; ++c) kf[j][c] = src[c];
-        }
-#pragma unroll
-        for (int j = 0; j < 2 * KD; ++j) {
-            const uint4* src = reinterpret_cast<const uint4*>(pv.vpage + (long long)(8 * j + g) * TD_PAGE + 16 * t);
-            vf[j][0] = src[0];
-            vf[j][1] = src[1];
-        }
-    };
-
-    const int my_first = first_page + warp;
-    PageView pv = {};
-    if (my_first <= last_page) {
-        pv = view_of(my_first);
-        fetch(pv);
-    }
-    // later pages of this warp: ask for them now, so that their turn finds them in L2
-    for (int p = my_first + NW; p <= last_page; p += NW) {
-        const char* kb = reinterpret_cast<const char*>(kv + ((long long)pages[p] * 2 * n_kv_heads + kvh) * head_stride);
-        const char* vb = kb + (long long)n_kv_heads * head_stride * (long long)sizeof(__nv_bfloat16);
-        for (int off = lane * 128; off < TD_PAGE * DH * (int)sizeof(__nv_bfloat16); off += 32 * 128) {
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + off));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + off));
-        }
-    }
-    pdl_wait();                                    // this step's query, key and value from here on
-
-    // the query rows as left-operand fragments: thread (g, t) holds dims [t dh/4, (t+1) dh/4) of rows g, g + 8
-    uint32_t qa[KD][4];
-    {
-        uint4 lo4[KV4], hi4[KV4];
-#pragma unroll
-        for (int c = 0; c < KV4; ++c) { lo4[c] = make_uint4(0, 0, 0, 0); hi4[c] = make_uint4(0, 0, 0, 0); }
-        if (g < rows) {
-            const uint4* src = reinterpret_cast<const uint4*>(q + (long long)tk * ldq + (long long)(kvh * rows + g) * DH + (DH / 4) * t);
-#pragma unroll
-            for (int c = 0; c < KV4; ++c) lo4[c] = src[c];
-        }
-        if (g + 8 < rows) {
-            const uint4* src = reinterpret_cast<const uint4*>(q + (long long)tk * ldq + (long long)(kvh * rows + g + 8) * DH + (DH / 4) * t);
-#pragma unroll
-            for (int c = 0; c < KV4; ++c) hi4[c] = src[c];
-        }
-        const uint32_t* lw = reinterpret_cast<const uint32_t*>(lo4);
-        const uint32_t* hw = reinterpret_cast<const uint32_t*>(hi4);
-#pragma unroll
-        for (int kk = 0; kk < KD; ++kk) {
-            qa[kk][0] = lw[2 * kk]; qa[kk][1] = hw[2 * kk]; qa[kk][2] = lw[2 * kk + 1]; qa[kk][3] = hw[2 * kk + 1];
-        }
-    }
-    const float c_log2 = scale * 1.4426950408889634f;          // scores are exponentiated in base 2
-
-    for (int page_idx = my_first; page_idx <= last_page; page_idx += NW) {
-        if (page_idx != my_first) {
-            pv = view_of(page_idx);
-            fetch(pv);
-        }
-        const int lo = pv.lo, hi = pv.hi;
-        const bool has_new = pv.has_new;
-        const __nv_bfloat16* kn = has_new ? k_new + (long long)tk * ldk + kvh * DH : nullptr;
-        const __nv_bfloat16* vn = has_new ? v_new + (long long)tk * ldv + kvh * DH : nullptr;
-        const int new_key = hi - 1;                            // where the step's own token sits, if in this page
-        if (has_new) {
-            // append: this block is the only one for this (sequence, kv head)
-            for (int d = lane; d < DH; d += 32) {
-                pv.kpage[(long long)new_key * DH + d] = kn[d];
-                pv.vpage[(long long)d * TD_PAGE + new_key] = vn[d];
-            }
-            // the thread group that holds the new key's column takes the key from the projections
-            const int jn = (new_key & 15) >> 1;
-            if (16 * (g >> 1) + 2 * jn + (g & 1) == new_key) {
-                const uint4* src = reinterpret_cast<const uint4*>(kn + (DH / 4) * t);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (j == jn) {
-#pragma unroll
-                        for (int c = 0; c < KV4; ++c) kf[j][c] = src[c];
-                    }
-            }
-        }
-
-        // S = Q K^T: 8 tiles of 8 keys
-        float s[8][4];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-            const uint32_t* kw = reinterpret_cast<const uint32_t*>(kf[j]);
-#pragma unroll
-            for (int kk = 0; kk < KD; ++kk) td_mma(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kw[2 * kk], kw[2 * kk + 1]);
-        }
-        // the thread's columns are keys 16 t + 2 j + c
-        float mx[2] = {m_run[0], m_run[1]};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = 16 * t + 2 * j + (i & 1);
-                const bool seen = key >= lo && key < hi;
-                const float v = seen ? s[j][i] * c_log2 : -INFINITY;
-                s[j][i] = v;
-                mx[i >> 1] = fmaxf(mx[i >> 1], v);
-            }
-        }
-        float corr[2], sum[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));      // finite: the page has a visible key
-            corr[r] = exp2f(m_run[r] - mx[r]);
-            m_run[r] = mx[r];
-        }
-        // probabilities; the new key's is set aside (its value is not in the cache yet) and kept as w_new
-        float w_new[2] = {0.0f, 0.0f};
-        uint32_t pa[4][4];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float p[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                p[i] = exp2f(s[j][i] - mx[i >> 1]);
-                sum[i >> 1] += p[i];
-                if (has_new && 16 * t + 2 * j + (i & 1) == new_key) { w_new[i >> 1] = p[i]; p[i] = 0.0f; }
-            }
-            pa[j >> 1][(j & 1) * 2] = td_pack(p[0], p[1]);
-            pa[j >> 1][(j & 1) * 2 + 1] = td_pack(p[2], p[3]);
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + sum[r];
-        // O = O * corr + P V: tiles of 8 dimensions, 4 steps of 16 positions
-#pragma unroll
-        for (int j = 0; j < 2 * KD; ++j) {
-            o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0]; o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
-            const uint32_t* vw = reinterpret_cast<const uint32_t*>(vf[j]);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-                td_mma(o_acc[j], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], vw[2 * kk], vw[2 * kk + 1]);
-        }
-        if (has_new) {
-            // every thread of a row's group needs the new key's weight: it sits in the thread with t = new_key / 16
-            const int src_lane = (lane & ~3) | ((new_key >> 4) & 3);
-            const float w0 = __shfl_sync(0xffffffffu, w_new[0], src_lane);
-            const float w1 = __shfl_sync(0xffffffffu, w_new[1], src_lane);
-#pragma unroll
-            for (int j = 0; j < 2 * KD; ++j) {
-                const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vn + 8 * j + 2 * t));
-                o_acc[j][0] = fmaf(w0, v.x, o_acc[j][0]); o_acc[j][1] = fmaf(w0, v.y, o_acc[j][1]);
-                o_acc[j][2] = fmaf(w1, v.x, o_acc[j][2]); o_acc[j][3] = fmaf(w1, v.y, o_acc[j][3]);
-            }
-        }
-    }
-
-    // per-warp results to shared memory: thread (g, t) holds rows g, g + 8, dims 8 j + 2 t, + 1
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-    float* mine = part_o + (long long)warp * rows * (DH + 1);
-#pragma unroll
-    for (int j = 0; j < 2 * KD; ++j) {
-        if (g < rows) {
-            mine[g * (DH + 1) + 8 * j + 2 * t] = o_acc[j][0];
-            mine[g * (DH + 1) + 8 * j + 2 * t + 1] = o_acc[j][1];
-        }
-        if (g + 8 < rows) {
-            mine[(g + 8) * (DH + 1) + 8 * j + 2 * t] = o_acc[j][2];
-            mine[(g + 8) * (DH + 1) + 8 * j + 2 * t + 1] = o_acc[j][3];
-        }
-    }
-    if (t == 0) {
-        part_m[warp][g] = m_run[0]; part_m[warp][g + 8] = m_run[1];
-        part_l[warp][g] = l_run[0]; part_l[warp][g + 8] = l_run[1];
-    }
-    __syncthreads();
-    // merge in warp order: weights once per (warp, row), then every output element by one thread
-    if (threadIdx.x < NW * 16) {
-        const int w = threadIdx.x / 16, r = threadIdx.x % 16;
-        float big = -INFINITY;
-#pragma unroll
-        for (int x = 0; x < NW; ++x) big = fmaxf(big, part_m[x][r]);
-        weight[w][r] = part_m[w][r] == -INFINITY ? 0.0f : exp2f(part_m[w][r] - big);
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32) {
-        const int r = idx / DH, d = idx % DH;
-        float total = 0.0f, o = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            total = fmaf(part_l[w][r], weight[w][r], total);
-            o = fmaf(part_o[(w * rows + r) * (DH + 1) + d], weight[w][r], o);
-        }
-        out[(long long)tk * ldo + (long long)(kvh * rows + r) * DH + d] = __float2bfloat16_rn(o / total);
-    }
-}
-
-
-// ------------------------------------------------------------------------------------------------
-// The same kernel with the pages staged in shared memory.  A key page and a value page of one kv head
-// are each one contiguous run of the cache, so one thread brings a page in with two bulk copies
-// (cp.async.bulk, completion counted by an mbarrier); every warp owns a ring of RING page buffers and
-// keeps that many of its pages in flight while it works on the oldest.  The bytes in flight no longer
-// sit in registers, so more warps fit on an SM and memory streams while the tensor cores work: this is
-// the variant for many sequences, and it lets a block of few sequences ask for all of its pages at once.
-// Fragments are read from shared memory with the same addressing as from the cache (rows of a page are
+// Pages are staged in shared memory.  A key page and a value page of one kv head are each one
+// contiguous run of the cache, so one thread brings a page in with two bulk copies (cp.async.bulk,
+// completion counted by an mbarrier); every warp owns a ring of RING page buffers and keeps that many
+// of its pages in flight while it works on the oldest.  The bytes in flight do not sit in registers,
+// so several blocks fit on an SM and memory streams while the tensor cores work, and a block of few
+// sequences can ask for all of its pages at once.  KD = head_dim / 16 (even), NW = warps per block.
+// Fragments are read from shared memory with the addressing described above (rows of a page are
 // 64 or 128 bytes apart, so the two rows that a quarter of a warp reads together collide on banks two
 // ways at most).  Waits on a copy are bounded; a wait that runs out sets *status to 4 and the block
 // writes nothing.
@@ -586,23 +329,21 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
 
 }  // namespace mu
 
-// Arguments as mu_attention_decode (bfloat16 only).  ring 0: pages go from the cache straight into
-// registers, n_warps (1, 2, 4 or 8) warps per block.  ring 1: pages are staged in shared memory by bulk
-// copies, n_warps 2 (many blocks: three of them share an SM) or 6 (few blocks); `status` is a device word
-// that is set to 4 if a wait for a copy runs out.
+// Arguments as mu_attention_decode (bfloat16 only).  n_warps 2 (many blocks: three of them share an SM) or
+// 6 (few blocks: all pages in flight at once); `status` is a device word that is set to 4 if a wait for a
+// copy runs out.
 MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k_new, long long ldk,
                                      const void* v_new, long long ldv, void* out, long long ldo, void* kv,
                                      const int* block_table, int max_pages, int page_tokens,
                                      const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads,
                                      int n_kv_heads, int head_dim, float scale, int window, int n_warps,
-                                     int ring, int* status, void* stream) {
+                                     int* status, void* stream) {
     if (n_tokens <= 0) return MU_OK;
     if (page_tokens != mu::TD_PAGE) return MU_ERR_UNSUPPORTED_SIZE;
-    // staged in shared memory: head sizes 32, 64, 96, 128; straight into registers: 32 and 64
-    if (head_dim != 32 && head_dim != 64 && !(ring && (head_dim == 96 || head_dim == 128))) return MU_ERR_UNSUPPORTED_SIZE;
+    if (head_dim != 32 && head_dim != 64 && head_dim != 96 && head_dim != 128) return MU_ERR_UNSUPPORTED_SIZE;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || window < 0) return MU_ERR_BAD_ARGUMENT;
     if (n_heads / n_kv_heads > 16) return MU_ERR_UNSUPPORTED_SIZE;
-    if (!q || !out || !kv || !block_table || !tok_pos) return MU_ERR_BAD_ARGUMENT;
+    if (!q || !out || !kv || !block_table || !tok_pos || !status) return MU_ERR_BAD_ARGUMENT;
     if ((k_new == nullptr) != (v_new == nullptr)) return MU_ERR_BAD_ARGUMENT;
     if (ldq % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)kv & 15)) return MU_ERR_ALIGNMENT;
     if (k_new && (ldk % 8 != 0 || ldv % 2 != 0 || ((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 3))) return MU_ERR_ALIGNMENT;
@@ -610,9 +351,7 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
     if (blocks > 2147483647ll) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = MU_ERR_UNSUPPORTED_SIZE;
-    if (ring) {
-        if (!status) return MU_ERR_BAD_ARGUMENT;
-        const int rows = n_heads / n_kv_heads;
+    const int rows = n_heads / n_kv_heads;
 #define MU_TR(KD, NW)                                                                                          \
     do {                                                                                                       \
         auto kernel = mu::attention_decode_ring_kernel<KD, NW, 2>;                                             \
@@ -631,36 +370,14 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
             (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, n_heads,   \
             n_kv_heads, scale, window, status);                                                                \
     } while (0)
-        // six warps with their rings and many query heads per kv head may not fit: then two warps do it
-        const size_t six = (size_t)6 * 2 * 2 * mu::TD_PAGE * head_dim * sizeof(__nv_bfloat16) +
-                           (size_t)6 * rows * (head_dim + 1) * sizeof(float);
-        const bool wide = n_warps >= 6 && six <= 200 * 1024;
-        if (head_dim == 32) { if (wide) MU_TR(2, 6); else MU_TR(2, 2); }
-        else if (head_dim == 64) { if (wide) MU_TR(4, 6); else MU_TR(4, 2); }
-        else if (head_dim == 96) MU_TR(6, 2);
-        else MU_TR(8, 2);
+    // six warps with their rings and many query heads per kv head may not fit: then two warps do it
+    const size_t six = (size_t)6 * 2 * 2 * mu::TD_PAGE * head_dim * sizeof(__nv_bfloat16) +
+                       (size_t)6 * rows * (head_dim + 1) * sizeof(float);
+    const bool wide = n_warps >= 6 && six <= 200 * 1024;
+    if (head_dim == 32) { if (wide) MU_TR(2, 6); else MU_TR(2, 2); }
+    else if (head_dim == 64) { if (wide) MU_TR(4, 6); else MU_TR(4, 2); }
+    else if (head_dim == 96) MU_TR(6, 2);
+    else MU_TR(8, 2);
 #undef MU_TR
-        return rc;
-    }
-    const int nw = n_warps >= 8 ? 8 : n_warps >= 4 ? 4 : n_warps >= 2 ? 2 : 1;
-#define MU_TD(KD, NW)                                                                                       \
-    rc = mu::launch_pdl(mu::attention_decode_tc_kernel<KD, NW>, dim3((unsigned)blocks), dim3(NW * 32), \
-        (size_t)NW * (n_heads / n_kv_heads) * (16 * KD + 1) * sizeof(float), s, 1,                          \
-        (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_new, ldk, (const __nv_bfloat16*)v_new, ldv,   \
-        (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, n_heads,    \
-        n_kv_heads, scale, window)
-#define MU_TD_W(KD)                       \
-    do {                                  \
-        if (nw == 8) MU_TD(KD, 8);        \
-        else if (nw == 4) MU_TD(KD, 4);   \
-        else if (nw == 2) MU_TD(KD, 2);   \
-        else MU_TD(KD, 1);                \
-    } while (0)
-    switch (head_dim / 16) {
-        case 2: MU_TD_W(2); break;
-        case 4: MU_TD_W(4); break;
-    }
-#undef MU_TD_W
-#undef MU_TD
     return rc;
 }

@@ -16,7 +16,6 @@
 // Formulas: include/ai/Kernels.hpp:132-161.  Head sizes 16..128 in steps of 16.
 #include "common.cuh"
 
-#include <cstdlib>
 
 #include <math.h>
 
@@ -298,8 +297,7 @@ static int launch_prefill(const void* q, long long ldq, void* out, long long ldo
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, FP_THREADS, smem) != cudaSuccess ||
             sms <= 0 || per_sm <= 0)
             return MU_ERR_LAUNCH;
-        int cap = 2;                                // measured: two blocks per SM balance better than all that fit
-        if (const char* e = getenv("MU_B200_PREFILL_BLOCKS_PER_SM")) cap = atoi(e) > 0 ? atoi(e) : cap;
+        const int cap = 2;                          // two blocks per SM balance better than all that fit
         resident = sms * (per_sm < cap ? per_sm : cap);
     }
     const long long items = (long long)n_tiles * n_heads;

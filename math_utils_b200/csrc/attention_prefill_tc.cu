@@ -25,7 +25,6 @@
 // Formulas: include/ai/Kernels.hpp:132-161.
 #include "tcgen05.cuh"
 
-#include <cstdlib>
 #include <math.h>
 
 namespace mu {

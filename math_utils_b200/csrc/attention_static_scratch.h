@@ -17,7 +17,11 @@
  * cudaMalloc, cudaFree or any other allocating routine.  Inputs and outputs
  * are still the caller's.
  *
- * Arguments are those of mu_attention without part_o and part_ml.
+ * Arguments are those of mu_attention without part_o and part_ml.  Split s of
+ * n_splits takes the keys [s * split_keys, (s + 1) * split_keys) of every
+ * sequence, and the last split goes on to the query's own position, so a
+ * split_keys that falls short of a long sequence loses no key (it only makes
+ * the last split longer).  At most 65535 heads and 65535 splits.
  *
  * Limit: n_tokens * n_heads * n_splits * (head_dim + 2) must not exceed
  * MU_STATIC_SCRATCH_FLOATS; a larger request returns MU_ERR_STATIC_SCRATCH (6)

@@ -99,6 +99,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// SMs of the current device (asked once: this library drives one device per process); 0 on failure.
+inline int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+            sms = 0;
+    }
+    return sms;
+}
+
 inline int& pdl_enabled() {
     static int enabled = 1;
     return enabled;

@@ -333,11 +333,14 @@ static int launch_skinny(const __nv_bfloat16* A, const __nv_bfloat16* W, const f
 #define MU_SK(WN, WK, CK) \
     return launch_skinny_as<MT, WN, WK, CK, TC, LN>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act, norm, s)
     const int tiles = (N + 15) / 16, k_blocks = (K + 31) / 32;
-    if (N >= 16 * 8 * 296 && K <= 2048) MU_SK(8, 1, 1);
-    else if (N >= 16 * 4 * 296) MU_SK(4, 2, 1);
-    else if (N >= 16 * 2 * 296) MU_SK(2, 4, 1);
-    else if (tiles < 74 && k_blocks >= 64) MU_SK(1, 8, 4);
-    else if (tiles < 148 && k_blocks >= 48) MU_SK(1, 8, 2);
+    const int sms = sm_count();
+    if (sms <= 0) return MU_ERR_LAUNCH;
+    const long long wave = 16ll * 2 * sms;            // output columns that two blocks per SM of one tile each cover
+    if (N >= 8 * wave && K <= 2048) MU_SK(8, 1, 1);
+    else if (N >= 4 * wave) MU_SK(4, 2, 1);
+    else if (N >= 2 * wave) MU_SK(2, 4, 1);
+    else if (2 * tiles < sms && k_blocks >= 64) MU_SK(1, 8, 4);
+    else if (tiles < sms && k_blocks >= 48) MU_SK(1, 8, 2);
     else MU_SK(1, 8, 1);
 #undef MU_SK
 }

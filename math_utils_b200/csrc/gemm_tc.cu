@@ -13,9 +13,6 @@ SplitWorkspace g_split;
 int launch_tc_split(int bn, const void* A, const void* W, const float* bias, const float* residual, void* C, int M,
                     int N, int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int out_bf16,
                     int* status, int splits, cudaStream_t s);
-int set_tc_trace_split(unsigned long long* buffer);
-
-constexpr bool TC_SPLIT_AUTO_DEFAULT = true;    // what an unset MU_B200_TC_SPLIT means (ops.py holds the same)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -75,15 +72,6 @@ static bool make_map_uncached(CUtensorMap* map, const void* base, long long rows
 
 }  // namespace mu
 
-// For measurements: a device buffer of (blocks x TC_TRACE_WORDS) 64-bit words that the kernel's roles
-// stamp with %globaltimer from now on (see tc_stamp), or null to stop.  Returns the words per block.
-MU_EXPORT int mu_gemm_tc_trace(void* buffer) {
-    unsigned long long* p = (unsigned long long*)buffer;
-    if (cudaMemcpyToSymbol(mu::g_tc_trace, &p, sizeof(p)) != cudaSuccess) return -1;
-    if (mu::set_tc_trace_split(p) != 0) return -1;
-    return mu::TC_TRACE_WORDS;
-}
-
 // Gives the product kernel room for products that are cut along K (few tiles of C, long K): `parts` takes
 // the partial tiles (float32, 16-byte aligned), `tickets` n_tickets counters that are zero now and are left
 // zero by every launch.  Without it, or where it is too small, such products run uncut.
@@ -99,9 +87,11 @@ MU_EXPORT int mu_gemm_tc_split_workspace(void* parts, long long parts_bytes, int
 // bfloat16 A [M, K] (lda) and W [N, K] (ldw): K, lda, ldw multiples of 8, bases 16-byte aligned.
 // C bfloat16 or float32 (ldc); residual float32 (ldr), may be C itself.  `status` is a device word
 // that stays 0 unless a wait inside the kernel ran out (1 producer, 2 tensor-core issuer, 3 epilogue).
+// tile: width of the tiles of C (64, 128 or 256; 0: chosen here).  splits: parts that K is cut into
+// (-1: chosen here; 0 or 1: never cut; n: n parts wherever K allows).
 MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const float* residual, void* C,
                          int M, int N, int K, long long lda, long long ldw, long long ldc, long long ldr,
-                         int act, int out_bf16, int* status, void* stream) {
+                         int act, int out_bf16, int tile, int want_splits, int* status, void* stream) {
     if (M <= 0 || N <= 0) return MU_OK;
     if (K <= 0 || !A || !W || !C || !status) return MU_ERR_BAD_ARGUMENT;
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return MU_ERR_ALIGNMENT;
@@ -111,7 +101,9 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
     cudaStream_t s = (cudaStream_t)stream;
     // Tile width: wider tiles do more products per byte loaded, but the tiles must also fill whole
     // rounds of the SMs; take the width with the best (fill of the last round) x (worth of the width).
-    const int sms = mu::sm_count() > 0 ? mu::sm_count() : 148;
+    const int sms = mu::sm_count();
+    if (sms <= 0) return MU_ERR_LAUNCH;
+    if (tile != 0 && tile != 64 && tile != 128 && tile != 256) return MU_ERR_BAD_ARGUMENT;
     const long long m_tiles = (M + mu::TC_BM - 1) / mu::TC_BM;
     int best_bn = 64;
     double best = -1.0;
@@ -129,24 +121,17 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
                                                                 lda, ldw, ldc, ldr, act, status, 1, s)           \
               : mu::launch_tc<BN, ST, KS, float, false>(A, W, bias, residual, (float*)C, M, N, K, lda, ldw, ldc,   \
                                                         ldr, act, status, 1, s))
-    if (const char* forced = getenv("MU_B200_TC_TILE")) {       // for measurements: 64, 128 or 256
-        const int f = atoi(forced);
-        if (f == 64 || f == 128 || f == 256) best_bn = f;
-    }
+    if (tile) best_bn = tile;
     // Few tiles and a long K can be cut along K so that (tiles x parts) fill the SMs.  Handing the parts over
     // (stores, a fence, a ticket, the sum) costs some microseconds, as much as a dozen 64-deep stages of
-    // products.  MU_B200_TC_SPLIT: "auto" cuts a K of 2,048 or more into parts of six stages or more,
-    // "0" never cuts, n cuts into n parts wherever K allows; unset: TC_SPLIT_AUTO_DEFAULT.
+    // products, so the rule here cuts a K of 2,048 or more into parts of six stages or more.
     int splits = 1;
     {
         const long long tiles = m_tiles * ((N + best_bn - 1) / best_bn);
         const int kb64 = (K + 63) / 64;
-        const char* asked = getenv("MU_B200_TC_SPLIT");
-        const bool automatic = asked ? (asked[0] == 'a') : mu::TC_SPLIT_AUTO_DEFAULT;
-        if (asked && !automatic) {
-            const int f = atoi(asked);
-            splits = f <= 0 ? 1 : (f < kb64 ? f : kb64);
-        } else if (automatic && tiles * 2 <= sms && kb64 >= 32) {
+        if (want_splits >= 0) {
+            splits = want_splits <= 1 ? 1 : (want_splits < kb64 ? want_splits : kb64);
+        } else if (tiles * 2 <= sms && kb64 >= 32) {
             long long want = sms / tiles;
             if (want > kb64 / 6) want = kb64 / 6;
             if (want > 8) want = 8;
@@ -161,9 +146,8 @@ MU_EXPORT int mu_gemm_tc(const void* A, const void* W, const float* bias, const 
         return mu::launch_tc_split(best_bn, A, W, bias, residual, C, M, N, K, lda, ldw, ldc, ldr, act, out_bf16, status,
                                    splits, s);
     // narrow tiles: 128-deep stages (issuing, not multiplying, sets their pace); K of a single 64 keeps 64
-    static const bool deep = !(getenv("MU_B200_TC_DEEP") && atoi(getenv("MU_B200_TC_DEEP")) == 0);
-    if (best_bn == 64) return (deep && K > 64) ? MU_TC(64, 4, 2) : MU_TC(64, 6, 1);
-    if (best_bn == 128) return (deep && K > 64) ? MU_TC(128, 3, 2) : MU_TC(128, 5, 1);
+    if (best_bn == 64) return K > 64 ? MU_TC(64, 4, 2) : MU_TC(64, 6, 1);
+    if (best_bn == 128) return K > 64 ? MU_TC(128, 3, 2) : MU_TC(128, 5, 1);
     return MU_TC(256, 4, 1);
 #undef MU_TC
 }
@@ -181,5 +165,5 @@ MU_EXPORT int mu_layernorm_gemm_tc(const float* x, const int* rows, const float*
                                    void* stream) {
     if (!normed) return MU_ERR_BAD_ARGUMENT;
     if (int e = mu_layernorm(x, rows, gamma, beta, normed, M, K, eps, 1, stream)) return e;
-    return mu_gemm_tc(normed, W, bias, residual, C, M, N, K, K, ldw, ldc, ldr, act, out_bf16, status, stream);
+    return mu_gemm_tc(normed, W, bias, residual, C, M, N, K, K, ldw, ldc, ldr, act, out_bf16, 0, -1, status, stream);
 }

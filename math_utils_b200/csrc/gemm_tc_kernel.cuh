@@ -30,27 +30,11 @@
 #pragma once
 #include "tcgen05.cuh"
 
-#include <cstdlib>
 
 namespace mu {
 
 constexpr int TC_BM = 128, TC_BK = 64, TC_EPI_WARPS = 8, TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr int TC_PATCH_PITCH = 33;               // floats per row of an epilogue patch: odd, so columns and rows both spread over the banks
-
-// Optional time stamps for measurements (mu_gemm_tc_trace): per block TC_TRACE_WORDS words of
-// %globaltimer: [0] set-up done, [1] the kernel before has ended, then for each of the block's first
-// TC_TRACE_TILES tiles: first and last load issued, first stage arrived, last product issued,
-// accumulator seen complete by the epilogue, epilogue's stores issued.
-constexpr int TC_TRACE_TILES = 4, TC_TRACE_WORDS = 2 + 6 * TC_TRACE_TILES;
-static __device__ unsigned long long* g_tc_trace = nullptr;   // one per source file that holds kernels
-
-__device__ __forceinline__ void tc_stamp(unsigned long long* trace, int word) {
-    if (trace) {
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        trace[(long long)blockIdx.x * TC_TRACE_WORDS + word] = now;
-    }
-}
 
 template <int ACT> __device__ __forceinline__ float tc_act(float x, bool to_bf16) {
     if (ACT == ACT_GELU_NEW) return to_bf16 ? gelu_new_fast(x) : gelu_new(x);
@@ -245,11 +229,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
-    unsigned long long* const trace = g_tc_trace;
-    if (threadIdx.x == 0) tc_stamp(trace, 0);
     pdl_trigger();
     pdl_wait();                                  // barriers and tensor memory are set up while the kernel before ends
-    if (threadIdx.x == 0) tc_stamp(trace, 1);
 
     // consecutive tiles share a column block of W and differ in their rows of A, so the blocks that
     // run at the same time read few distinct tiles of either operand
@@ -273,8 +254,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tma_load_2d(sm.b[s][u], &map_w, (kb * KSUB + u) * TC_BK, n0, &sm.full[s]);
                     }
                     issued = it + 1;
-                    if (local < TC_TRACE_TILES && (kb == kb_begin || kb == kb_end - 1))
-                        tc_stamp(trace, 2 + 6 * local + (kb == kb_begin ? 0 : 1));
                 }
             }
             if (!ok) {
@@ -302,7 +281,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int s = (int)(it % STAGES);
                     ok = mbar_wait(&sm.full[s], (uint32_t)((it / STAGES) & 1));
                     if (!ok) break;
-                    if (kb == kb_begin && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int u = 0; u < KSUB; ++u) {
@@ -317,7 +295,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     umma_commit(&sm.empty[s]);            // the stage is free once these have read it
                 }
                 if (ok) umma_commit(&sm.acc_full[buf]);   // the accumulator is complete
-                if (local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 3);
             }
             if (!ok) atomicExch(status, 2);
         }
@@ -361,7 +338,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 4);
             // (asking for the next block before this one is finished measured slower)
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + half * COLS);
             if constexpr (SPLIT) {
@@ -445,7 +421,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                            ldc, ldr, vec_ok && nb + 32 <= N);
             }
             }
-            if (warp == 2 && lane == 0 && local < TC_TRACE_TILES) tc_stamp(trace, 2 + 6 * local + 5);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -453,18 +428,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
-}
-
-// SMs of the current device (asked once: this library drives one device per process).
-inline int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-            sms = 0;
-    }
-    return sms;
 }
 
 // Where the parts of split products go (mu_gemm_tc_split_workspace); one device and one stream at a time

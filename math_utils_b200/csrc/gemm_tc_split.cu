@@ -4,10 +4,6 @@
 
 namespace mu {
 
-int set_tc_trace_split(unsigned long long* buffer) {
-    return cudaMemcpyToSymbol(g_tc_trace, &buffer, sizeof(buffer)) == cudaSuccess ? 0 : -1;
-}
-
 int launch_tc_split(int bn, const void* A, const void* W, const float* bias, const float* residual, void* C, int M,
                     int N, int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int out_bf16,
                     int* status, int splits, cudaStream_t s) {

@@ -34,6 +34,17 @@ class KernelError(RuntimeError):
 _lib = None
 _lock = threading.Lock()
 
+
+def _switch(name: str) -> bool:
+    return os.environ.get(name, "1") != "0"
+
+
+# Switches for measurements, read once when this module is imported:
+#   MU_B200_PDL=0         plain stream order between kernels (no programmatic dependent launch)
+#   MU_B200_ATT_TC=0      single-token attention on CUDA cores instead of mma.sync
+#   MU_B200_PREFILL_TC=0  prompt attention on mma.sync instead of tcgen05
+PDL, ATT_TC, PREFILL_TC = _switch("MU_B200_PDL"), _switch("MU_B200_ATT_TC"), _switch("MU_B200_PREFILL_TC")
+
 _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
 
 _SIGNATURES = {
@@ -44,10 +55,9 @@ _SIGNATURES = {
                      _c_int, _c_int, _c_int, _c_p],
     "mu_gemm_skinny": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                        _c_int, _c_int, _c_p],
-    "mu_gemm_tc_trace": [_c_p],
     "mu_gemm_tc_split_workspace": [_c_p, _c_ll, _c_p, _c_int],
     "mu_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
-                   _c_int, _c_int, _c_p, _c_p],
+                   _c_int, _c_int, _c_int, _c_int, _c_p, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_p, _c_int, _c_p, _c_int, _c_p],
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
@@ -64,10 +74,9 @@ _SIGNATURES = {
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
     "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
-                            _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p],
+                            _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
-                               _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p,
-                               _c_p],
+                               _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
 }
 
@@ -90,8 +99,8 @@ def library() -> ctypes.CDLL:
                         continue          # optional kernels are looked up where they are used
                     fn.argtypes = argtypes
                     fn.restype = _c_int
-                if os.environ.get("MU_B200_PDL", "1") == "0":
-                    lib.mu_set_pdl(0)         # plain stream order between the single-token kernels
+                if not PDL:
+                    lib.mu_set_pdl(0)         # plain stream order between kernels
                 _lib = lib
     return _lib
 
@@ -150,7 +159,7 @@ def _i32(t: Optional[torch.Tensor], name: str) -> None:
 
 def set_pdl(enabled: bool) -> None:
     """Switches programmatic stream serialization of the launches on or off
-    (on unless MU_B200_PDL=0): with it a kernel may start, and fetch what no
+    (on unless MU_B200_PDL=0 when the module was imported): with it a kernel may start, and fetch what no
     kernel of the step writes, while the kernel before it ends.  Launches
     already recorded in a CUDA graph keep the mode they were recorded with."""
     library().mu_set_pdl(1 if enabled else 0)
@@ -201,9 +210,6 @@ def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Ten
         raise KernelError("embedding tables must be contiguous")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
-    if _recorder is not None:
-        _recorder.add_embed(ids, positions, table, pos_table, out)
-        return out
     _check(library().mu_embed(_ptr(ids), _ptr(positions), _ptr(table), _ptr(pos_table), _ptr(out),
                               n, hidden, _is_bf16(table), _stream()), "embed")
     return out
@@ -213,7 +219,6 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor]
               out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """LayerNorm of float32 rows (optionally the rows that ``rows`` picks)."""
-    _not_while_recording("layernorm")
     _need_cuda(x, gamma, beta, rows)
     _i32(rows, "rows")
     if x.dtype != torch.float32 or not x.is_contiguous():
@@ -266,7 +271,6 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
               out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """out = act(a @ w^T + bias) + residual on CUDA cores, any shape, any of the
     two dtypes; with float32 operands this is the true 32-bit product."""
-    _not_while_recording("gemm_simt")
     m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
     _check(library().mu_gemm_simt(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
@@ -288,19 +292,11 @@ def status_word(device) -> torch.Tensor:
     return word
 
 
-# Products of few tiles cut along k (mu_gemm_tc): "auto", "0" or a number of parts; the default is the
-# library's (TC_SPLIT_AUTO_DEFAULT in gemm_tc.cu).
-_TC_SPLIT = os.environ.get("MU_B200_TC_SPLIT", "auto")
-
-
 def _deep_to_tensor_cores(n: int, k: int) -> bool:
     """Whether a product of 33 to 64 rows whose weight is deeper than wide goes to the tensor-core
-    kernel (which then cuts k) instead of the few-rows kernel.  Measured at 64 rows: 768 x 3,072
-    11.0 us few-rows against 13.8 cut; 1,024 x 4,096 11.8 against 14.6; 1,600 x 6,400 30.5 against
-    17.9: the cut pays from some six million weights on."""
-    if _TC_SPLIT.startswith("a"):
-        return n * k >= 6_000_000
-    return _TC_SPLIT not in ("0", "")
+    kernel (which then cuts k) instead of the few-rows kernel: the cut pays from some six million
+    weights on."""
+    return n * k >= 6_000_000
 
 
 def _split_workspace(device) -> None:
@@ -308,10 +304,24 @@ def _split_workspace(device) -> None:
     long k: a batch of 33 to 128 single tokens): partial tiles for one tile per
     SM at the widest tile, and a ticket per tile.  Set once per device, at the
     first use of a kernel with a status word, hence never inside a capture."""
-    parts = scratch("gemm_tc_parts", device, _sm_count(device) * 128 * 256, torch.float32)
+    parts = scratch("gemm_tc_parts", device, sm_count(device) * 128 * 256, torch.float32)
     tickets = zeroed_workspace("gemm_tc_tickets", device, 4 * 1024)
     _check(library().mu_gemm_tc_split_workspace(parts.data_ptr(), parts.numel() * 4, tickets.data_ptr(),
                                                 tickets.numel() // 4), "gemm_tc_split_workspace", launches=0)
+
+
+_WAITS = {1: "tensor-core product: loads", 2: "tensor-core product: tensor cores",
+          3: "tensor-core product: epilogue", 4: "single-token attention: a page copy",
+          5: "prompt attention: loads", 6: "prompt attention: tensor cores", 7: "prompt attention: softmax"}
+
+
+def raise_status(device, code: int) -> None:
+    """Clears the status word and raises for the wait that ran out."""
+    word = _status.get(str(torch.device(device)))
+    if word is not None:
+        word.zero_()
+    raise KernelError(f"a kernel gave up a bounded wait ({_WAITS.get(code, f'code {code}')}); the results of "
+                      "the steps since the last check are not valid")
 
 
 def check_status(device="cuda:0") -> None:
@@ -321,9 +331,7 @@ def check_status(device="cuda:0") -> None:
     if word is not None:
         code = int(word.item())
         if code != 0:
-            word.zero_()
-            raise KernelError(f"a tensor-core product kernel gave up waiting (role {code}: 1 loads, 2 tensor "
-                              "cores, 3 epilogue); its results are not valid")
+            raise_status(device, code)
 
 
 def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -334,27 +342,18 @@ def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
             act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """The product on the tcgen05 tensor cores (TMA loads, accumulator in tensor memory)."""
-    _not_while_recording("gemm_tc")
+            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+            tile: int = 0, splits: int = -1) -> torch.Tensor:
+    """The product on the tcgen05 tensor cores (TMA loads, accumulator in tensor memory).
+    ``tile``: width of the output tiles (64, 128, 256; 0: the library chooses); ``splits``: parts that k
+    is cut into (-1: the library chooses; 0 or 1: none)."""
     m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
     _check(library().mu_gemm_tc(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
         out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
-        _is_bf16(out), _ptr(status_word(a.device)), _stream()), ("gemm_tc({}x{}x{})", m, n, k))
+        _is_bf16(out), int(tile), int(splits), _ptr(status_word(a.device)), _stream()),
+        ("gemm_tc({}x{}x{})", m, n, k))
     return out
-
-
-def gemm_tc_trace(buffer: Optional[torch.Tensor]) -> int:
-    """For measurements: from now on every gemm_tc block stamps the device clock
-    into ``buffer`` (int64, blocks x the returned number of words: set-up done,
-    wait for the kernel before over, then per tile first/last load issued, first
-    stage arrived, last product issued, accumulator complete, stores issued);
-    ``None`` stops it."""
-    words = library().mu_gemm_tc_trace(_ptr(buffer))
-    if words < 0:
-        raise KernelError("gemm_tc_trace: the trace pointer could not be set")
-    return words
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -378,7 +377,6 @@ def kv_append(k: torch.Tensor, v: torch.Tensor, tok_pos, tok_seq, block_table: t
     views, unit inner stride) into their pages (values transposed: dimension-major
     within a page).  ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of
     runs of tokens of one sequence) lets prompt values be written a tile at a time."""
-    _not_while_recording("kv_append")
     _need_cuda(k, v, tok_pos, tok_seq, block_table, kv_pages)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -399,7 +397,6 @@ def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_
               part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of each query token ([T, n_heads * head_dim] view) over the
     cached keys first..its position; writes ``out`` [T, n_heads * head_dim]."""
-    _not_while_recording("attention")
     _need_cuda(q, out, kv_pages, block_table, tok_pos, tok_seq, part_o, part_ml)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -480,6 +477,10 @@ class NormedInput:
             self._value = layernorm(self.x, self.gamma, self.beta, self.eps, self.out_dtype, rows=self.rows)
         return self._value
 
+    def materialize_copy(self) -> torch.Tensor:
+        """The norm computed for an onlooker; what a product does with this input stays as it was."""
+        return layernorm(self.x, self.gamma, self.beta, self.eps, self.out_dtype, rows=self.rows)
+
 
 def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, out_dtype) -> torch.Tensor:
     """act(LayerNorm(x) @ w^T + bias) + residual with the norm made inside the product kernel."""
@@ -499,25 +500,31 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
     return out
 
 
-_sm_counts = {}
+sm_counts = {}
 
 
-def _sm_count(device) -> int:
-    n = _sm_counts.get(device)
+def sm_count(device) -> int:
+    n = sm_counts.get(device)
     if n is None:
-        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+        n = sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
     return n
+
+
+def decode_ok(head_dim: int) -> bool:
+    """Whether the one-launch single-token attention kernels take this head size
+    (multiples of 16 up to 256: their key rows are read in 16-byte pieces); other
+    sizes append first and then run the general kernel."""
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
 def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv_heads: int,
                  head_dim: int) -> bool:
     """Whether the tensor-core single-token attention takes this case (else the
-    CUDA-core kernel does): bfloat16, head sizes 32, 64, 96 and 128 (96 and 128 only staged in shared memory), at most 16 query
+    CUDA-core kernel does): bfloat16, head sizes 32, 64, 96 and 128, at most 16 query
     heads per kv head, 16-byte aligned rows.  MU_B200_ATT_TC=0 switches it off."""
-    if os.environ.get("MU_B200_ATT_TC", "1") == "0":
+    if not ATT_TC:
         return False
-    staged = os.environ.get("MU_B200_ATT_RING", "1") != "0"
-    if kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim not in ((32, 64, 96, 128) if staged else (32, 64)):
+    if kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim not in (32, 64, 96, 128):
         return False
     if n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 16:
         return False
@@ -530,32 +537,24 @@ def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv
 def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
                      out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, page_tokens: int,
                      tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                     window: int, n_splits: int) -> torch.Tensor:
+                     window: int, n_splits: int, warps: int = 0) -> torch.Tensor:
     """Single-token attention, one launch: appends ``k_new`` / ``v_new`` (if
     given), attends page by page, merges in shared memory.  ``n_splits``: how
     many warps share a sequence's pages (its page count is a good choice; at most
-    16 are used).  ``tok_seq`` None: token t is sequence t."""
-    if _recorder is not None:
-        _recorder.add_attention(q, k_new, v_new, out, kv_pages, block_table, page_tokens, tok_pos, tok_seq,
-                                n_heads, n_kv_heads, head_dim, scale, window)
-        return out
+    16 are used).  ``tok_seq`` None: token t is sequence t.  ``warps``: warps per
+    block (tensor-core kernel: 2 or 6; CUDA-core kernel: an upper bound); 0: chosen here."""
     _need_cuda(q, k_new, v_new, out, kv_pages, block_table, tok_pos, tok_seq)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     n_tokens = q.shape[0]
     if decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens, n_heads, n_kv_heads, head_dim):
-        ring = os.environ.get("MU_B200_ATT_RING", "1") != "0"
-        warps = int(os.environ.get("MU_B200_ATT_TC_WARPS", "0"))
-        if not warps:
-            if ring:          # many blocks: small ones, three to an SM; few blocks: all pages in flight at once
-                warps = 2 if n_tokens * n_kv_heads >= 2 * _sm_count(q.device) else 6
-            else:
-                warps = min(8, max(1, int(n_splits)))
+        if not warps:         # many blocks: small ones, three to an SM; few blocks: all pages in flight at once
+            warps = 2 if n_tokens * n_kv_heads >= 2 * sm_count(q.device) else 6
         _check(library().mu_attention_decode_tc(
             _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
             v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
             _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
-            n_heads, n_kv_heads, head_dim, float(scale), int(window), warps, int(ring),
+            n_heads, n_kv_heads, head_dim, float(scale), int(window), int(warps),
             _ptr(status_word(q.device)), _stream()),
             ("attention_decode_tc(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
         return out
@@ -563,7 +562,8 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
         v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
         _ptr(block_table), block_table.shape[1], page_tokens, _ptr(tok_pos), _ptr(tok_seq), n_tokens,
-        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), _is_bf16(kv_pages), _stream()),
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), int(n_splits), int(warps), _is_bf16(kv_pages),
+        _stream()),
         ("attention_decode(heads={}/{}, head_dim={})", n_heads, n_kv_heads, head_dim))
     return out
 
@@ -596,7 +596,7 @@ def prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_tokens
     """Whether the tcgen05 prompt attention takes this case: bfloat16, head size
     64, pages of 64, query and output rows 16-byte aligned.  MU_B200_PREFILL_TC=0
     switches it off (the mma.sync kernel then runs)."""
-    if os.environ.get("MU_B200_PREFILL_TC", "1") == "0":
+    if not PREFILL_TC:
         return False
     return (q.dtype == torch.bfloat16 and head_dim == 64 and page_tokens == 64 and q.stride(0) % 8 == 0
             and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)
@@ -687,17 +687,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     dtype and the shape.  float32 operands always take the CUDA-core kernel.
     ``x`` may be a ``NormedInput``: with few rows and bfloat16 weights the norm is
     made inside the product kernel, otherwise it is computed first."""
-    if _recorder is not None:
-        normed = isinstance(x, NormedInput)
-        m = x.n_rows if normed else x.shape[0]
-        if out is None:
-            want = out_dtype or (x.out_dtype if normed else x.dtype)
-            out = torch.empty((m, weight.shape[0]), dtype=want, device=weight.device)
-        _recorder.add_gemm(x, weight, bias, act, residual, out)
-        return out
     if isinstance(x, NormedInput):
-        if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 16
-                and x.x.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
+        k_in = x.x.shape[1]
+        # the few-rows kernel keeps the normed rows (8 or 16 of them), gamma and beta in shared memory
+        fits = 8 * (1 if x.n_rows <= 8 else 2) * (k_in + 8) * 2 + 8 * k_in <= SKINNY_LN_SMEM
+        if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 16 and fits
+                and k_in % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
             return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
         fused = _layernorm_gemm_tc(x, weight, bias, act, residual, out, out_dtype)
@@ -744,150 +739,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
                                   _is_bf16(out), _stream()), ("gemm_skinny({}x{}x{})", m, n, k))
     elif tensor_cores:
         _check(lib.mu_gemm_tc(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
-                              _is_bf16(out), status_word(x.device).data_ptr(), _stream()),
+                              _is_bf16(out), 0, -1, status_word(x.device).data_ptr(), _stream()),
                ("gemm_tc({}x{}x{})", m, n, k))
     else:
         _check(lib.mu_gemm_simt(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
                                 _is_bf16(x), _is_bf16(out), _stream()), ("gemm_simt({}x{}x{})", m, n, k))
     return out
-
-
-# ---------------------------------------------------- a single-token step as one recorded program
-class NotRecordable(RuntimeError):
-    """The step contains an operation the persistent step kernel does not have."""
-
-
-class ProgramOp(ctypes.Structure):
-    """One operation of a recorded step; the layout is ``mu::ProgramOp`` of decode_program.cu."""
-    _fields_ = (
-        [(n, _c_int) for n in ("type", "M", "N", "K", "act", "out_bf16", "has_ln", "ksplit")]
-        + [(n, _c_p) for n in ("a", "w", "bias", "residual", "c", "ln_x", "ln_rows", "ln_gamma", "ln_beta")]
-        + [(n, _c_ll) for n in ("lda", "ldw", "ldc", "ldr", "ln_ldx")]
-        + [("part", _c_p), ("tickets", _c_p), ("ln_eps", _c_f), ("scale", _c_f)]
-        + [(n, _c_p) for n in ("q", "k_new", "v_new", "out", "kv", "block_table", "tok_pos")]
-        + [(n, _c_ll) for n in ("ldq", "ldk", "ldv", "ldo")]
-        + [(n, _c_int) for n in ("max_pages", "n_heads", "n_kv_heads", "head_dim", "window", "n_tokens",
-                                 "hidden", "table_bf16")]
-        + [(n, _c_p) for n in ("ids", "table", "pos_table", "x")])
-
-
-OP_EMBED, OP_GEMM, OP_ATTENTION = 1, 2, 3
-PROGRAM_MAX_ROWS = 16
-
-
-class StepProgram:
-    """The operations of one single-token step, recorded from the model's own
-    forward pass, and everything they point at.  ``run`` executes them in one
-    cooperative kernel."""
-
-    def __init__(self, device):
-        self.device = torch.device(device)
-        self.ops = []
-        self.keep = []                 # tensors the records point into
-        self.max_rows = 1
-        self.max_ln_k = 0
-        self.n_blocks = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.device_ops = None
-        self.barrier = torch.zeros(2, dtype=torch.int32, device=self.device)
-
-    def _hold(self, *tensors):
-        self.keep.extend(t for t in tensors if t is not None)
-
-    def add_embed(self, ids, positions, table, pos_table, out):
-        op = ProgramOp()
-        op.type, op.n_tokens, op.hidden, op.table_bf16 = OP_EMBED, ids.numel(), table.shape[1], _is_bf16(table)
-        op.ids, op.tok_pos, op.table, op.pos_table, op.x = _ptr(ids), _ptr(positions), _ptr(table), _ptr(pos_table), _ptr(out)
-        self._hold(ids, positions, table, pos_table, out)
-        self.ops.append(op)
-
-    def add_gemm(self, x, w, bias, act, residual, out):
-        op = ProgramOp()
-        normed = isinstance(x, NormedInput)
-        m = x.n_rows if normed else x.shape[0]
-        n, k = w.shape
-        if w.dtype != torch.bfloat16 or m > PROGRAM_MAX_ROWS or k % 8 or w.stride(0) % 8 or w.data_ptr() % 16:
-            raise NotRecordable(f"product {m}x{n}x{k} of {w.dtype}")
-        op.type, op.M, op.N, op.K = OP_GEMM, m, n, k
-        op.act, op.out_bf16, op.has_ln = ACT_CODES[act], _is_bf16(out), int(normed)
-        if normed:
-            if (x.x.dtype != torch.float32 or x.x.stride(1) != 1 or x.x.stride(0) % 4 or x.x.data_ptr() % 16
-                    or k > 2048 or x.out_dtype != torch.bfloat16):
-                raise NotRecordable("a norm the step kernel cannot fold in")
-            op.ln_x, op.ln_ldx, op.ln_rows = _ptr(x.x), x.x.stride(0), _ptr(x.rows)
-            op.ln_gamma, op.ln_beta, op.ln_eps = _ptr(x.gamma), _ptr(x.beta), float(x.eps)
-            self.max_ln_k = max(self.max_ln_k, k)
-            self._hold(x.x, x.rows, x.gamma, x.beta)
-        else:
-            if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
-                raise NotRecordable("activations the step kernel cannot read")
-            op.a, op.lda = _ptr(x), x.stride(0)
-            self._hold(x)
-        op.w, op.ldw, op.bias = _ptr(w), w.stride(0), _ptr(bias)
-        op.residual, op.ldr = _ptr(residual), residual.stride(0) if residual is not None else 0
-        op.c, op.ldc = _ptr(out), out.stride(0)
-        # narrow outputs: several blocks share a tile, each a slice of K with at least a k-block per warp
-        tiles, k_blocks = -(-n // 16), -(-k // 32)
-        op.ksplit = max(1, min(self.n_blocks // tiles, k_blocks // 8, 8)) if tiles * 2 <= self.n_blocks else 1
-        if op.ksplit > 1:
-            part = torch.empty(tiles * op.ksplit * 16 * 16, dtype=torch.float32, device=self.device)
-            tickets = torch.zeros(tiles, dtype=torch.int32, device=self.device)
-            op.part, op.tickets = _ptr(part), _ptr(tickets)
-            self._hold(part, tickets)
-        self.max_rows = max(self.max_rows, m)
-        self._hold(w, bias, residual, out)
-        self.ops.append(op)
-
-    def add_attention(self, q, k_new, v_new, out, kv_pages, block_table, page_tokens, tok_pos, tok_seq,
-                      n_heads, n_kv_heads, head_dim, scale, window):
-        if (kv_pages.dtype != torch.bfloat16 or page_tokens != 64 or head_dim > 128 or head_dim % 16
-                or tok_seq is not None or q.shape[0] > PROGRAM_MAX_ROWS):
-            raise NotRecordable("attention the step kernel cannot run")
-        op = ProgramOp()
-        op.type, op.n_tokens = OP_ATTENTION, q.shape[0]
-        op.q, op.ldq, op.out, op.ldo = _ptr(q), q.stride(0), _ptr(out), out.stride(0)
-        op.k_new, op.ldk = _ptr(k_new), k_new.stride(0) if k_new is not None else 0
-        op.v_new, op.ldv = _ptr(v_new), v_new.stride(0) if v_new is not None else 0
-        op.kv, op.block_table, op.tok_pos, op.max_pages = _ptr(kv_pages), _ptr(block_table), _ptr(tok_pos), block_table.shape[1]
-        op.n_heads, op.n_kv_heads, op.head_dim, op.window, op.scale = n_heads, n_kv_heads, head_dim, int(window), float(scale)
-        self._hold(q, k_new, v_new, out, kv_pages, block_table, tok_pos)
-        self.ops.append(op)
-
-    def finish(self) -> "StepProgram":
-        size = ctypes.sizeof(ProgramOp)
-        if library().mu_decode_program_op_size() != size:
-            raise KernelError("the recorded-step layout of the Python side and of the kernel library differ")
-        raw = b"".join(bytes(op) for op in self.ops)
-        self.device_ops = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
-        self.dyn_smem = 16 * (self.max_ln_k + 8) * 2 if self.max_ln_k else 0
-        return self
-
-    def run(self, trace: Optional[torch.Tensor] = None) -> None:
-        """``trace``: optional int64 [2 * n_ops] that receives, per operation, when
-        block 0 began and ended its share (nanoseconds of the device's timer)."""
-        lib = library()
-        lib.mu_decode_program.argtypes = [_c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p]
-        lib.mu_decode_program.restype = _c_int
-        _check(lib.mu_decode_program(_ptr(self.device_ops), len(self.ops), self.max_rows, self.dyn_smem,
-                                     _ptr(self.barrier), _ptr(status_word(self.device)), _ptr(trace), _stream()),
-               "decode_program")
-
-
-_recorder: Optional[StepProgram] = None
-
-
-def begin_record(device) -> None:
-    """From here on ``embed``, ``linear`` and ``attention_decode`` add to a
-    program instead of launching; any other kernel raises ``NotRecordable``."""
-    global _recorder
-    _recorder = StepProgram(device)
-
-
-def end_record() -> Optional[StepProgram]:
-    global _recorder
-    rec, _recorder = _recorder, None
-    return rec
-
-
-def _not_while_recording(name: str) -> None:
-    if _recorder is not None:
-        raise NotRecordable(name)

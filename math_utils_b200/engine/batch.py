@@ -75,9 +75,19 @@ class StepContext:
     max_q_len: int
     max_kv_len: int                       # longest sequence after this step
     workspace: dict = field(default_factory=dict)
-    split_target_warps: int = 148 * 8
     q_tiles: Optional[torch.Tensor] = None  # [n, 2] int32: (first flat token, count <= 64) of each query tile
     q_tiles_wide: Optional[torch.Tensor] = None  # the same in tiles of up to 128 queries
+    trace: Optional[object] = None          # callable(name, tensor): told every named intermediate result
+    tag: str = ""                           # prefix of the names noted now ("h.3." inside layer run 3)
+
+    def note(self, name: str, tensor) -> None:
+        """Hands an intermediate result to the step's trace, if there is one.  A
+        ``NormedInput`` is computed for the trace; the product that takes it still
+        makes its own."""
+        if self.trace is not None:
+            if hasattr(tensor, "materialize"):
+                tensor = tensor.materialize_copy()
+            self.trace(self.tag + name, tensor)
 
     @property
     def is_decode(self) -> bool:
@@ -125,7 +135,7 @@ class StepContext:
         if not self.is_decode:
             return 1, 0, None, None
         items = self.n_tokens * n_heads
-        by_fill = -(-self.split_target_warps // items)
+        by_fill = -(-(8 * self.runtime.ops.sm_count(self.runtime.device)) // items)      # eight warps per SM
         by_keys = max(1, -(-self.max_kv_len // 64))
         n_splits = max(1, min(by_fill, by_keys))
         if n_splits == 1:
@@ -139,7 +149,7 @@ class StepContext:
 
 
 def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts: Sequence[int],
-                  ring: PinnedRing, workspace: dict) -> StepContext:
+                  ring: PinnedRing, workspace: dict, trace=None) -> StepContext:
     """Packs the step's index arrays and sends them to the device."""
     q_lens = [len(e.tokens) for e in entries]
     n_tokens, n_seqs = sum(q_lens), len(entries)
@@ -200,4 +210,4 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
         q_tiles_wide=part(6, 2 * len(wide)).view(len(wide), 2) if wide else None,
         slots=[e.slot for e in entries], starts=list(starts), q_lens=q_lens,
         max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
-        workspace=workspace)
+        workspace=workspace, trace=trace)

@@ -21,7 +21,6 @@ Three ways to drive it:
 """
 from __future__ import annotations
 
-import os
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -33,8 +32,7 @@ from .batch import StepContext
 
 class DecodeSession:
     def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
-                 request_ids: Sequence[int], kv_bound: Optional[int] = None, use_program: Optional[bool] = None,
-                 pipelined: bool = False):
+                 request_ids: Sequence[int], kv_bound: Optional[int] = None, pipelined: bool = False):
         """``pipelined``: two graphs that take turns; each starts with the copy of
         the step's positions from a pinned buffer of its own and ends with the
         copy of the sampled tokens to a pinned buffer of its own, so a step is
@@ -88,11 +86,8 @@ class DecodeSession:
             self._done = [torch.cuda.Event() for _ in range(2)]
             self._unread = [False, False]
             self._first_tokens = torch.zeros(n, dtype=torch.int32, pin_memory=True)
-        self.program = None
-        # One persistent kernel for the whole step instead of a graph of ~60 launches.  Measured on
-        # GPT-2 small at batch 8 it is the slower of the two (0.65 ms against 0.41 ms: its 61
-        # grid-wide barriers cost 2.5-5 us each), so it is off unless asked for.
-        self.use_program = (os.environ.get("MU_B200_PROGRAM", "0") == "1") if use_program is None else use_program
+            # the kernels' status word as each step left it, read with the step's samples
+            self._status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.launches_per_step = 0
         self.logits: Optional[torch.Tensor] = None
         self._tables_host = [None] * len(self.tables_shape)
@@ -174,38 +169,20 @@ class DecodeSession:
         step only)."""
         self._done[ticket].synchronize()
         self._unread[ticket] = False
+        code = int(self._status_host[ticket][0])
+        if code != 0:
+            self.model.runtime.ops.raise_status(self.model.runtime.device, code)
         return self._out_host[ticket].tolist()
 
     # ------------------------------------------------------------------- steps
-    def _record(self) -> None:
-        """Tries to record the model's forward pass of this step as one program
-        for the persistent step kernel; a step with an operation that kernel
-        does not have keeps launching its kernels one by one."""
-        ops = self.model.runtime.ops
-        self.program = None
-        if not self.use_program:
-            return
-        try:
-            ops.begin_record(self.model.runtime.device)
-            self.logits = self.model.forward(self.ctx, self.cache)
-            self.program = ops.end_record().finish()
-        except ops.NotRecordable:
-            ops.end_record()
-            self.program = None
-
     def _run_once(self) -> None:
         ops = self.model.runtime.ops
-        if self.program is not None:
-            self.program.run()
-            logits = self.logits
-        else:
-            logits = self.model.forward(self.ctx, self.cache)
-            self.logits = logits
+        logits = self.logits = self.model.forward(self.ctx, self.cache)
         feed = (self.token_ids, self.tok_pos, self.kv_bound - 1)     # samples become the next step's inputs
         if self.params.greedy:
             ops.argmax(logits, out=self.next_tokens, feed=feed)
         else:
-            ops.sample(logits, self.params.temperature, self.params.top_k, self.params.seed,
+            ops.sample(logits, self.params.temperature, self.params.kept, self.params.seed,
                        self.request_ids, self.draws, out=self.next_tokens, feed=feed)
 
     def capture(self) -> None:
@@ -217,7 +194,6 @@ class DecodeSession:
             raise RuntimeError("feed() the real tokens and positions before the first launch: the set-up run "
                                "writes keys and values at the positions it is given")
         ops = self.model.runtime.ops
-        self._record()
         saved = (self.token_ids.clone(), self.tok_pos.clone(), self.draws.clone())
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -232,6 +208,7 @@ class DecodeSession:
                 ops.copy_async(self.tok_pos, self._pos_host[turn])
                 self._run_once()
                 ops.copy_async(self._out_host[turn], self.next_tokens)
+                ops.copy_async(self._status_host[turn], ops.status_word(self.model.runtime.device))
             self._turn_graphs = [self._record_graph(lambda turn=turn: turn_body(turn), side) for turn in range(2)]
         else:
             self.graph = self._record_graph(self._run_once, side)

@@ -63,6 +63,12 @@ class RequestState:
     produced: List[int] = field(default_factory=list)
     finished: bool = False
     reason: str = ""
+    held: int = 0                   # positions its slot held before this prompt (a conversation's earlier turns)
+
+    @property
+    def positions(self) -> int:
+        """Positions the sequence has once everything produced so far is fed."""
+        return self.held + len(self.prompt) + len(self.produced)
 
 
 def take_token(state: RequestState, token: int, stop_ids, max_tokens: int, context: int) -> bool:
@@ -75,7 +81,7 @@ def take_token(state: RequestState, token: int, stop_ids, max_tokens: int, conte
     if len(state.produced) >= max_tokens:
         state.finished, state.reason = True, "max_tokens"
         return False
-    if len(state.prompt) + len(state.produced) >= context:
+    if state.positions >= context:
         # the reference samples only while cache.length < context (src/LLM.cpp:696)
         state.finished, state.reason = True, "context"
         return False
@@ -91,7 +97,7 @@ def run_batch(step: Callable, sample: Callable, acquire: Callable, release: Call
     try:
         live = []
         for k, st in enumerate(states):
-            if max_tokens <= 0 or len(st.prompt) >= context:
+            if max_tokens <= 0 or st.held + len(st.prompt) >= context:
                 st.finished, st.reason = True, "max_tokens" if max_tokens <= 0 else "context"
                 continue
             slots[k] = acquire()
@@ -116,7 +122,7 @@ def run_batch(step: Callable, sample: Callable, acquire: Callable, release: Call
 
 
 def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[RequestState], stop_ids,
-                      max_tokens: int, context: int) -> None:
+                      max_tokens: int, context: int, kept_slots: Optional[Sequence[int]] = None) -> None:
     """The same batch as ``run_batch``, with the single-token steps replayed
     from CUDA graphs (``DecodeSession``, pipelined).  The prompts run as one
     eager step.  Then the host stays one step behind the device: each step's
@@ -130,24 +136,36 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
     of another sequence is touched) and keeps its slot until the batch has
     halved, when the rest moves to a smaller graph.  With a windowed cache group
     the host does not run behind (pages are given back as a sequence moves on,
-    and the page lists on the device must match the step that reads them)."""
+    and the page lists on the device must match the step that reads them).
+
+    ``kept_slots``: the slot of each request, taken by the caller, which may
+    already hold ``state.held`` positions (a conversation); such slots are not
+    given back, and at the end each holds exactly what was fed and emitted (see
+    ``settle``)."""
     from .decode_session import session_for
     ops = model.runtime.ops
     slots = {}
     try:
         live = []
         for k, st in enumerate(states):
-            if max_tokens <= 0 or len(st.prompt) >= context:
+            if max_tokens <= 0 or st.held + len(st.prompt) >= context:
                 st.finished, st.reason = True, "max_tokens" if max_tokens <= 0 else "context"
                 continue
-            slots[k] = cache.acquire()
+            slots[k] = kept_slots[k] if kept_slots is not None else cache.acquire()
             live.append(k)
         if not live:
             return
+
+        def leave(k):
+            slot = slots.pop(k)
+            if kept_slots is None:
+                cache.release(slot)
+
         sampler = Sampler(params, [states[k].index for k in live], model.runtime.device, ops)
         logits = model.step(cache, [StepEntry(slots[k], list(states[k].prompt), [len(states[k].prompt) - 1])
                                     for k in live])
         tokens = sampler.sample(logits).cpu().tolist()
+        check_kernels(model)
         draws = {k: 1 for k in live}
         feed = {}
         for k, tok in zip(list(live), tokens):
@@ -155,9 +173,11 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
                 feed[k] = int(tok)
             else:
                 live.remove(k)
-                cache.release(slots.pop(k))
+                leave(k)
         windowed = any(g.spec.window > 0 for g in cache.kv_groups)
-        depth = 1 if windowed else 2                     # steps launched and not yet read
+        # steps launched and not yet read: two, unless a step that ran ahead of the news of its sequence's end
+        # could not be taken back (pages given back by a window; fixed-size state of a slot that is kept)
+        depth = 1 if windowed or (kept_slots is not None and cache.state_groups) else 2
         while live:
             members = list(live)                         # the graph's batch; some may park later
             session = session_for(model, cache, params, len(members))
@@ -170,10 +190,42 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
             while run.in_flight:                         # steps launched before the batch halved or ended
                 run.read()
             for k in run.parked:
-                cache.release(slots.pop(k))
+                leave(k)
+        if kept_slots is not None:
+            settle(model, cache, states, kept_slots, context)
     finally:
-        for slot in slots.values():
-            cache.release(slot)
+        if kept_slots is None:
+            for slot in slots.values():
+                cache.release(slot)
+
+
+def check_kernels(model) -> None:
+    """Raises if a kernel gave up one of its bounded waits since the last look; called where the host
+    has just waited for the device anyway."""
+    ops = model.runtime.ops
+    if ops is not None:
+        ops.check_status(model.runtime.device)
+
+
+def settle(model, cache, states: Sequence[RequestState], slots: Sequence[int], context: int) -> None:
+    """Leaves every kept slot holding exactly its earlier turns, this prompt and
+    every emitted token, as the reference's conversation does (it forwards each
+    token it emits, include/ai/LLM.hpp:226-243; a stop token is never fed).  The
+    loop above does not feed a request's last token when the end was known in
+    advance, and may have stepped a stop token before it saw it: the first is
+    fed here with nothing wanted, the second is cut off (its key and value stay
+    in the page, past the length, and are overwritten by the next turn)."""
+    late = []
+    for st, slot in zip(states, slots):
+        have, want = cache.length(slot), st.positions
+        if have > want:
+            cache.truncate(slot, want)
+        elif have < want:
+            if have != want - 1 or not st.produced:
+                raise RuntimeError(f"slot {slot} holds {have} positions, the conversation has {want}")
+            late.append(StepEntry(slot, [st.produced[-1]], []))
+    if late:
+        model.step(cache, late)
 
 
 class _GraphedStretch:
@@ -217,7 +269,7 @@ class _GraphedStretch:
             self.stepped_at[i] = positions[i]
             self.unread[k] += 1
             made = len(st.produced) + self.unread[k]                    # if none of the unread samples is a stop token
-            if made < self.max_tokens and len(st.prompt) + made < self.context:
+            if made < self.max_tokens and st.held + len(st.prompt) + made < self.context:
                 positions[i] += 1
                 goes_on.append(k)
             # else this step's sample is its last, whatever it is: it stays where it is
@@ -229,7 +281,7 @@ class _GraphedStretch:
         if not self.in_flight:                           # cannot be: a live request is running or has a step unread
             raise RuntimeError("the generation loop has live requests and nothing to wait for")
         ticket, stepped = self.in_flight.popleft()
-        tokens = self.session.read_step(ticket)
+        tokens = self.session.read_step(ticket)              # raises if a kernel of the step gave up a wait
         for k in stepped:
             self.unread[k] -= 1
             if self.states[k].finished:                  # the step ran ahead of the news of its end
@@ -246,6 +298,34 @@ class _GraphedStretch:
                 if k in self.running:
                     self.running.remove(k)
                     self.positions[self.place[k]] = self.stepped_at[self.place[k]]
+
+
+def run_requests(model, cache, params: SamplingParams, states: Sequence[RequestState], stop_ids, max_tokens: int,
+                 context: int, kept_slots: Optional[Sequence[int]] = None, use_graph: bool = True) -> None:
+    """One batch through the loop that fits the model: graph replay where every
+    part can be replayed, eager steps otherwise.  Everything that generates
+    (``generate``, ``LLM.prompt``, the command line) comes through here."""
+    if use_graph and getattr(model, "graph_safe", True):
+        run_batch_graphed(model, cache, params, states, stop_ids, max_tokens, context, kept_slots)
+        return
+    ops = model.runtime.ops
+    sampler = Sampler(params, [s.index for s in states], model.runtime.device, ops)
+    n = len(states)
+
+    def sample(logits, rows):
+        tokens = sampler.sample(logits, None if len(rows) == n else rows).cpu().tolist()
+        check_kernels(model)
+        return tokens
+
+    if kept_slots is None:
+        run_batch(lambda entries: model.step(cache, entries), sample, cache.acquire, cache.release,
+                  states, stop_ids, max_tokens, context)
+        return
+    taken = iter([slot for st, slot in zip(states, kept_slots)
+                  if max_tokens > 0 and st.held + len(st.prompt) < context])
+    run_batch(lambda entries: model.step(cache, entries), sample, lambda: next(taken), lambda slot: None,
+              states, stop_ids, max_tokens, context)
+    settle(model, cache, states, kept_slots, context)
 
 
 def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams,
@@ -268,18 +348,7 @@ def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: S
     batches = plan_batches([len(p) for p in prompts], max_tokens, context, min(max_batch, cache.n_slots),
                            cache.n_pages * page, page)
     states = [RequestState(i + request_offset, p) for i, p in enumerate(prompts)]
-    ops = model.runtime.ops
     for batch in batches:
-        members = [states[i] for i in batch]
-        if use_graph and getattr(model, "graph_safe", True):
-            run_batch_graphed(model, cache, params, members, stop, max_tokens, context)
-            continue
-        sampler = Sampler(params, [s.index for s in members], model.runtime.device, ops)
-
-        def sample(logits, rows, sampler=sampler, n=len(members)):
-            toks = sampler.sample(logits, None if len(rows) == n else rows)
-            return toks.cpu().tolist()
-
-        run_batch(lambda entries: model.step(cache, entries), sample, cache.acquire, cache.release,
-                  members, stop, max_tokens, context)
+        run_requests(model, cache, params, [states[i] for i in batch], stop, max_tokens, context,
+                     use_graph=use_graph)
     return [s.produced for s in states]

@@ -70,10 +70,26 @@ class DecoderModel:
                              self.runtime.device, n_slots=n_slots)
 
     # ------------------------------------------------------------------- step
-    def step(self, cache: SequenceCache, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, cache: SequenceCache, entries: Sequence[StepEntry], trace=None) -> Optional[torch.Tensor]:
         """Runs the given tokens; returns float32 logits [wanted, vocab] in the
         order of the entries and of their ``want`` lists, or None if nothing is
-        wanted."""
+        wanted.
+
+        ``trace``: for finding the stage at which a result goes wrong.  A dict
+        (filled with name -> float32 host array) or a callable ``(name, tensor)``
+        that is told every named intermediate result of the step, all tokens of
+        the step as rows: ``embed``, per layer run ``h.N.ln1``, ``h.N.qkv``,
+        ``h.N.attn`` (heads merged, before the output projection), ``h.N.res1``,
+        ``h.N.ln2``, ``h.N.act`` (the feed-forward's hidden row after the
+        activation), ``h.N.res2``, then ``lnf`` and ``logits`` (wanted rows
+        only).  The names are those of the reference's ``LocalTrace``
+        (include/ai/LocalModel.hpp:1213-1224, filled at 3699-3801) where it has
+        them."""
+        if isinstance(trace, dict):
+            sink = trace
+
+            def trace(name, tensor, sink=sink):
+                sink[name] = tensor.detach().float().cpu().numpy().copy()
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
@@ -85,7 +101,7 @@ class DecoderModel:
                 raise ValueError(f"token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
         starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
         ctx = build_context(self.runtime, self.assembly.position, cache, entries, starts,
-                            self._ring, self._workspace)
+                            self._ring, self._workspace, trace)
         logits = self.forward(ctx, cache)
         for e in entries:
             cache.commit(e.slot, len(e.tokens))
@@ -94,11 +110,17 @@ class DecoderModel:
     def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:
         a = self.assembly
         x = a.embedding.forward(ctx, a.position.embedding_table())
+        ctx.note("embed", x)
         for i, entry in enumerate(self.plan.schedule):
             layer = a.layers[entry.layer]
+            ctx.tag = f"h.{i}."
             layer.arrangement.forward(x, layer, ctx, cache.entry(entry.cache_of), entry.cache_of == i)
+        ctx.tag = ""
         if ctx.want_rows is None:
             return None
         lazy = getattr(a.head, "takes_lazy_norm", False)
         h = a.final_norm.lazy(x, rows=ctx.want_rows) if lazy else a.final_norm.forward(x, rows=ctx.want_rows)
-        return a.head.forward(h)
+        ctx.note("lnf", h)
+        logits = a.head.forward(h)
+        ctx.note("logits", logits)
+        return logits

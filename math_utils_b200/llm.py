@@ -12,11 +12,10 @@ from __future__ import annotations
 from dataclasses import dataclass, replace
 from typing import List, Optional, Sequence
 
-from .engine.batch import StepEntry
 from .engine.generate import generate as _generate
-from .engine.generate import RequestState, take_token
+from .engine.generate import RequestState, run_requests
 from .engine.model import DecoderModel
-from .sampling import Sampler, SamplingParams
+from .sampling import SamplingParams
 
 
 @dataclass
@@ -25,7 +24,7 @@ class Options:
     context: int = 4096             # cache positions per sequence, clamped to the model's maximum
     max_tokens: int = 512           # most tokens one answer may have
     temperature: float = 0.7        # <= 0: greedy
-    top_k: int = 40                 # 1: greedy; 0: the whole vocabulary
+    top_k: int = 40                 # 0 or 1: greedy; negative: the whole vocabulary
     seed: int = 0
     stateless: bool = False         # every prompt() starts from an empty cache
     dtype: str = "bfloat16"         # "float32": the true 32-bit path
@@ -43,6 +42,7 @@ class LLM:
         self._batch_cache = None
         self._slot = None
         self._turns = 0
+        self.last: dict = {}            # figures of the last prompt(): tokens in and out, why it ended
         if model_dir is not None:
             self.use(model_dir)
 
@@ -82,7 +82,11 @@ class LLM:
     def prompt(self, ids: Sequence[int], max_tokens: Optional[int] = None) -> List[int]:
         """Feeds ``ids`` after what the conversation already holds and returns
         the answer's tokens.  When the context would fill, the conversation is
-        forgotten first, as the reference does (include/ai/LLM.hpp:214-221)."""
+        forgotten first, as the reference does (include/ai/LLM.hpp:214-221).
+        Afterwards the cache holds the prompt and every token of the answer
+        (the reference forwards each token it emits, include/ai/LLM.hpp:226-243),
+        so the next turn continues from there.  The steps run through the same
+        loop as ``generate``: a batch of one on a slot that is kept."""
         self._need_model()
         if not ids:
             raise ValueError("the prompt is empty")
@@ -100,19 +104,17 @@ class LLM:
             raise ValueError("the prompt alone does not fit in the context")
         if self._slot is None:
             self._slot = self._cache.acquire()
-        sampler = Sampler(self._params(None, None, None), [self._turns], self.model.runtime.device,
-                          self.model.runtime.ops)
+        # the conversation so far counts toward the context rule; the turn keys the sampling stream
+        state = RequestState(self._turns, list(ids), held=held)
         self._turns += 1
-        # a request whose "prompt" is all the conversation so far: its length drives the context rule
-        state = RequestState(0, [0] * held + list(ids))
-        stop = frozenset(self.model.stop_ids)
-        entry = StepEntry(self._slot, list(ids), [len(ids) - 1])
-        while True:
-            logits = self.model.step(self._cache, [entry])
-            token = int(sampler.sample(logits).cpu()[0])
-            if not take_token(state, token, stop, max_tokens, limit):
-                break
-            entry = StepEntry(self._slot, [token], [0])
+        try:
+            run_requests(self.model, self._cache, self._params(None, None, None), [state],
+                         frozenset(self.model.stop_ids), max_tokens, limit, kept_slots=[self._slot])
+        except Exception:
+            self.reset()               # the cache may hold half a turn
+            raise
+        self.last = {"prompt_tokens": len(ids), "produced": len(state.produced), "reason": state.reason,
+                     "context_used": self._cache.length(self._slot)}
         return state.produced
 
     def once(self, ids: Sequence[int], max_tokens: Optional[int] = None) -> List[int]:

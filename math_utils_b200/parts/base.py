@@ -99,6 +99,24 @@ class Part:
         except KeyError:
             raise ConfigError(f"part '{self.spec.kind}' needs a tensor name for '{role}'") from None
 
+    def bias_spec(self, role: str, size: int, init: str = "bias"):
+        """The ``TensorSpec`` of a bias vector under the part's ``bias`` parameter:
+        true (the default) the file must hold it, ``"if_present"`` it is used when
+        the file holds it, false it is never read.  Returns a tuple of zero or one
+        specs, to be spliced into ``tensor_specs``."""
+        mode = self.param("bias", True)
+        if mode is False:
+            return ()
+        if mode not in (True, "if_present"):
+            raise ConfigError(f"part '{self.spec.kind}': parameter 'bias' must be true, false or 'if_present'")
+        return (TensorSpec(self.tensor_name(role), (size,), role="vector", init=init, optional=mode != True),)
+
+    def bias_tensor(self, tensors: Mapping[str, Any], role: str):
+        """The bound bias of ``role``, or None where the part has none."""
+        if self.param("bias", True) is False:
+            return None
+        return tensors.get(self.tensor_name(role))
+
 
 class Mixer(Part):
     """Interface of a mixer.

@@ -1,7 +1,8 @@
 """Dense two-matrix feed-forward: up projection, activation, down projection
 (include/ai/LocalModel.hpp:3767-3774).  The activation is a parameter:
 ``gelu_new`` (tanh form, include/ai/LocalModel.hpp:1388-1391) or ``gelu``
-(erf form)."""
+(erf form).  Parameter ``bias``: true (both biases must be in the file),
+``"if_present"`` or false."""
 from __future__ import annotations
 
 from ..config.base import ConfigError, PartSpec
@@ -29,20 +30,20 @@ class DenseFeedForward(FeedForward):
 
     def tensor_specs(self):
         d, i = self.hidden_size, self.inner_size
-        return (self._matrix("up_weight", i, d, "normal"),
-                TensorSpec(self.tensor_name("up_bias"), (i,), role="vector", init="bias"),
-                self._matrix("down_weight", d, i, "residual_projection"),
-                TensorSpec(self.tensor_name("down_bias"), (d,), role="vector", init="bias"))
+        return ((self._matrix("up_weight", i, d, "normal"),) + self.bias_spec("up_bias", i)
+                + (self._matrix("down_weight", d, i, "residual_projection"),) + self.bias_spec("down_bias", d))
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        self.up = Linear(tensors[self.tensor_name("up_weight")], tensors[self.tensor_name("up_bias")], runtime)
-        self.down = Linear(tensors[self.tensor_name("down_weight")], tensors[self.tensor_name("down_bias")], runtime)
+        self.up = Linear(tensors[self.tensor_name("up_weight")], self.bias_tensor(tensors, "up_bias"), runtime)
+        self.down = Linear(tensors[self.tensor_name("down_weight")], self.bias_tensor(tensors, "down_bias"), runtime)
 
     def forward(self, h, residual, ctx) -> None:
         hidden = None if ctx is None else ctx.buffer("feed_forward.hidden", (ctx.n_tokens, self.inner_size),
                                                      self.runtime.dtype)
         u = self.up(h, act=self.activation, out=hidden)
+        if ctx is not None:
+            ctx.note("act", u)
         self.down(u, residual=residual, out=residual)
 
 

@@ -1,9 +1,10 @@
 """Greedy and temperature / top-k sampling, on the device.
 
 The rule is the reference's ``sampleTopK`` (include/ai/LocalModel.hpp:3809-3841):
-``temperature <= 0`` or ``top_k == 1`` is greedy (first maximum wins); otherwise
-the ``top_k`` largest logits are kept (``0`` keeps the whole vocabulary), softmax
-at the temperature, and one uniform draw walks them in descending order.  Each
+``temperature <= 0`` or ``top_k`` of 0 or 1 is greedy (first maximum wins);
+otherwise the ``top_k`` largest logits are kept, softmax at the temperature, and
+one uniform draw walks them in descending order.  A negative ``top_k`` keeps the
+whole vocabulary (the reference's count is unsigned and has no such value).  Each
 request has its own stream of draws keyed by (seed, request index), so a
 request's tokens do not depend on which batch it ran in.
 """
@@ -23,7 +24,12 @@ class SamplingParams:
 
     @property
     def greedy(self) -> bool:
-        return self.temperature <= 0.0 or self.top_k == 1
+        return self.temperature <= 0.0 or 0 <= self.top_k <= 1
+
+    @property
+    def kept(self) -> int:
+        """The count the kernel is given: how many of the largest logits stay, 0 for all of them."""
+        return max(self.top_k, 0)
 
 
 class Sampler:
@@ -42,11 +48,11 @@ class Sampler:
         if self.params.greedy:
             return self.ops.argmax(logits)
         if rows is None:
-            return self.ops.sample(logits, self.params.temperature, self.params.top_k, self.params.seed,
+            return self.ops.sample(logits, self.params.temperature, self.params.kept, self.params.seed,
                                    self.request_ids, self.draws)
         index = torch.tensor(list(rows), dtype=torch.int64, device=self.device)
         draws = self.draws[index].contiguous()
-        out = self.ops.sample(logits, self.params.temperature, self.params.top_k, self.params.seed,
+        out = self.ops.sample(logits, self.params.temperature, self.params.kept, self.params.seed,
                               self.request_ids[index].contiguous(), draws)
         self.draws[index] = draws
         return out

@@ -100,7 +100,9 @@ def load_weights(model_dir: str, specs: Sequence[TensorSpec], compute_dtype: tor
             base = n[len(prefix):] if n.startswith(prefix) else None
             if base is not None and base in wanted:
                 continue
-            if base is not None and any(r.fullmatch(base) for r in ignore):
+            # a name the model never reads may stand with the prefix or without it (a checkpoint that
+            # keeps its layers under "transformer." has its tied output copy as plain "lm_head.weight")
+            if any(r.fullmatch(c) for r in ignore for c in (base, n) if c is not None):
                 continue
             unexpected.append(n)
         if missing or wrong or unexpected:

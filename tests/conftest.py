@@ -23,7 +23,13 @@ TINY_B = {
     "vocab_size": 1031, "n_positions": 80, "layer_norm_epsilon": 1e-6,
     "scale_attn_by_inverse_layer_idx": True, "eos_token_id": [11, 500],
 }
-TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B}
+# head size 20: no multiple of 16, which GPT-2's config.json allows (n_embd / n_head)
+TINY_C = {
+    "model_type": "gpt2", "architectures": ["GPT2LMHeadModel"],
+    "n_layer": 2, "n_embd": 100, "n_head": 5, "activation_function": "gelu_new",
+    "vocab_size": 333, "n_positions": 150, "layer_norm_epsilon": 1e-5,
+}
+TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
 
 
 def pytest_configure(config):
@@ -47,3 +53,14 @@ def model_dirs(tmp_path_factory):
 def plain_models(model_dirs):
     import plain_gpt2
     return {name: plain_gpt2.read_model(d) for name, d in model_dirs.items()}
+
+
+def pytest_terminal_summary(terminalreporter):
+    """How much of their bounds the logit comparisons used: a bound that is never approached pins little."""
+    try:
+        import helpers
+    except ImportError:
+        return
+    for dtype, (used, what) in helpers.OBSERVED.items():
+        if used > 0.0:
+            terminalreporter.write_line(f"logits, {dtype}: largest error was {used:.2f} of its bound ({what})")

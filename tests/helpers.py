@@ -12,6 +12,9 @@ FP32_ABS = 1e-4
 BF16_REL = 0.04
 
 
+OBSERVED = {"float32": (0.0, ""), "bfloat16": (0.0, "")}    # the largest error seen so far, as a fraction of its bound
+
+
 def check_logits(got, want, dtype, what=""):
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
@@ -21,10 +24,14 @@ def check_logits(got, want, dtype, what=""):
     if dtype == "float32":
         bad = err > FP32_ABS
         bound = FP32_ABS
+        used = float(err.max() / FP32_ABS) if err.size else 0.0
     else:
         spread = want.std(axis=-1)
         bad = err > BF16_REL * np.maximum(spread, 1e-3)
         bound = f"{BF16_REL} x row spread"
+        used = float((err / (BF16_REL * np.maximum(spread, 1e-3))).max()) if err.size else 0.0
+    if used > OBSERVED[dtype][0]:
+        OBSERVED[dtype] = (used, what)
     assert not bad.any(), (f"{what}: first wrong row {int(np.argmax(bad))} of {len(err)}, "
                            f"max |diff| {err.max():.3e} (bound {bound})")
 

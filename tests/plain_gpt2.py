@@ -85,7 +85,10 @@ def gelu_new(x):
 def gelu_erf(x):
     """0.5 x (1 + erf(x / sqrt 2)): the exact form that ``activation_function``
     "gelu" names.  The reference has only the tanh form."""
-    erf = np.vectorize(math.erf, otypes=[x.dtype])
+    try:
+        from scipy.special import erf
+    except ImportError:                                        # pragma: no cover
+        erf = np.vectorize(math.erf, otypes=[x.dtype])
     return 0.5 * x * (1.0 + erf(x / math.sqrt(2.0)))
 
 
@@ -127,50 +130,95 @@ def causal_attention(q, k, v, n_heads, n_kv_heads, scale, window=0, start=0):
     return out
 
 
-def attention_block(h, w, prefix, cfg, layer):
+def causal_attention_masked(q, k, v, n_heads, n_kv_heads, scale, window=0):
+    """The same attention in the reference's other form: the whole [T, T] score
+    matrix of a head, everything a query may not see filled with -1e10 before
+    the softmax (include/ai/GPT2.hpp:261-271; tools/gpt2_oracle.py:258-267; in
+    float64 the filled entries weigh exactly nothing, exp underflows to 0).  No
+    loop over queries, so long sequences stay affordable."""
+    T = q.shape[0]
+    dh = q.shape[1] // n_heads
+    out = np.zeros_like(q)
+    group = n_heads // n_kv_heads
+    i, j = np.arange(T)[:, None], np.arange(T)[None, :]
+    hidden = j > i
+    if window:
+        hidden = hidden | (j < i + 1 - window)
+    for h in range(n_heads):
+        kv = h // group
+        s = (q[:, h * dh:(h + 1) * dh] @ k[:, kv * dh:(kv + 1) * dh].T) * scale
+        s = np.where(hidden, -1e10, s)
+        out[:, h * dh:(h + 1) * dh] = softmax(s) @ v[:, kv * dh:(kv + 1) * dh]
+    return out
+
+
+def attention_block(h, w, prefix, cfg, layer, trace=None, masked=False):
     """c_attn, split into q|k|v by columns, heads, c_proj
     (include/ai/LocalModel.hpp:2130-2145, 2604-2667; include/ai/GPT2.hpp:248-276)."""
     d = cfg["n_embd"]
     n_head = cfg["n_head"]
     qkv = linear_in_out(h, w[prefix + ".attn.c_attn.weight"], w[prefix + ".attn.c_attn.bias"])
+    if trace is not None:
+        trace[prefix + ".qkv"] = qkv.copy()
     q, k, v = qkv[:, :d], qkv[:, d:2 * d], qkv[:, 2 * d:]
     scale = 1.0
     if cfg.get("scale_attn_weights", True):
         scale = 1.0 / math.sqrt(d // n_head)                    # include/ai/Kernels.hpp:136
     if cfg.get("scale_attn_by_inverse_layer_idx", False):
         scale = scale / float(layer + 1)
-    a = causal_attention(q, k, v, n_head, n_head, scale)
+    attend = causal_attention_masked if masked else causal_attention
+    a = attend(q, k, v, n_head, n_head, scale)
+    if trace is not None:
+        trace[prefix + ".attn"] = a.copy()
     return linear_in_out(a, w[prefix + ".attn.c_proj.weight"], w[prefix + ".attn.c_proj.bias"])
 
 
-def feed_forward(h, w, prefix, cfg):
+def feed_forward(h, w, prefix, cfg, trace=None):
     """c_fc, activation, c_proj (include/ai/LocalModel.hpp:3767-3774;
     include/ai/GPT2.hpp:279-290)."""
     act = ACTIVATIONS[cfg.get("activation_function", "gelu_new")]
-    u = linear_in_out(h, w[prefix + ".mlp.c_fc.weight"], w[prefix + ".mlp.c_fc.bias"])
-    return linear_in_out(act(u), w[prefix + ".mlp.c_proj.weight"], w[prefix + ".mlp.c_proj.bias"])
+    u = act(linear_in_out(h, w[prefix + ".mlp.c_fc.weight"], w[prefix + ".mlp.c_fc.bias"]))
+    if trace is not None:
+        trace[prefix + ".act"] = u.copy()
+    return linear_in_out(u, w[prefix + ".mlp.c_proj.weight"], w[prefix + ".mlp.c_proj.bias"])
 
 
-def forward(ids, cfg, w, trace=None):
+def forward(ids, cfg, w, trace=None, rows=None, masked=None):
     """Logits [len(ids), vocab] of one whole sequence
     (include/ai/LocalModel.hpp:3648-3802; include/ai/GPT2.hpp:300-339;
-    tools/gpt2_oracle.py:285-321)."""
+    tools/gpt2_oracle.py:285-321).  ``rows``: only these positions' logits (the
+    reference computes the last row only, include/ai/LocalModel.hpp:3788-3799).
+    ``masked``: attention in the masked-matrix form instead of query by query
+    (default: for sequences of more than 200 tokens).  ``trace``: a dict that
+    receives every stage by the reference's names (include/ai/LocalModel.hpp:
+    3699-3801): embed, h.N.ln1, h.N.qkv, h.N.attn, h.N.res1, h.N.ln2, h.N.act,
+    h.N.res2, lnf, logits."""
     eps = cfg.get("layer_norm_epsilon", 1e-5)
+    masked = len(ids) > 200 if masked is None else masked
     x = embed(ids, 0, w["wte.weight"], w["wpe.weight"])
     if trace is not None:
         trace["embed"] = x.copy()
     for i in range(cfg["n_layer"]):
         p = f"h.{i}"
         h = layer_norm(x, w[p + ".ln_1.weight"], w[p + ".ln_1.bias"], eps)
-        x = x + attention_block(h, w, p, cfg, i)
+        if trace is not None:
+            trace[p + ".ln1"] = h.copy()
+        x = x + attention_block(h, w, p, cfg, i, trace, masked)
         if trace is not None:
             trace[p + ".res1"] = x.copy()
         h = layer_norm(x, w[p + ".ln_2.weight"], w[p + ".ln_2.bias"], eps)
-        x = x + feed_forward(h, w, p, cfg)
+        if trace is not None:
+            trace[p + ".ln2"] = h.copy()
+        x = x + feed_forward(h, w, p, cfg, trace)
         if trace is not None:
             trace[p + ".res2"] = x.copy()
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     x = layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], eps)
-    return x @ w["wte.weight"].T                               # tied head, no bias
+    logits = x @ w["wte.weight"].T                             # tied head, no bias
+    if trace is not None:
+        trace["lnf"], trace["logits"] = x.copy(), logits.copy()
+    return logits
 
 
 # ------------------------------------------------------------------ sampling
@@ -202,16 +250,18 @@ def uniform_draw(seed, request, n):
 
 def sample_top_k(row, temperature, top_k, u):
     """include/ai/LocalModel.hpp:3815-3841: greedy when temperature <= 0 or
-    top_k == 1; else keep the top_k largest (0: all), p = exp(l/T - best/T),
+    top_k <= 1 (the reference's count is unsigned; a negative top_k here keeps
+    all, which the reference cannot ask for); else keep the top_k largest,
+    p = exp(l/T - best/T),
     pick = u * sum p, walk in descending order subtracting p until <= 0.  Ties
     are ordered by index.  Returns (token, distance of pick to the nearest
     boundary relative to the total), so a test can tell a rounding-level
     disagreement from a real one."""
     row = np.asarray(row, dtype=np.float32)
-    if temperature <= 0.0 or top_k == 1:
+    if temperature <= 0.0 or 0 <= top_k <= 1:
         return argmax(row), 1.0
     n = len(row)
-    keep = n if top_k <= 0 else min(top_k, n)
+    keep = n if top_k < 0 else min(top_k, n)
     order = sorted(range(n), key=lambda i: (-float(row[i]), i))[:keep]
     t = np.float32(temperature)
     best = row[order[0]] / t

@@ -91,3 +91,17 @@ def test_schedule_validation():
         replace(plan, schedule=(ScheduleEntry(5, 0),)).validate()
     with pytest.raises(ConfigError, match="owns none"):
         replace(plan, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 0), ScheduleEntry(1, 1))).validate()
+
+
+def test_stop_ids_of_generation_config_are_added(tmp_path):
+    """eos_token_id of generation_config.json joins config.json's (include/ai/LocalModel.hpp:1788-1792)."""
+    import json
+    from math_utils_b200.config import load_config
+    (tmp_path / "config.json").write_text(json.dumps(TINY_B))
+    assert load_config(str(tmp_path))[2].stop_ids == (11, 500)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [500, 3], "max_length": 20}))
+    assert load_config(str(tmp_path))[2].stop_ids == (11, 500, 3)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 9}))
+    assert load_config(str(tmp_path))[2].stop_ids == (11, 500, 9)
+    (tmp_path / "generation_config.json").write_text("not json")
+    assert load_config(str(tmp_path))[2].stop_ids == (11, 500)

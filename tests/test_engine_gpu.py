@@ -43,11 +43,12 @@ def plain_logits(plain_models):
     return get
 
 
-LENGTHS = {"tiny_a": [5, 17, 32, 128, 70], "tiny_b": [1, 2, 9, 40, 63, 80]}
+LENGTHS = {"tiny_a": [5, 17, 32, 128, 70], "tiny_b": [1, 2, 9, 40, 63, 80], "tiny_c": [3, 64, 65, 150]}
+NAMES = ["tiny_a", "tiny_b", "tiny_c"]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_whole_requests(name, dtype, engines, plain_models, plain_logits):
     model = engines(name, dtype)
     cfg = plain_models[name][0]
@@ -59,7 +60,7 @@ def test_whole_requests(name, dtype, engines, plain_models, plain_logits):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_last_tokens_one_by_one(name, dtype, engines, plain_models, plain_logits):
     model = engines(name, dtype)
     cfg = plain_models[name][0]
@@ -70,7 +71,7 @@ def test_last_tokens_one_by_one(name, dtype, engines, plain_models, plain_logits
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_unequal_batches_reuse_slots(name, dtype, engines, plain_models, plain_logits):
     model = engines(name, dtype)
     cfg = plain_models[name][0]
@@ -111,3 +112,39 @@ def test_long_decoding_from_one_token(dtype, engines, plain_models, plain_logits
     cache = model.new_cache(max_tokens=128)
     got = run_tail_one_by_one(model, cache, tokens, tail=127)
     check_logits(got, plain_logits(name, tokens), dtype, "decode from the first token")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_stage_trace_matches_plain(dtype, engines, plain_models):
+    """``step(..., trace=...)`` hands out every stage by name; each is held against the plain
+    model's stage of the same name, for a prompt and for a single-token step after it, so a wrong
+    logit can be followed back to the first stage that is off."""
+    from math_utils_b200 import StepEntry
+    name = "tiny_b"
+    cfg, w = plain_models[name]
+    model = engines(name, dtype)
+    tokens = requests_for(cfg, 8, [41])[0]
+    want = {}
+    plain_gpt2.forward(tokens, cfg, w, trace=want)
+    cache = model.new_cache(max_tokens=128)
+    slot = cache.acquire()
+    got_prompt, got_step = {}, {}
+    model.step(cache, [StepEntry(slot, tokens[:40], [39])], trace=got_prompt)
+    model.step(cache, [StepEntry(slot, tokens[40:], [0])], trace=got_step)
+    cache.release(slot)
+    names = ["embed"] + [f"h.{i}.{s}" for i in range(cfg["n_layer"])
+                         for s in ("ln1", "qkv", "attn", "res1", "ln2", "act", "res2")] + ["lnf", "logits"]
+    assert list(got_prompt) == names and list(got_step) == names          # in the order they are computed
+    for n in names:
+        full = want[n]
+        for got, rows in ((got_prompt[n], full[:40] if n not in ("lnf", "logits") else full[39:40]),
+                          (got_step[n], full[40:41])):
+            assert got.shape == rows.shape, n
+            scale = max(float(np.abs(rows).max()), 1.0)
+            bound = 1e-4 * scale if dtype == "float32" else 0.03 * scale
+            assert np.abs(got - rows).max() < bound, (n, float(np.abs(got - rows).max()), scale)
+    # the trace changes nothing
+    slot = cache.acquire()
+    a = model.step(cache, [StepEntry(slot, tokens[:40], [39])]).cpu().numpy()
+    cache.release(slot)
+    assert np.array_equal(a, got_prompt["logits"])

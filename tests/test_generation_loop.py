@@ -293,3 +293,71 @@ def test_loop_one_step_behind_on_drawn_cases(monkeypatch):
             assert cache.slots.n_free == n_req and cache.free_pages(0) == cache.n_pages
         assert dev.most_unread <= (1 if window else 2)
     assert reasons == {"stop", "max_tokens", "context"}
+
+
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("max_tokens,stop", [(5, set()), (40, {13, 33, 7, 21}), (1, set()), (64, {49})])
+def test_conversation_on_a_kept_slot(monkeypatch, window, max_tokens, stop):
+    """Turn after turn on one slot that the caller keeps (``kept_slots``): after each turn the slot
+    holds the earlier turns, the prompt and every emitted token, whether the turn ended on a stop
+    token (which the device had already stepped when the host saw it: cut off again), on the token
+    budget or on the context (the last token is fed afterwards); the next turn continues from there."""
+    from math_utils_b200.cache import SequenceCache
+    from math_utils_b200.engine import decode_session, generate as gen
+    from math_utils_b200.parts.base import KVCacheSpec
+    from math_utils_b200.sampling import SamplingParams
+    context = 200
+    cache = SequenceCache([KVCacheSpec(1, 16, window)], 256, 200, torch.float32, "cpu", n_slots=1)
+    dev = FakeDevice(cache, window, limit=context)
+    sessions = {}
+    monkeypatch.setattr(decode_session, "session_for",
+                        lambda model, c, params, n, pipelined=True: sessions.setdefault(n, dev.session(n)))
+
+    class FakeSampler:
+        def __init__(self, *a):
+            pass
+
+        def sample(self, logits):
+            return logits
+    monkeypatch.setattr(gen, "Sampler", FakeSampler)
+    rng = np.random.default_rng(max_tokens + window)
+    slot = cache.acquire()
+    history, reasons = [], set()
+    for turn in range(6):
+        ids = rng.integers(0, 50, size=int(rng.integers(1, 20))).tolist()
+        if len(history) + len(ids) + max_tokens > context:
+            break
+        state = RequestState(turn, ids, held=len(history))
+        gen.run_batch_graphed(dev, cache, SamplingParams(temperature=0.0), [state], stop, max_tokens, context,
+                              kept_slots=[slot])
+        want = expected_windowed(history + ids, max_tokens, stop, context, window)
+        assert state.produced == want, (turn, state.reason)
+        history += ids + want
+        assert cache.length(slot) == len(history) == state.positions
+        assert cache.slots.is_held(slot)
+        reasons.add(state.reason)
+    assert reasons                                     # at least one turn ran
+    cache.release(slot)
+    assert cache.free_pages(0) == cache.n_pages
+
+
+def test_cache_cut_back():
+    from math_utils_b200.cache import CacheError, SequenceCache
+    from math_utils_b200.parts.base import KVCacheSpec, StateCacheSpec
+    cache = SequenceCache([KVCacheSpec(1, 16, 0)], 256, 200, torch.float32, "cpu", n_slots=2)
+    slot = cache.acquire()
+    cache.reserve(slot, 70); cache.commit(slot, 70)
+    held = cache.kv_groups[0].pages_held(slot)
+    cache.truncate(slot, 64)
+    assert cache.length(slot) == 64 and cache.kv_groups[0].pages_held(slot) == held     # the page stays
+    cache.reserve(slot, 3); cache.commit(slot, 3)                                        # and is used again
+    assert cache.length(slot) == 67 and cache.kv_groups[0].pages_held(slot) == held
+    with pytest.raises(CacheError):
+        cache.truncate(slot, 68)
+    for spec in (KVCacheSpec(1, 16, 40), StateCacheSpec(8)):
+        other = SequenceCache([spec, KVCacheSpec(1, 16, 0)], 256, 200, torch.float32, "cpu", n_slots=1)
+        s = other.acquire()
+        other.reserve(s, 5); other.commit(s, 5)
+        with pytest.raises(CacheError, match="cannot be cut back"):
+            other.truncate(s, 4)
+        other.truncate(s, 5)                                                             # nothing to cut: allowed

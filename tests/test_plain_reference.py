@@ -61,6 +61,18 @@ def test_attention_window_and_groups():
         assert np.allclose(one[:, h * dh:(h + 1) * dh], v[:, (h // 2) * dh:(h // 2 + 1) * dh])
 
 
+def test_attention_forms_agree():
+    """Query by query (include/ai/Kernels.hpp:132-161) and the masked score matrix
+    (include/ai/GPT2.hpp:261-271) are the same attention, window or not."""
+    rng = np.random.default_rng(5)
+    T, H, Hkv, dh = 37, 6, 2, 10
+    q, k, v = (rng.standard_normal((T, n * dh)) for n in (H, Hkv, Hkv))
+    for window in (0, 1, 9, 50):
+        a = plain_gpt2.causal_attention(q, k, v, H, Hkv, 0.3, window)
+        b = plain_gpt2.causal_attention_masked(q, k, v, H, Hkv, 0.3, window)
+        assert np.abs(a - b).max() < 1e-12, window
+
+
 def test_sampling_rules():
     row = np.array([0.1, 2.0, 2.0, -1.0, 1.5], dtype=np.float32)
     assert plain_gpt2.argmax(row) == 1                      # first maximum wins
@@ -68,7 +80,8 @@ def test_sampling_rules():
     assert plain_gpt2.sample_top_k(row, 1.0, 1, 0.7)[0] == 1
     assert plain_gpt2.sample_top_k(row, 1.0, 2, 0.0)[0] == 1       # walk starts at the best, lower index first
     assert plain_gpt2.sample_top_k(row, 1.0, 2, 0.999)[0] == 2
-    assert plain_gpt2.sample_top_k(row, 1.0, 0, 0.999999)[0] == 3  # the smallest comes last
+    assert plain_gpt2.sample_top_k(row, 1.0, -1, 0.999999)[0] == 3  # the smallest comes last
+    assert plain_gpt2.sample_top_k(row, 1.0, 0, 0.999999)[0] == 1   # a count of 0 is greedy, as the reference's
     u = [plain_gpt2.uniform_draw(1, 2, n) for n in range(1000)]
     assert 0.0 <= min(u) and max(u) < 1.0 and 0.45 < float(np.mean(u)) < 0.55
     assert plain_gpt2.uniform_draw(1, 2, 3) != plain_gpt2.uniform_draw(1, 3, 3)

@@ -1,7 +1,7 @@
 """More toy parts, defined here and registered from outside the package: a rotary
 position encoding (through the ``rotate`` hook), a feed-forward with routing
-over experts, grouped heads and a windowed layer next to a full one (two cache
-groups in one model).  None of these is a model of anyone's; they show that the
+over experts, grouped heads, a windowed layer next to a full one (two cache
+groups in one model) and a layer whose projections have no bias.  None of these is a model of anyone's; they show that the
 part interfaces carry more than GPT-2."""
 import math
 
@@ -96,6 +96,11 @@ class ToyConfig2:
             return PartSpec("layer_norm", {"size": d, "eps": 1e-5}, {"weight": name + ".w", "bias": name + ".b"})
 
         def attn(i, window):
+            if i == 1:              # the second layer's projections have no bias: no names, nothing in the file
+                return PartSpec("causal_attention",
+                                {"hidden_size": d, "n_heads": heads, "n_kv_heads": kv_heads, "head_dim": dh,
+                                 "softmax_scale": dh ** -0.5, "window": window, "bias": False},
+                                {"qkv_weight": f"l{i}.qkv.w", "out_weight": f"l{i}.o.w"})
             return PartSpec("causal_attention",
                             {"hidden_size": d, "n_heads": heads, "n_kv_heads": kv_heads, "head_dim": dh,
                              "softmax_scale": dh ** -0.5, "window": window},
@@ -105,8 +110,8 @@ class ToyConfig2:
         routed = PartSpec("toy_routed_ffn", {"hidden_size": d, "inner_size": r["inner"], "n_experts": r["experts"]},
                           {"router": "l0.router", "up": "l0.e{e}.up.w", "up_bias": "l0.e{e}.up.b",
                            "down": "l0.e{e}.down.w", "down_bias": "l0.e{e}.down.b"})
-        dense = PartSpec("dense_ffn", {"hidden_size": d, "inner_size": r["inner"], "activation": "gelu"},
-                         {"up_weight": "l1.up.w", "up_bias": "l1.up.b", "down_weight": "l1.down.w", "down_bias": "l1.down.b"})
+        dense = PartSpec("dense_ffn", {"hidden_size": d, "inner_size": r["inner"], "activation": "gelu", "bias": False},
+                         {"up_weight": "l1.up.w", "down_weight": "l1.down.w"})
         layers = (LayerSpec("pre_norm", norm("l0.n1"), attn(0, r["window"]), norm("l0.n2"), routed),
                   LayerSpec("pre_norm", norm("l1.n1"), attn(1, 0), norm("l1.n2"), dense))
         return ModelPlan("ToyModel2", r["vocab"], d, r["positions"],
@@ -133,11 +138,11 @@ def toy2_plain(ids, r, w):
     for i, window in ((0, r["window"]), (1, 0)):
         p = f"l{i}"
         h = plain_gpt2.layer_norm(x, w[p + ".n1.w"], w[p + ".n1.b"], 1e-5)
-        qkv = h @ w[p + ".qkv.w"].T + w[p + ".qkv.b"]
+        qkv = h @ w[p + ".qkv.w"].T + (w[p + ".qkv.b"] if i == 0 else 0.0)
         qw, kw = heads * dh, kv_heads * dh
         q, k, v = rotate(qkv[:, :qw]), rotate(qkv[:, qw:qw + kw]), qkv[:, qw + kw:]
         a = plain_gpt2.causal_attention(q, k, v, heads, kv_heads, dh ** -0.5, window)
-        x = x + a @ w[p + ".o.w"].T + w[p + ".o.b"]
+        x = x + a @ w[p + ".o.w"].T + (w[p + ".o.b"] if i == 0 else 0.0)
         h = plain_gpt2.layer_norm(x, w[p + ".n2.w"], w[p + ".n2.b"], 1e-5)
         if i == 0:
             choice = np.argmax(h @ w["l0.router"].T, axis=-1)
@@ -147,7 +152,7 @@ def toy2_plain(ids, r, w):
                 y += (u @ w[f"l0.e{e}.down.w"].T + w[f"l0.e{e}.down.b"]) * (choice == e)[:, None]
             x = x + y
         else:
-            x = x + plain_gpt2.gelu_erf(h @ w["l1.up.w"].T + w["l1.up.b"]) @ w["l1.down.w"].T + w["l1.down.b"]
+            x = x + plain_gpt2.gelu_erf(h @ w["l1.up.w"].T) @ w["l1.down.w"].T
     return plain_gpt2.layer_norm(x, w["final.w"], w["final.b"], 1e-5) @ w["emb"].T
 
 
@@ -171,6 +176,7 @@ def test_toy_model_with_rotary_routing_groups_and_window(toy2):
     cache = model.new_cache(max_tokens=1024, n_slots=4)
     assert [g.spec.window for g in cache.kv_groups] == [50, 0]          # the windowed layer has storage of its own
     w = plain_gpt2.read_safetensors(folder + "/model.safetensors")
+    assert "l0.qkv.b" in w and not any(n.startswith("l1.") and n.endswith(".b") and ".n" not in n for n in w)
     rng = np.random.default_rng(2)
     reqs = [rng.integers(0, raw["vocab"], size=n).tolist() for n in (200, 70, 129, 3)]
     want = [toy2_plain(r, raw, w) for r in reqs]

@@ -128,3 +128,38 @@ def test_prefixed_names_are_found(tmp_path):
     w = load_weights(d, collect_tensor_specs(plan), torch.float32, "cpu", ignored=plan.ignored_tensors,
                      prefixes=("", "transformer."))
     assert "wte.weight" in w and len(w) == len(tensors)
+    # the usual layout of such a checkpoint: layers under the prefix, the tied output copy beside them
+    tensors["lm_head.weight"] = torch.zeros(512, 64)
+    write_safetensors(path, tensors)
+    w = load_weights(d, collect_tensor_specs(plan), torch.float32, "cpu", ignored=plan.ignored_tensors,
+                     prefixes=("", "transformer."))
+    assert "lm_head.weight" not in w and len(w) == len(tensors) - 1
+
+
+def test_bias_modes_of_a_part(tmp_path):
+    """A part's ``bias`` parameter: true wants the vector in the file, "if_present" takes it when it
+    is there, false never reads it (a file that holds it anyway has an unexpected tensor)."""
+    import dataclasses
+    d = write_random_model(str(tmp_path / "m"), TINY_A, seed=2)
+    path = os.path.join(d, "model.safetensors")
+    with SafetensorsFile(path) as f:
+        tensors = {n: f.read(n) for n in f.names()}
+    del tensors["h.0.mlp.c_fc.bias"]
+    write_safetensors(path, tensors)
+    plan = Gpt2Config.from_json(TINY_A).plan()
+
+    def with_bias(mode):
+        layers = list(plan.layers)
+        ff = layers[0].feed_forward
+        layers[0] = dataclasses.replace(layers[0], feed_forward=dataclasses.replace(ff, params=dict(ff.params, bias=mode)))
+        return dataclasses.replace(plan, layers=tuple(layers))
+
+    with pytest.raises(WeightError) as e:
+        load_weights(d, collect_tensor_specs(with_bias(True)), torch.float32, "cpu", ignored=plan.ignored_tensors)
+    assert e.value.missing == ["h.0.mlp.c_fc.bias"]
+    w = load_weights(d, collect_tensor_specs(with_bias("if_present")), torch.float32, "cpu",
+                     ignored=plan.ignored_tensors)
+    assert "h.0.mlp.c_fc.bias" not in w and "h.0.mlp.c_proj.bias" in w
+    with pytest.raises(WeightError) as e:
+        load_weights(d, collect_tensor_specs(with_bias(False)), torch.float32, "cpu", ignored=plan.ignored_tensors)
+    assert e.value.unexpected == ["h.0.mlp.c_proj.bias"] and not e.value.missing

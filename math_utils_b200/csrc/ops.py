@@ -500,13 +500,15 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
     return out
 
 
-sm_counts = {}
+SKINNY_LN_SMEM = 160 * 1024          # the limit of mu_gemm_skinny_ln (gemm_skinny.cuh)
+
+_sm_counts = {}
 
 
 def sm_count(device) -> int:
-    n = sm_counts.get(device)
+    n = _sm_counts.get(device)
     if n is None:
-        n = sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
     return n
 
 

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "mu_gemm_tc_split_workspace": [_c_p, _c_ll, _c_p, _c_int],
     "mu_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                    _c_int, _c_int, _c_int, _c_int, _c_p, _c_p],
+    "mu_gemm_rows": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
+                     _c_int, _c_int, _c_int, _c_p, _c_p],
     "mu_kv_append": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_p, _c_int, _c_p, _c_int, _c_p],
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
@@ -292,11 +294,11 @@ def status_word(device) -> torch.Tensor:
     return word
 
 
-def _deep_to_tensor_cores(n: int, k: int) -> bool:
-    """Whether a product of 33 to 64 rows whose weight is deeper than wide goes to the tensor-core
-    kernel (which then cuts k) instead of the few-rows kernel: the cut pays from some six million
-    weights on."""
-    return n * k >= 6_000_000
+def _rows_kernel(m: int, n: int, k: int) -> bool:
+    """Whether a product of m rows goes to ``mu_gemm_rows``: 33 to 64 rows always; up to 32 rows where the
+    weights are 16 million or more (the output head, which that kernel streams faster than the few-rows
+    kernel even with the norm as a launch of its own)."""
+    return 33 <= m <= 64 or (m <= 32 and n * k >= (1 << 24))
 
 
 def _split_workspace(device) -> None:
@@ -353,6 +355,21 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
         _is_bf16(out), int(tile), int(splits), _ptr(status_word(a.device)), _stream()),
         ("gemm_tc({}x{}x{})", m, n, k))
+    return out
+
+
+def gemm_rows(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+              splits: int = 0) -> torch.Tensor:
+    """The product for up to 64 rows on the tcgen05 tensor cores: tiles of 16 output columns, a block per
+    tile, k cut over a thread-block cluster where the tiles are few (``splits`` blocks per tile, 0: chosen
+    by the library), the parts added in rank order in the first block's shared memory."""
+    m, n, k, out = _gemm_args(a, w, bias, residual, out, out_dtype or a.dtype)
+    _check(library().mu_gemm_rows(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), m, n, k, a.stride(0), w.stride(0),
+        out.stride(0), residual.stride(0) if residual is not None else 0, ACT_CODES[act],
+        _is_bf16(out), int(splits), _ptr(status_word(a.device)), _stream()), ("gemm_rows({}x{}x{})", m, n, k))
     return out
 
 
@@ -689,6 +706,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     dtype and the shape.  float32 operands always take the CUDA-core kernel.
     ``x`` may be a ``NormedInput``: with few rows and bfloat16 weights the norm is
     made inside the product kernel, otherwise it is computed first."""
+    if isinstance(x, NormedInput) and weight.dtype == torch.bfloat16 and _rows_kernel(x.n_rows, *weight.shape):
+        x = x.materialize()          # a very wide product: the norm as a launch of its own costs less than it saves
     if isinstance(x, NormedInput):
         k_in = x.x.shape[1]
         # the few-rows kernel keeps the normed rows (8 or 16 of them), gamma and beta in shared memory
@@ -733,10 +752,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     code = ACT_CODES[act]
     tensor_cores = (dtype == torch.bfloat16 and k % 8 == 0 and lda % 8 == 0 and ldw % 8 == 0
                     and pa % 16 == 0 and pw % 16 == 0)
-    # up to 32 rows the few-rows kernel; up to 64 too where the weight is deeper than wide (its split
-    # along k fills the SMs); wider weights go to the tcgen05 kernel from 33 rows on, whose TMA
-    # pipeline streams them faster once every block has to read that many rows of activations anyway
-    if tensor_cores and m <= 64 and (m <= 32 or (n < k and not _deep_to_tensor_cores(n, k))):
+    # 33 to 64 rows, and fewer where the weights are very many (the output head): the tcgen05 kernel for few
+    # rows (weights as the wide operand, k cut over a cluster); up to 32 rows otherwise the mma.sync kernel
+    # that streams weights straight into fragments; more than 64 rows the large tcgen05 kernel
+    if tensor_cores and _rows_kernel(m, n, k):
+        _check(lib.mu_gemm_rows(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
+                                _is_bf16(out), 0, status_word(x.device).data_ptr(), _stream()),
+               ("gemm_rows({}x{}x{})", m, n, k))
+    elif tensor_cores and m <= 32:
         _check(lib.mu_gemm_skinny(pa, pw, pb, pr, out.data_ptr(), m, n, k, lda, ldw, out.stride(0), ldr, code,
                                   _is_bf16(out), _stream()), ("gemm_skinny({}x{}x{})", m, n, k))
     elif tensor_cores:

@@ -343,12 +343,13 @@ MU_EXPORT int mu_kv_append(const void* k, long long ldk, const void* v, long lon
         if (tiled) {
             dim3 grid(n_tiles, n_kv_heads);
             const size_t smem = (size_t)64 * (head_dim * (is_bf16 ? 2 : 4) + 4);
-            if (is_bf16)
+            if (is_bf16) {
+                mu::prefer_shared_memory(reinterpret_cast<const void*>(mu::kv_append_tiles_kernel<__nv_bfloat16>));   // a prompt-step kernel
                 return mu::launch_pdl(mu::kv_append_tiles_kernel<__nv_bfloat16>, grid, dim3(256), smem, s, 1,
                                       (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv, tok_pos, tok_seq,
                                       block_table, max_pages, page_tokens, tiles, n_kv_heads, head_dim,
                                       (__nv_bfloat16*)kv);
-            else {
+            } else {
                 if (smem > 48 * 1024) {
                     static bool raised = false;
                     if (!raised && cudaFuncSetAttribute(mu::kv_append_tiles_kernel<float>,

@@ -449,6 +449,7 @@ MU_EXPORT int mu_attention_prefill_tc(const void* q, long long ldq, int n_tokens
     if (!raised) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MU_ERR_LAUNCH;
+        mu::prefer_shared_memory(reinterpret_cast<const void*>(kernel));
         raised = true;
     }
     return mu::launch_pdl(kernel, dim3((unsigned)items), dim3(mu::PT_THREADS), smem, (cudaStream_t)stream, 1, map_q,

@@ -10,6 +10,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <unordered_set>
+
 #define MU_OK 0
 #define MU_ERR_BAD_ARGUMENT 1      // a size or pointer the kernel cannot take
 #define MU_ERR_UNSUPPORTED_SIZE 2  // a size outside what this kernel was written for
@@ -118,6 +121,20 @@ inline int& pdl_enabled() {
 
 // Launches with the programmatic-serialization attribute (if enabled) and, when cluster_y > 1,
 // as thread-block clusters of (1, cluster_y, 1).
+// The kernels of a prompt step ask for the largest shared-memory share of the SM's on-chip memory, whether
+// they use it or not: the large products and the attention need it, and an SM that has to change the split
+// between shared memory and L1 from one kernel to the next first runs empty.  (The kernels of single-token
+// steps are better off with the L1 they get by default.)
+inline void prefer_shared_memory(const void* kernel) {
+    static std::mutex mutex;
+    static std::unordered_set<const void*> seen;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (seen.insert(kernel).second) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
+    }
+}
+
 template <typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                       int cluster_y, Args&&... args) {

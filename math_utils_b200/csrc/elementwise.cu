@@ -76,7 +76,9 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, flo
     *reinterpret_cast<uint2*>(dst) = packed;
 }
 
-template <typename TO>
+// MANY: the instantiation for the many rows of a prompt step (it prefers shared memory over L1 like the
+// kernels around it there, see prefer_shared_memory); the code is the same.
+template <typename TO, bool MANY>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                       const float* __restrict__ gamma, const float* __restrict__ beta,
@@ -149,10 +151,20 @@ MU_EXPORT int mu_layernorm(const float* x, const int* rows, const float* gamma, 
                          ((uintptr_t)gamma & 15) == 0 && (!beta || ((uintptr_t)beta & 15) == 0);
     if (aligned && hidden <= 32 * mu::LN_V * 4) {
         const unsigned blocks = (n_rows + mu::LN_WARPS - 1) / mu::LN_WARPS;
+        if (n_rows > 64) {
+            if (out_bf16) {
+                mu::prefer_shared_memory(reinterpret_cast<const void*>(mu::layernorm_rows_kernel<__nv_bfloat16, true>));
+                return mu::launch_pdl(mu::layernorm_rows_kernel<__nv_bfloat16, true>, dim3(blocks), dim3(mu::LN_WARPS * 32),
+                                      0, s, 1, x, rows, gamma, beta, (__nv_bfloat16*)y, n_rows, hidden, eps);
+            }
+            mu::prefer_shared_memory(reinterpret_cast<const void*>(mu::layernorm_rows_kernel<float, true>));
+            return mu::launch_pdl(mu::layernorm_rows_kernel<float, true>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0, s, 1,
+                                  x, rows, gamma, beta, (float*)y, n_rows, hidden, eps);
+        }
         if (out_bf16)
-            return mu::launch_pdl(mu::layernorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0, s,
-                                  1, x, rows, gamma, beta, (__nv_bfloat16*)y, n_rows, hidden, eps);
-        return mu::launch_pdl(mu::layernorm_rows_kernel<float>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0, s, 1, x,
+            return mu::launch_pdl(mu::layernorm_rows_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0,
+                                  s, 1, x, rows, gamma, beta, (__nv_bfloat16*)y, n_rows, hidden, eps);
+        return mu::launch_pdl(mu::layernorm_rows_kernel<float, false>, dim3(blocks), dim3(mu::LN_WARPS * 32), 0, s, 1, x,
                               rows, gamma, beta, (float*)y, n_rows, hidden, eps);
     }
     if (hidden > 12288) return MU_ERR_UNSUPPORTED_SIZE;   // the row must fit 48 KB of shared memory

@@ -35,9 +35,9 @@ static EncodeTiledFn encode_tiled() {
 // model asks for the same ones step after step (weights always, activations whenever the allocator hands
 // the same buffer back).
 struct MapKey {
-    const void* base; long long rows; int cols, box_rows; long long ld;
+    const void* base; long long rows; int cols, box_rows; long long ld; int kind;      // kind 0: operand tiles
     bool operator==(const MapKey& o) const {
-        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && ld == o.ld;
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && ld == o.ld && kind == o.kind;
     }
 };
 struct MapSlot { MapKey key; CUtensorMap map; bool used; };
@@ -47,12 +47,35 @@ static std::mutex map_mutex;
 static bool make_map_uncached(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows);
 
 bool tensor_map_bf16(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
-    const MapKey key = {base, rows, cols, box_rows, ld};
+    const MapKey key = {base, rows, cols, box_rows, ld, 0};
     const size_t h = ((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)rows * 31 + (size_t)cols * 131 + box_rows;
     MapSlot& slot = map_cache[(h >> 20) & 511];
     std::lock_guard<std::mutex> lock(map_mutex);
     if (slot.used && slot.key == key) { *map = slot.map; return true; }
     if (!make_map_uncached(map, base, rows, cols, ld, box_rows)) return false;
+    slot.key = key; slot.map = *map; slot.used = true;
+    return true;
+}
+
+// An output matrix [rows, cols] of bfloat16 or float32 with `ld` elements between rows, cut into boxes of
+// 32 x 32 that lie row after row in shared memory (no swizzle): what the epilogue's bulk stores write.
+bool tensor_map_out(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int is_bf16) {
+    const MapKey key = {base, rows, cols, 32, ld, is_bf16 ? 1 : 2};
+    const size_t h = ((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)rows * 37 + (size_t)cols * 113 + key.kind;
+    MapSlot& slot = map_cache[(h >> 20) & 511];
+    std::lock_guard<std::mutex> lock(map_mutex);
+    if (slot.used && slot.key == key) { *map = slot.map; return true; }
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const size_t elem_bytes = is_bf16 ? 2 : 4;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t elem[2] = {1, 1};
+    if (fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims,
+           strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
     slot.key = key; slot.map = *map; slot.used = true;
     return true;
 }

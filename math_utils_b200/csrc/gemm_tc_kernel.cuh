@@ -102,6 +102,60 @@ __device__ __forceinline__ void tc_finish_block(const uint32_t (&r)[32], float* 
     }
 }
 
+// The same block through a bulk store: every thread lays its row (bias and activation applied) into the warp's
+// patch, row after row, and one lane hands the 32 x 32 box to the copy engine, which writes it (or, where the
+// result is to be added to the float32 matrix that is there already, adds it: the residual stream never passes
+// through registers) and leaves out what lies beyond the matrix.  The warp goes on at once; it waits for the
+// engine to have read the patch only when it needs the patch again.
+template <int ACT, typename TC>
+__device__ __forceinline__ void tc_finish_block_bulk(const uint32_t (&r)[32], float* patch, int lane,
+                                                     const float* __restrict__ bias, const CUtensorMap* map_c,
+                                                     int N, int row0, int nb, bool add) {
+    float v[32];
+    if (bias) {
+        if (nb + 32 <= N && (((uintptr_t)(bias + nb)) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + nb) + i);      // the same for every lane
+                v[4 * i] = b4.x; v[4 * i + 1] = b4.y; v[4 * i + 2] = b4.z; v[4 * i + 3] = b4.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = nb + i < N ? __ldg(bias + nb + i) : 0.0f;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = tc_act<ACT>(__uint_as_float(r[i]) + v[i], sizeof(TC) == 2);
+    if (lane == 0) tma_store_wait_read();                  // the copy engine has read what the patch held before
+    __syncwarp();
+    if (sizeof(TC) == 2) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(patch) + lane * 64);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * e], v[8 * j + 2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(patch) + lane * 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        if (add) tma_add_2d(map_c, patch, nb, row0);
+        else tma_store_2d(map_c, patch, nb, row0);
+    }
+}
+
 // A 32 x 32 block of a partial accumulator to the workspace (a tile's part is [128][BN] float32), turned in
 // the patch so that an instruction stores 128 bytes of one row.
 __device__ __forceinline__ void tc_store_partial(const uint32_t (&r)[32], float* patch, int lane, float* ws_block,
@@ -177,6 +231,9 @@ template <int BN, int STAGES, int KSUB>
 struct TcSmem {
     __nv_bfloat16 a[STAGES][KSUB][TC_BM * TC_BK];      // each sub-tile 1024-byte aligned: rows of 128 bytes
     __nv_bfloat16 b[STAGES][KSUB][BN * TC_BK];
+    // where each epilogue warp turns a 32 x 32 block before it stores it, or lays it out row after row for a bulk
+    // store: 4,224 bytes each, a multiple of 128 (what a bulk store's source must be aligned to)
+    alignas(128) float patch[TC_EPI_WARPS][32 * TC_PATCH_PITCH];
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t acc_full[2];                        // an accumulator is complete (tensor cores -> epilogue)
@@ -185,8 +242,6 @@ struct TcSmem {
     uint64_t split_decided;                      // ... and one of them has drawn the tile's ticket
     uint32_t tmem_base;
     int split_last;                              // this block drew the last ticket: it finishes the tile
-    alignas(16) float patch[TC_EPI_WARPS][32 * TC_PATCH_PITCH + 8];   // where each epilogue warp turns a 32 x 32 block
-                                                     // (a multiple of 16 bytes each: packed rows go in 16-byte pieces)
 };
 
 // Persistent: a block per SM walks over the tiles of C (tile = block, block + grid, ...); the ring of
@@ -196,9 +251,9 @@ struct TcSmem {
 template <int BN, int STAGES, int KSUB, typename TC, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const float* __restrict__ bias, const float* residual, TC* C, int M, int N, int K,
-               long long ldc, long long ldr, int act, int* status, int splits, float* split_ws,
-               int* split_tickets) {
+               const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias, const float* residual, TC* C,
+               int M, int N, int K, long long ldc, long long ldr, int act, int* status, int splits, float* split_ws,
+               int* split_tickets, int bulk_out) {
     extern __shared__ unsigned char tc_raw[];
     TcSmem<BN, STAGES, KSUB>& sm =
         *reinterpret_cast<TcSmem<BN, STAGES, KSUB>*>(((uintptr_t)tc_raw + 1023) & ~(uintptr_t)1023);
@@ -266,6 +321,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
+            // The descriptors of stage 0, sub-tile 0, k = 0; every other operand tile is a fixed number of
+            // 16-byte units further on (the address sits in the low bits of the descriptor), so that one
+            // issuing thread, whose every instruction waits for the one before, spends an addition per
+            // operand and not a dozen instructions building it.
+            const uint64_t a_desc0 = smem_desc_sw128(smem_u32(sm.a[0][0]));
+            const uint64_t b_desc0 = smem_desc_sw128(smem_u32(sm.b[0][0]));
+            constexpr uint32_t A_SUB = TC_BM * TC_BK * sizeof(__nv_bfloat16) / 16, B_SUB = BN * TC_BK * sizeof(__nv_bfloat16) / 16;
             long long it = 0;
             int local = 0;
             for (int item = blockIdx.x; item < tiles && ok; item += gridDim.x, ++local) {
@@ -282,14 +344,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbar_wait(&sm.full[s], (uint32_t)((it / STAGES) & 1));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t a_stage = a_desc0 + (uint64_t)((uint32_t)s * (KSUB * A_SUB));
+                    const uint64_t b_stage = b_desc0 + (uint64_t)((uint32_t)s * (KSUB * B_SUB));
 #pragma unroll
                     for (int u = 0; u < KSUB; ++u) {
-                        const uint32_t a_addr = smem_u32(sm.a[s][u]), b_addr = smem_u32(sm.b[s][u]);
 #pragma unroll
                         for (int k = 0; k < TC_BK / 16; ++k) {
-                            // 16 elements of k = 32 bytes further along the swizzled 128-byte rows
-                            umma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                                      (kb > kb_begin || u > 0 || k > 0) ? 1u : 0u);
+                            // 16 elements of k = 32 bytes (two units) further along the swizzled 128-byte rows
+                            umma_bf16(tmem_d, a_stage + (uint64_t)(u * A_SUB + 2 * k), b_stage + (uint64_t)(u * B_SUB + 2 * k),
+                                      idesc, (kb > kb_begin || u > 0 || k > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&sm.empty[s]);            // the stage is free once these have read it
@@ -408,6 +471,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 const int nb = n0 + c0;
                 if (row0 >= M || nb >= N) continue;                   // the same for the whole warp
+                if (bulk_out) {
+                    // bulk_out 1: stored; 2: added to the matrix that is there (the residual, in place)
+                    if (act == ACT_GELU_NEW)
+                        tc_finish_block_bulk<ACT_GELU_NEW, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
+                    else if (act == ACT_GELU_ERF)
+                        tc_finish_block_bulk<ACT_GELU_ERF, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
+                    else
+                        tc_finish_block_bulk<0, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
+                    continue;
+                }
                 // the activation is the same for the whole launch: chosen here, outside the loops over the
                 // elements (inside them the compiler evaluated every activation for every element)
                 if (act == ACT_GELU_NEW)
@@ -423,6 +496,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     }
+    if (bulk_out && warp >= 2 && lane == 0) tma_store_wait_all();      // this warp's bulk stores have landed
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -444,14 +518,24 @@ template <int BN, int STAGES, int KSUB, typename TC, bool SPLIT>
 static int launch_tc(const void* A, const void* W, const float* bias, const float* residual, TC* C, int M, int N,
                      int K, long long lda, long long ldw, long long ldc, long long ldr, int act, int* status,
                      int splits, cudaStream_t s) {
-    CUtensorMap map_a, map_w;
+    CUtensorMap map_a, map_w, map_c;
     if (!tensor_map_bf16(&map_a, A, M, K, lda, TC_BM) || !tensor_map_bf16(&map_w, W, N, K, ldw, BN)) return MU_ERR_LAUNCH;
+    // The epilogue hands whole 32 x 32 boxes to the copy engine where the output allows it (16-byte aligned
+    // rows) and the residual, if any, is the output itself (then the boxes are added in place); products cut
+    // along K finish their tiles from the workspace instead.
+    int bulk_out = 0;
+    if (!SPLIT && (((uintptr_t)C) & 15) == 0 && (ldc * (long long)sizeof(TC)) % 16 == 0 &&
+        (residual == nullptr || (sizeof(TC) == 4 && (const void*)residual == (const void*)C && ldr == ldc)) &&
+        tensor_map_out(&map_c, C, M, N, ldc, sizeof(TC) == 2))
+        bulk_out = residual ? 2 : 1;
+    if (!bulk_out) map_c = map_a;                    // a valid descriptor that is never used
     auto kernel = gemm_tc_kernel<BN, STAGES, KSUB, TC, SPLIT>;
     const size_t smem = sizeof(TcSmem<BN, STAGES, KSUB>) + 1024;
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return MU_ERR_LAUNCH;
+        prefer_shared_memory(reinterpret_cast<const void*>(kernel));
         raised = true;
     }
     const int sms = sm_count();
@@ -469,8 +553,8 @@ static int launch_tc(const void* A, const void* W, const float* bias, const floa
     }
     const long long items = tiles * splits;
     dim3 grid((unsigned)(items < sms ? items : sms));
-    return launch_pdl(kernel, grid, dim3(TC_THREADS), smem, s, 1, map_a, map_w, bias, residual, C, M, N, K, ldc, ldr,
-                      act, status, splits, g_split.parts, g_split.tickets);
+    return launch_pdl(kernel, grid, dim3(TC_THREADS), smem, s, 1, map_a, map_w, map_c, bias, residual, C, M, N, K, ldc, ldr,
+                      act, status, splits, g_split.parts, g_split.tickets, bulk_out);
 }
 
 }  // namespace mu

@@ -698,6 +698,41 @@ def _layernorm_gemm_tc(x: "NormedInput", weight, bias, act, residual, out, out_d
     return out
 
 
+# ------------------------------------------------------ a whole layer of a prompt step in one call
+class PromptLayerArgs(ctypes.Structure):
+    """Everything ``mu_prompt_layer`` needs; the layout is ``MuPromptLayerArgs`` of prompt_layer.cu."""
+    _fields_ = (
+        [(n, _c_p) for n in ("x", "normed", "qkv", "attn", "inner_buf", "tok_pos", "tok_seq", "block_table",
+                             "tiles_wide", "tiles", "status", "stream", "kv_pages", "ln1_gamma", "ln1_beta",
+                             "qkv_weight", "qkv_bias", "out_weight", "out_bias", "ln2_gamma", "ln2_beta",
+                             "up_weight", "up_bias", "down_weight", "down_bias")]
+        + [(n, _c_ll) for n in ("n_cache_pages", "ld_qkv_weight", "ld_out_weight", "ld_up_weight", "ld_down_weight")]
+        + [(n, _c_f) for n in ("eps1", "eps2", "scale")]
+        + [(n, _c_int) for n in ("n_tokens", "hidden", "inner", "n_heads", "n_kv_heads", "head_dim", "window", "act",
+                                 "max_pages", "page_tokens", "n_tiles_wide", "n_tiles", "owns_cache")])
+
+
+_PROMPT_LAUNCHES = ("", "the norm and the q | k | v product", "the cache append and the attention", "the output projection",
+                    "the norm and the feed-forward's first product", "the feed-forward's second product")
+
+
+def prompt_layer(args: PromptLayerArgs) -> None:
+    """Issues the launches of one pre-norm layer of a prompt step (eight kernels) from one call."""
+    lib = library()
+    fn = lib.mu_prompt_layer
+    if fn.argtypes is None:
+        if lib.mu_prompt_layer_args_size() != ctypes.sizeof(PromptLayerArgs):
+            raise KernelError("the layer-call layout of the Python side and of the kernel library differ")
+        fn.argtypes, fn.restype = [ctypes.POINTER(PromptLayerArgs)], _c_int
+    args.stream = _stream()
+    code = fn(ctypes.byref(args))
+    if code != 0:
+        raise KernelError(f"prompt layer, {_PROMPT_LAUNCHES[min(code // 100, 5)]}: "
+                          f"{_ERRORS.get(code % 100, f'error {code % 100}')}")
+    global launch_count
+    launch_count += 7 + int(bool(args.owns_cache))
+
+
 # -------------------------------------------------------------------- dispatch
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            act: Optional[str] = None, residual: Optional[torch.Tensor] = None,

@@ -146,4 +146,25 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // 128-byte swizzle (gemm_tc.cu; descriptors are cached by address and shape).  False if the driver refuses.
 bool tensor_map_bf16(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows);
 
+// An output matrix [rows, cols] of bfloat16 or float32, cut into boxes of 32 x 32 without swizzle, for the
+// bulk stores (and bulk additions) of an epilogue.  The base must be 16-byte aligned and rows 16 bytes apart
+// or a multiple.  False if the driver refuses.
+bool tensor_map_out(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int is_bf16);
+
+// A 32 x 32 box from shared memory (rows one after another) to its place in the matrix, or added to what is
+// there; whatever lies outside the matrix is left out.  One thread issues it, commits the group, and later
+// waits (tma_store_wait_read before the shared memory is written again, tma_store_wait_all before the end).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 }  // namespace mu

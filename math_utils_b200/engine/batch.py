@@ -149,8 +149,9 @@ class StepContext:
 
 
 def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts: Sequence[int],
-                  ring: PinnedRing, workspace: dict, trace=None) -> StepContext:
-    """Packs the step's index arrays and sends them to the device."""
+                  ring: PinnedRing, workspace: dict, trace=None, tokens=None) -> StepContext:
+    """Packs the step's index arrays and sends them to the device.  ``tokens``: the entries' tokens as
+    integer arrays, if the caller has them already."""
     q_lens = [len(e.tokens) for e in entries]
     n_tokens, n_seqs = sum(q_lens), len(entries)
     n_want = sum(len(e.want) for e in entries)
@@ -178,7 +179,7 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
     flat = 0
     for s, e in enumerate(entries):
         n = q_lens[s]
-        h[offsets[0] + flat: offsets[0] + flat + n] = np.asarray(e.tokens, dtype=np.int32)
+        h[offsets[0] + flat: offsets[0] + flat + n] = tokens[s] if tokens is not None else np.asarray(e.tokens, dtype=np.int32)
         h[offsets[1] + flat: offsets[1] + flat + n] = np.arange(starts[s], starts[s] + n, dtype=np.int32)
         h[offsets[2] + flat: offsets[2] + flat + n] = s
         for w in e.want:

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import SequenceCache
@@ -95,13 +96,15 @@ class DecoderModel:
             return None
         if len({e.slot for e in entries}) != len(entries):
             raise ValueError("a slot appears twice in one step")
-        for e in entries:
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
-            if bad:
-                raise ValueError(f"token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
+        # the tokens once as arrays: checked here, packed for the device by build_context
+        tokens = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+        for ids in tokens:
+            if ids.ndim != 1 or int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
+                bad = [int(t) for t in ids.reshape(-1) if not 0 <= int(t) < self.vocab_size]
+                raise ValueError(f"token id {bad[0] if bad else ids} is outside the vocabulary of {self.vocab_size}")
         starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
         ctx = build_context(self.runtime, self.assembly.position, cache, entries, starts,
-                            self._ring, self._workspace, trace)
+                            self._ring, self._workspace, trace, tokens)
         logits = self.forward(ctx, cache)
         for e in entries:
             cache.commit(e.slot, len(e.tokens))

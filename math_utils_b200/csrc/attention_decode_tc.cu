@@ -81,8 +81,12 @@ __device__ __forceinline__ bool td_wait(uint64_t* bar, uint32_t parity) {
     }
 }
 
-template <int KD, int NW, int RING>
-__global__ void __launch_bounds__(NW * 32)
+// NG groups of SUB warps: a group owns a ring of RING page buffers and takes every NG-th page of the
+// sequence; its SUB warps share each page, KPW = 64 / SUB keys a warp.  More warps on the same bytes in
+// flight: a warp's work on a page is a chain of dependent steps (fragments in, scores, softmax, weighted
+// values), and an SM hides one chain behind the others only if there are enough of them.
+template <int KD, int NG, int SUB, int RING>
+__global__ void __launch_bounds__(NG * SUB * 32)
 attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
                              const __nv_bfloat16* __restrict__ k_new, long long ldk,
                              const __nv_bfloat16* __restrict__ v_new, long long ldv,
@@ -90,28 +94,38 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
                              const int* __restrict__ block_table, int max_pages,
                              const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
                              int n_kv_heads, float scale, int window, int* status) {
+    constexpr int NW = NG * SUB;
     constexpr int DH = 16 * KD;
     constexpr int KV4 = KD / 2;                    // 16-byte pieces of a key row that a thread holds
+    constexpr int KPW = TD_PAGE / SUB;             // keys of a page that one warp takes
+    constexpr int TJ = KPW / 8;                    // score tiles of 8 keys
+    constexpr int KT = KPW / 4;                    // consecutive keys whose scores one thread ends up holding
+    constexpr int KK = KPW / 16;                   // steps of 16 positions in the second product
     constexpr int PAGE_ELEMS = TD_PAGE * DH;       // one kv head's keys (or values) of a page
     constexpr uint32_t PAGE_BYTES = PAGE_ELEMS * sizeof(__nv_bfloat16);
+    static_assert(SUB == 1 || SUB == 2 || SUB == 4, "a warp takes 64, 32 or 16 keys of a page");
     extern __shared__ __align__(128) unsigned char ring_raw[];
-    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(ring_raw);              // [NW][RING][2][PAGE_ELEMS]
-    float* part_o = reinterpret_cast<float*>(ring_raw + (size_t)NW * RING * 2 * PAGE_BYTES);   // [NW][rows][DH + 1]
-    __shared__ uint64_t full[NW][RING];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(ring_raw);              // [NG][RING][2][PAGE_ELEMS]
+    float* part_o = reinterpret_cast<float*>(ring_raw + (size_t)NG * RING * 2 * PAGE_BYTES);   // [NW][rows][DH + 1]
+    __shared__ uint64_t full[NG][RING];            // a page has landed
+    __shared__ uint64_t done[NG][RING];            // every warp of the group has read it
     __shared__ float part_m[NW][16], part_l[NW][16];
     __shared__ float weight[NW][16];
     __shared__ int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = warp / SUB, sub = warp % SUB;
     const int g = lane >> 2, t = lane & 3;
     const int tk = blockIdx.x / n_kv_heads, kvh = blockIdx.x % n_kv_heads;
     const int rows = n_heads / n_kv_heads;
     pdl_trigger();
     if (threadIdx.x == 0) failed = 0;
-    if (lane == 0) {
+    if (lane == 0 && sub == 0) {
 #pragma unroll
-        for (int r = 0; r < RING; ++r)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(td_smem(&full[warp][r])) : "memory");
+        for (int r = 0; r < RING; ++r) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(td_smem(&full[group][r])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(td_smem(&done[group][r])), "r"(SUB) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -120,17 +134,18 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = first / TD_PAGE, last_page = pos / TD_PAGE;
     const long long head_stride = (long long)PAGE_ELEMS;
-    const int my_first = first_page + warp;
-    const int n_mine = my_first <= last_page ? (last_page - my_first) / NW + 1 : 0;
-    __nv_bfloat16* my_ring = ring + (size_t)warp * RING * 2 * PAGE_ELEMS;
+    const int my_first = first_page + group;
+    const int n_mine = my_first <= last_page ? (last_page - my_first) / NG + 1 : 0;
+    __nv_bfloat16* my_ring = ring + (size_t)group * RING * 2 * PAGE_ELEMS;
+    const bool issuer = sub == 0 && lane == 0;
 
-    // one lane asks for the warp's i-th page: two contiguous runs of the cache, one barrier
+    // one lane asks for the group's i-th page: two contiguous runs of the cache, one barrier
     auto issue = [&](int i) {
         const int slot = i % RING;
-        const long long page = pages[my_first + i * NW];
+        const long long page = pages[my_first + i * NG];
         const __nv_bfloat16* ksrc = kv + (page * 2 * n_kv_heads + kvh) * head_stride;
         const __nv_bfloat16* vsrc = ksrc + (long long)n_kv_heads * head_stride;
-        const uint32_t bar = td_smem(&full[warp][slot]);
+        const uint32_t bar = td_smem(&full[group][slot]);
         const uint32_t dst = td_smem(my_ring + (size_t)slot * 2 * PAGE_ELEMS);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * PAGE_BYTES) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -140,7 +155,7 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     };
     // rows written by earlier steps, which no kernel of this step touches, may be asked for at once
     int issued = 0;
-    if (lane == 0)
+    if (issuer)
         for (; issued < n_mine && issued < RING; ++issued) issue(issued);
     pdl_wait();                                    // this step's query, key and value from here on
 
@@ -178,107 +193,135 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     bool ok = true;
     for (int i = 0; i < n_mine; ++i) {
         const int slot = i % RING;
-        const int page_idx = my_first + i * NW;
-        if (!td_wait(&full[warp][slot], (uint32_t)((i / RING) & 1))) { ok = false; break; }
+        const int page_idx = my_first + i * NG;
+        if (!td_wait(&full[group][slot], (uint32_t)((i / RING) & 1))) { ok = false; break; }
         const __nv_bfloat16* ks = my_ring + (size_t)slot * 2 * PAGE_ELEMS;
         const __nv_bfloat16* vs = ks + PAGE_ELEMS;
         const int base = page_idx * TD_PAGE;
-        const int lo = max(first - base, 0), hi = min(pos + 1 - base, TD_PAGE);
-        const bool has_new = (k_new != nullptr) && page_idx == last_page;
+        // the keys of the page this warp takes: [key0, key0 + KPW); of those, [lo, hi) can be seen
+        const int key0 = sub * KPW;
+        const int lo = max(first - base, 0) - key0, hi = min(pos + 1 - base, TD_PAGE) - key0;      // relative to key0
+        const bool in_page = (k_new != nullptr) && page_idx == last_page;
+        const int new_key = pos - base - key0;                  // the step's own token, relative to key0
+        const bool has_new = in_page && new_key >= 0 && new_key < KPW;
         const __nv_bfloat16* kn = has_new ? k_new + (long long)tk * ldk + kvh * DH : nullptr;
         const __nv_bfloat16* vn = has_new ? v_new + (long long)tk * ldv + kvh * DH : nullptr;
-        const int new_key = hi - 1;
         if (has_new) {
-            // append to the cache: this block is the only one for this (sequence, kv head)
+            // append to the cache: this warp is the only one for this (sequence, kv head, key)
             const long long page = pages[page_idx];
             __nv_bfloat16* kpage = kv + (page * 2 * n_kv_heads + kvh) * head_stride;
             __nv_bfloat16* vpage = kpage + (long long)n_kv_heads * head_stride;
             for (int d = lane; d < DH; d += 32) {
-                kpage[(long long)new_key * DH + d] = kn[d];
-                vpage[(long long)d * TD_PAGE + new_key] = vn[d];
+                kpage[(long long)(key0 + new_key) * DH + d] = kn[d];
+                vpage[(long long)d * TD_PAGE + key0 + new_key] = vn[d];
             }
         }
-        const int jn = (new_key & 15) >> 1;
-        const bool mine_new = has_new && (16 * (g >> 1) + 2 * jn + (g & 1) == new_key);
+        if (hi > 0 && lo < KPW) {                               // some key of this warp's share can be seen
+            const int jn = (new_key % KT) >> 1;
+            const bool mine_new = has_new && (KT * (g >> 1) + 2 * jn + (g & 1) == new_key);
 
-        float s[8][4];
+            // S = Q K^T: TJ tiles of 8 keys; which key is column n of tile j: KT (n / 2) + 2 j + n % 2, so that
+            // a thread ends up with the scores of KT consecutive keys
+            float s[TJ][4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-            const int key = 16 * (g >> 1) + 2 * j + (g & 1);
-            uint4 kf[KV4];
-            const uint4* src = (mine_new && j == jn) ? reinterpret_cast<const uint4*>(kn + (DH / 4) * t)
-                                                     : reinterpret_cast<const uint4*>(ks + key * DH + (DH / 4) * t);
+            for (int j = 0; j < TJ; ++j) {
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+                const int key = key0 + KT * (g >> 1) + 2 * j + (g & 1);
+                uint4 kf[KV4];
+                const uint4* src = (mine_new && j == jn) ? reinterpret_cast<const uint4*>(kn + (DH / 4) * t)
+                                                         : reinterpret_cast<const uint4*>(ks + key * DH + (DH / 4) * t);
 #pragma unroll
-            for (int c = 0; c < KV4; ++c) kf[c] = src[c];
-            const uint32_t* kw = reinterpret_cast<const uint32_t*>(kf);
+                for (int c = 0; c < KV4; ++c) kf[c] = src[c];
+                const uint32_t* kw = reinterpret_cast<const uint32_t*>(kf);
 #pragma unroll
-            for (int kk = 0; kk < KD; ++kk) td_mma(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kw[2 * kk], kw[2 * kk + 1]);
-        }
-        float mx[2] = {m_run[0], m_run[1]};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = 16 * t + 2 * j + (e & 1);
-                const float v = (key >= lo && key < hi) ? s[j][e] * c_log2 : -INFINITY;
-                s[j][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                for (int kk = 0; kk < KD; ++kk) td_mma(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kw[2 * kk], kw[2 * kk + 1]);
             }
-        }
-        float corr[2], sum[2] = {0.0f, 0.0f};
+            float mx[2] = {m_run[0], m_run[1]};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            corr[r] = exp2f(m_run[r] - mx[r]);
-            m_run[r] = mx[r];
-        }
-        float w_new[2] = {0.0f, 0.0f};
-        uint32_t pa[4][4];
+            for (int j = 0; j < TJ; ++j) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float p[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                p[e] = exp2f(s[j][e] - mx[e >> 1]);
-                sum[e >> 1] += p[e];
-                if (has_new && 16 * t + 2 * j + (e & 1) == new_key) { w_new[e >> 1] = p[e]; p[e] = 0.0f; }
+                for (int e = 0; e < 4; ++e) {
+                    const int key = KT * t + 2 * j + (e & 1);
+                    const float v = (key >= lo && key < hi) ? s[j][e] * c_log2 : -INFINITY;
+                    s[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
             }
-            pa[j >> 1][(j & 1) * 2] = td_pack(p[0], p[1]);
-            pa[j >> 1][(j & 1) * 2 + 1] = td_pack(p[2], p[3]);
-        }
+            float corr[2], sum[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + sum[r];
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));      // finite: a key can be seen
+                corr[r] = exp2f(m_run[r] - mx[r]);
+                m_run[r] = mx[r];
+            }
+            // probabilities; the new key's is set aside (its value is not in the cache yet) and kept as w_new
+            float w_new[2] = {0.0f, 0.0f};
+            uint32_t pa[KK][4];
 #pragma unroll
-        for (int j = 0; j < 2 * KD; ++j) {
-            o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0]; o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
-            const uint4* src = reinterpret_cast<const uint4*>(vs + (8 * j + g) * TD_PAGE + 16 * t);
-            uint4 vf[2] = {src[0], src[1]};
-            const uint32_t* vw = reinterpret_cast<const uint32_t*>(vf);
+            for (int j = 0; j < TJ; ++j) {
+                float p[4];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-                td_mma(o_acc[j], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], vw[2 * kk], vw[2 * kk + 1]);
-        }
-        if (has_new) {
-            const int src_lane = (lane & ~3) | ((new_key >> 4) & 3);
-            const float w0 = __shfl_sync(0xffffffffu, w_new[0], src_lane);
-            const float w1 = __shfl_sync(0xffffffffu, w_new[1], src_lane);
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = exp2f(s[j][e] - mx[e >> 1]);
+                    sum[e >> 1] += p[e];
+                    if (has_new && KT * t + 2 * j + (e & 1) == new_key) { w_new[e >> 1] = p[e]; p[e] = 0.0f; }
+                }
+                pa[j >> 1][(j & 1) * 2] = td_pack(p[0], p[1]);
+                pa[j >> 1][(j & 1) * 2 + 1] = td_pack(p[2], p[3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * corr[r] + sum[r];
+            // O = O * corr + P V: tiles of 8 dimensions, KK steps of 16 positions; a thread's KT positions of a
+            // dimension row are one run of the page
 #pragma unroll
             for (int j = 0; j < 2 * KD; ++j) {
-                const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vn + 8 * j + 2 * t));
-                o_acc[j][0] = fmaf(w0, v.x, o_acc[j][0]); o_acc[j][1] = fmaf(w0, v.y, o_acc[j][1]);
-                o_acc[j][2] = fmaf(w1, v.x, o_acc[j][2]); o_acc[j][3] = fmaf(w1, v.y, o_acc[j][3]);
+                o_acc[j][0] *= corr[0]; o_acc[j][1] *= corr[0]; o_acc[j][2] *= corr[1]; o_acc[j][3] *= corr[1];
+                const __nv_bfloat16* vrow = vs + (8 * j + g) * TD_PAGE + key0 + KT * t;
+                uint32_t vw[2 * KK];
+                if constexpr (KT == 16) {
+                    const uint4 a4 = reinterpret_cast<const uint4*>(vrow)[0], b4 = reinterpret_cast<const uint4*>(vrow)[1];
+                    vw[0] = a4.x; vw[1] = a4.y; vw[2] = a4.z; vw[3] = a4.w; vw[4] = b4.x; vw[5] = b4.y; vw[6] = b4.z; vw[7] = b4.w;
+                } else if constexpr (KT == 8) {
+                    const uint4 a4 = reinterpret_cast<const uint4*>(vrow)[0];
+                    vw[0] = a4.x; vw[1] = a4.y; vw[2] = a4.z; vw[3] = a4.w;
+                } else {
+                    const uint2 a2 = reinterpret_cast<const uint2*>(vrow)[0];
+                    vw[0] = a2.x; vw[1] = a2.y;
+                }
+#pragma unroll
+                for (int kk = 0; kk < KK; ++kk)
+                    td_mma(o_acc[j], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], vw[2 * kk], vw[2 * kk + 1]);
+            }
+            if (has_new) {
+                // every thread of a row's group needs the new key's weight: it sits in the thread with t = new_key / KT
+                const int src_lane = (lane & ~3) | ((new_key / KT) & 3);
+                const float w0 = __shfl_sync(0xffffffffu, w_new[0], src_lane);
+                const float w1 = __shfl_sync(0xffffffffu, w_new[1], src_lane);
+#pragma unroll
+                for (int j = 0; j < 2 * KD; ++j) {
+                    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vn + 8 * j + 2 * t));
+                    o_acc[j][0] = fmaf(w0, v.x, o_acc[j][0]); o_acc[j][1] = fmaf(w0, v.y, o_acc[j][1]);
+                    o_acc[j][2] = fmaf(w1, v.x, o_acc[j][2]); o_acc[j][3] = fmaf(w1, v.y, o_acc[j][3]);
+                }
             }
         }
-        __syncwarp();                              // every lane has read the buffer: it may be filled again
-        if (lane == 0 && issued < n_mine) issue(issued++);
+        __syncwarp();                              // every lane has read the buffer
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(td_smem(&done[group][slot])) : "memory");
+        if (issuer && issued < n_mine) {
+            // the slot is filled again once every warp of the group has read it; if that never happens the
+            // page is not asked for, and the warps that wait for it give up in their turn
+            if (td_wait(&done[group][slot], (uint32_t)((i / RING) & 1))) issue(issued++);
+            else atomicExch(status, 4);
+        }
     }
     if (!ok) {
         // let the copies still under way land before the block goes away, then report
-        if (lane == 0) {
+        if (issuer) {
             for (int i = 0; i < issued; ++i)
-                if (i + RING >= issued) td_wait(&full[warp][i % RING], (uint32_t)((i / RING) & 1));
+                if (i + RING >= issued) td_wait(&full[group][i % RING], (uint32_t)((i / RING) & 1));
+        }
+        if (lane == 0) {
             atomicExch(status, 4);
             failed = 1;
         }
@@ -330,8 +373,8 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
 }  // namespace mu
 
 // Arguments as mu_attention_decode (bfloat16 only).  n_warps 2 (many blocks: three of them share an SM) or
-// 6 (few blocks: all pages in flight at once); `status` is a device word that is set to 4 if a wait for a
-// copy runs out.
+// 6 (few blocks: all pages in flight at once) groups of warps, each group a ring of pages; `status` is a
+// device word that is set to 4 if a wait for a copy runs out.
 MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k_new, long long ldk,
                                      const void* v_new, long long ldv, void* out, long long ldo, void* kv,
                                      const int* block_table, int max_pages, int page_tokens,
@@ -352,11 +395,11 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
     cudaStream_t s = (cudaStream_t)stream;
     int rc = MU_ERR_UNSUPPORTED_SIZE;
     const int rows = n_heads / n_kv_heads;
-#define MU_TR(KD, NW)                                                                                          \
+#define MU_TR(KD, NG, SUB)                                                                                     \
     do {                                                                                                       \
-        auto kernel = mu::attention_decode_ring_kernel<KD, NW, 2>;                                             \
-        const size_t smem = (size_t)NW * 2 * 2 * mu::TD_PAGE * 16 * KD * sizeof(__nv_bfloat16) +               \
-                            (size_t)NW * rows * (16 * KD + 1) * sizeof(float);                                 \
+        auto kernel = mu::attention_decode_ring_kernel<KD, NG, SUB, 2>;                                        \
+        const size_t smem = (size_t)NG * 2 * 2 * mu::TD_PAGE * 16 * KD * sizeof(__nv_bfloat16) +               \
+                            (size_t)NG * SUB * rows * (16 * KD + 1) * sizeof(float);                           \
         static bool raised = false;                                                                            \
         if (!raised) {                                                                                         \
             if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=       \
@@ -365,19 +408,22 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
             raised = true;                                                                                     \
         }                                                                                                      \
         if (smem > 200 * 1024) return MU_ERR_UNSUPPORTED_SIZE;                                                 \
-        rc = mu::launch_pdl(kernel, dim3((unsigned)blocks), dim3(NW * 32), smem, s, 1,                         \
+        rc = mu::launch_pdl(kernel, dim3((unsigned)blocks), dim3(NG * SUB * 32), smem, s, 1,                   \
             (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_new, ldk, (const __nv_bfloat16*)v_new, ldv,  \
             (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, n_heads,   \
             n_kv_heads, scale, window, status);                                                                \
     } while (0)
-    // six warps with their rings and many query heads per kv head may not fit: then two warps do it
+    // six groups with their rings and many query heads per kv head may not fit: then two groups do it.  With
+    // many blocks (two groups each, three blocks an SM) two warps share each page where the head is small
+    // enough for the registers to allow it: more chains of work for the SM to switch between.  With few blocks
+    // a warp per page is the shorter chain.
     const size_t six = (size_t)6 * 2 * 2 * mu::TD_PAGE * head_dim * sizeof(__nv_bfloat16) +
                        (size_t)6 * rows * (head_dim + 1) * sizeof(float);
     const bool wide = n_warps >= 6 && six <= 200 * 1024;
-    if (head_dim == 32) { if (wide) MU_TR(2, 6); else MU_TR(2, 2); }
-    else if (head_dim == 64) { if (wide) MU_TR(4, 6); else MU_TR(4, 2); }
-    else if (head_dim == 96) MU_TR(6, 2);
-    else MU_TR(8, 2);
+    if (head_dim == 32) { if (wide) MU_TR(2, 6, 1); else MU_TR(2, 2, 2); }
+    else if (head_dim == 64) { if (wide) MU_TR(4, 6, 1); else MU_TR(4, 2, 2); }
+    else if (head_dim == 96) MU_TR(6, 2, 1);
+    else MU_TR(8, 2, 1);
 #undef MU_TR
     return rc;
 }

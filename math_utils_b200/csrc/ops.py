@@ -295,10 +295,11 @@ def status_word(device) -> torch.Tensor:
 
 
 def _rows_kernel(m: int, n: int, k: int) -> bool:
-    """Whether a product of m rows goes to ``mu_gemm_rows``: 33 to 64 rows always; up to 32 rows where the
+    """Whether a product of m rows goes to ``mu_gemm_rows``: 33 to 64 rows always; 17 to 32 rows where the
     weights are 16 million or more (the output head, which that kernel streams faster than the few-rows
-    kernel even with the norm as a launch of its own)."""
-    return 33 <= m <= 64 or (m <= 32 and n * k >= (1 << 24))
+    kernel does at that many rows).  Up to 16 rows the few-rows kernel with the norm folded in stays ahead
+    inside a step, where its weights are on their way while the kernels before it end."""
+    return 33 <= m <= 64 or (17 <= m <= 32 and n * k >= (1 << 24))
 
 
 def _split_workspace(device) -> None:

@@ -48,7 +48,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--config", help="with --random: a config.json to invent weights for")
     ap.add_argument("--fp32", action="store_true", help="the true 32-bit path instead of bfloat16")
     ap.add_argument("--stop", help="stop token ids (default: eos_token_id of config.json)")
-    ap.add_argument("--profile", action="store_true", help="print load, prompt and decode timings")
+    ap.add_argument("--profile", action="store_true",
+                    help="print load time and, per answer, prompt and generation rates and per-stage device times "
+                         "(steps then run one by one instead of from recorded graphs)")
     ap.add_argument("--load-only", action="store_true", help="load, report, and exit")
     return ap
 
@@ -75,7 +77,8 @@ def main(argv=None) -> int:
     from .llm import LLM, Options
     t0 = time.time()
     llm = LLM(model_dir, Options(context=args.ctx, max_tokens=args.tokens, temperature=args.temp,
-                                 top_k=args.topk, seed=args.seed, dtype="float32" if args.fp32 else "bfloat16"))
+                                 top_k=args.topk, seed=args.seed, dtype="float32" if args.fp32 else "bfloat16",
+                                 profile=args.profile))
     if args.stop is not None:
         llm.model.stop_ids = tuple(parse_ids(args.stop))
     load_s = time.time() - t0
@@ -85,21 +88,26 @@ def main(argv=None) -> int:
     if args.load_only:
         return 0
 
-    last = {}
-
     def run(ids: List[int]) -> None:
-        import torch
-        torch.cuda.synchronize()
-        t = time.time()
         out = llm.prompt(ids)
-        torch.cuda.synchronize()
-        last.update(prompt=len(ids), produced=len(out), seconds=time.time() - t)
         print(" ".join(str(t) for t in out), flush=True)
 
     def stats() -> None:
-        if last:
-            print(f"prompt {last['prompt']} tokens, produced {last['produced']} tokens in {last['seconds']:.3f}s "
-                  f"({last['produced'] / max(last['seconds'], 1e-9):.1f} tok/s incl. prompt)")
+        """Prompt and generation apart, as the reference reports them (src/LLM.cpp:716-730)."""
+        last = llm.last
+        if not last:
+            return
+        made = max(last["produced"] - 1, 0)               # the first token comes out of the prompt step
+        print(f"  prompt {last['prompt_tokens']} tok in {last['prompt_s']:.4f}s "
+              f"({last['prompt_tokens'] / max(last['prompt_s'], 1e-9):.1f} tok/s)   "
+              f"generated {made} tok in {last['decode_s']:.4f}s ({made / max(last['decode_s'], 1e-9):.1f} tok/s)   "
+              f"context {last['context_used']}/{last['context']}")
+        if llm.stage_times:
+            from .engine.stage_timer import STAGE_NAMES
+            print("  stage                              prompt(s)   decode(s)")
+            for kind, (prompt_s, decode_s) in llm.stage_times.items():
+                if prompt_s or decode_s:
+                    print(f"  {STAGE_NAMES.get(kind, kind):<33} {prompt_s:9.4f}   {decode_s:9.4f}")
 
     if args.prompt is not None:
         run(parse_ids(args.prompt))

@@ -53,16 +53,6 @@ struct PtSmem {
     int failed;
 };
 
-// Optional time stamps for measurements (mu_attention_prefill_tc_trace): block 0 writes its SM's clock per page:
-// [4 j + 0] scores issued, [4 j + 1] P V issued (the issuing lane), [4 j + 2] scores loaded, [4 j + 3] P handed
-// over (first thread of the page's softmax group); 64 pages at most.
-__device__ unsigned long long* g_pt_trace = nullptr;
-__device__ __forceinline__ void pt_stamp(unsigned long long* trace, int word) {
-    if (trace && blockIdx.x == 0 && word < 256) {
-        trace[word] = (unsigned long long)clock64();
-    }
-}
-
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -111,7 +101,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sm.tmem_base;
-    unsigned long long* const trace = g_pt_trace;
     pdl_trigger();
     pdl_wait();                                      // queries and this step's cache rows come from the kernels before
 
@@ -190,7 +179,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     umma_bf16(tmem_base + 64 * g, smem_desc_sw128(q_addr + k * 32), smem_desc_sw128(k_addr + k * 32), idesc,
                               k > 0 ? 1u : 0u);
                 umma_commit(&sm.s_full[g]);
-                pt_stamp(trace, 4 * j);
             }
             if (!ok) {
                 atomicExch(status, 6);
@@ -216,7 +204,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     umma_bf16(tmem_base + 128 + 128 * g + 64 * b, smem_desc_sw128(p_addr + k * 32),
                               smem_desc_sw128(v_addr + k * 32), idesc, k > 0 ? 1u : 0u);
                 umma_commit(&sm.pv_full[g][b]);
-                pt_stamp(trace, 4 * j + 1);
             }
             if (!ok) {
                 atomicExch(status, 6);
@@ -279,7 +266,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 mbar_arrive(&sm.s_free[grp]);
                 mbar_arrive(&sm.k_empty[j % PT_STAGES]);         // the scores are complete: the keys have been read
             }
-            if (row == 0) pt_stamp(trace, 4 * j + 2);
             // columns [lo, hi] of the page are visible to this row (all 64 if the page lies before the tile)
             const int hi = min(qpos - key0, PT_K - 1);
             const int lo = window > 0 ? max(qpos - window + 1 - key0, 0) : 0;
@@ -324,7 +310,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the tensor cores read P through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full[grp][b]);
-            if (row == 0) pt_stamp(trace, 4 * j + 3);
             // the group's page before this one: its P V joins the output row
             if (u >= 1) {
                 ok = take_pv(u - 1, corr_prev);
@@ -398,12 +383,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 }
 
 }  // namespace mu
-
-// For measurements: a device buffer of 256 64-bit words for block 0's time stamps (see pt_stamp), or null.
-MU_EXPORT int mu_attention_prefill_tc_trace(void* buffer) {
-    unsigned long long* p = (unsigned long long*)buffer;
-    return cudaMemcpyToSymbol(mu::g_pt_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -1;
-}
 
 // q: bfloat16 rows of n_heads x 64 (ldq elements apart, n_tokens of them); kv: the paged cache of
 // n_cache_pages pages; tiles: int32 [n_tiles][2] = (flat index of the tile's first query token, number of

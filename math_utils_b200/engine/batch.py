@@ -86,7 +86,8 @@ class StepContext:
         makes its own."""
         if self.trace is not None:
             if hasattr(tensor, "materialize"):
-                tensor = tensor.materialize_copy()
+                # (a trace that only keeps time does not look at values: nothing is computed for it)
+                tensor = tensor.materialize_copy() if getattr(self.trace, "wants_values", True) else None
             self.trace(self.tag + name, tensor)
 
     @property

@@ -122,7 +122,8 @@ def run_batch(step: Callable, sample: Callable, acquire: Callable, release: Call
 
 
 def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[RequestState], stop_ids,
-                      max_tokens: int, context: int, kept_slots: Optional[Sequence[int]] = None) -> None:
+                      max_tokens: int, context: int, kept_slots: Optional[Sequence[int]] = None,
+                      first_sample: Optional[list] = None) -> None:
     """The same batch as ``run_batch``, with the single-token steps replayed
     from CUDA graphs (``DecodeSession``, pipelined).  The prompts run as one
     eager step.  Then the host stays one step behind the device: each step's
@@ -165,6 +166,9 @@ def run_batch_graphed(model, cache, params: SamplingParams, states: Sequence[Req
         logits = model.step(cache, [StepEntry(slots[k], list(states[k].prompt), [len(states[k].prompt) - 1])
                                     for k in live])
         tokens = sampler.sample(logits).cpu().tolist()
+        if first_sample is not None:
+            import time
+            first_sample.append(time.perf_counter())       # the prompt step is over: the caller times it apart
         check_kernels(model)
         draws = {k: 1 for k in live}
         feed = {}
@@ -301,31 +305,48 @@ class _GraphedStretch:
 
 
 def run_requests(model, cache, params: SamplingParams, states: Sequence[RequestState], stop_ids, max_tokens: int,
-                 context: int, kept_slots: Optional[Sequence[int]] = None, use_graph: bool = True) -> None:
+                 context: int, kept_slots: Optional[Sequence[int]] = None, use_graph: bool = True,
+                 timing: Optional[dict] = None, stage_timer=None) -> None:
     """One batch through the loop that fits the model: graph replay where every
     part can be replayed, eager steps otherwise.  Everything that generates
-    (``generate``, ``LLM.prompt``, the command line) comes through here."""
-    if use_graph and getattr(model, "graph_safe", True):
-        run_batch_graphed(model, cache, params, states, stop_ids, max_tokens, context, kept_slots)
-        return
-    ops = model.runtime.ops
-    sampler = Sampler(params, [s.index for s in states], model.runtime.device, ops)
-    n = len(states)
+    (``generate``, ``LLM.prompt``, the command line) comes through here.
 
-    def sample(logits, rows):
-        tokens = sampler.sample(logits, None if len(rows) == n else rows).cpu().tolist()
-        check_kernels(model)
-        return tokens
+    ``timing``: a dict that receives ``prompt_s`` (the prompt step up to its
+    first sample) and ``decode_s`` (everything after), as the reference times
+    them apart (src/LLM.cpp:687-711).  ``stage_timer``: a ``StageTimer`` for
+    per-stage device times; the steps then run eagerly."""
+    import time
+    t0 = time.perf_counter()
+    first_sample = []
+    if use_graph and stage_timer is None and getattr(model, "graph_safe", True):
+        run_batch_graphed(model, cache, params, states, stop_ids, max_tokens, context, kept_slots, first_sample)
+    else:
+        ops = model.runtime.ops
+        sampler = Sampler(params, [s.index for s in states], model.runtime.device, ops)
+        n = len(states)
 
-    if kept_slots is None:
-        run_batch(lambda entries: model.step(cache, entries), sample, cache.acquire, cache.release,
-                  states, stop_ids, max_tokens, context)
-        return
-    taken = iter([slot for st, slot in zip(states, kept_slots)
-                  if max_tokens > 0 and st.held + len(st.prompt) < context])
-    run_batch(lambda entries: model.step(cache, entries), sample, lambda: next(taken), lambda slot: None,
-              states, stop_ids, max_tokens, context)
-    settle(model, cache, states, kept_slots, context)
+        def step(entries):
+            if stage_timer is not None:
+                stage_timer.begin(is_prompt=not first_sample)
+            return model.step(cache, entries, trace=stage_timer)
+
+        def sample(logits, rows):
+            tokens = sampler.sample(logits, None if len(rows) == n else rows).cpu().tolist()
+            if not first_sample:
+                first_sample.append(time.perf_counter())
+            check_kernels(model)
+            return tokens
+
+        if kept_slots is None:
+            run_batch(step, sample, cache.acquire, cache.release, states, stop_ids, max_tokens, context)
+        else:
+            taken = iter([slot for st, slot in zip(states, kept_slots)
+                          if max_tokens > 0 and st.held + len(st.prompt) < context])
+            run_batch(step, sample, lambda: next(taken), lambda slot: None, states, stop_ids, max_tokens, context)
+            settle(model, cache, states, kept_slots, context)
+    if timing is not None:
+        t1 = first_sample[0] if first_sample else time.perf_counter()
+        timing["prompt_s"], timing["decode_s"] = t1 - t0, time.perf_counter() - t1
 
 
 def generate(model, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams,

@@ -29,6 +29,7 @@ class Options:
     stateless: bool = False         # every prompt() starts from an empty cache
     dtype: str = "bfloat16"         # "float32": the true 32-bit path
     max_batch: int = 64             # most sequences that step together in generate()
+    profile: bool = False           # prompt() keeps per-stage device times (eager steps; see stage_times)
 
 
 class LLM:
@@ -42,7 +43,8 @@ class LLM:
         self._batch_cache = None
         self._slot = None
         self._turns = 0
-        self.last: dict = {}            # figures of the last prompt(): tokens in and out, why it ended
+        self.last: dict = {}            # figures of the last prompt(): tokens in and out, seconds, why it ended
+        self.stage_times = None         # with options.profile: {stage: [prompt seconds, decode seconds]} of the last prompt()
         if model_dir is not None:
             self.use(model_dir)
 
@@ -107,14 +109,21 @@ class LLM:
         # the conversation so far counts toward the context rule; the turn keys the sampling stream
         state = RequestState(self._turns, list(ids), held=held)
         self._turns += 1
+        timing, timer = {}, None
+        if self.options.profile:
+            from .engine.stage_timer import StageTimer
+            timer = StageTimer()
         try:
             run_requests(self.model, self._cache, self._params(None, None, None), [state],
-                         frozenset(self.model.stop_ids), max_tokens, limit, kept_slots=[self._slot])
+                         frozenset(self.model.stop_ids), max_tokens, limit, kept_slots=[self._slot],
+                         timing=timing, stage_timer=timer)
         except Exception:
             self.reset()               # the cache may hold half a turn
             raise
+        self.stage_times = timer.totals() if timer is not None else None
         self.last = {"prompt_tokens": len(ids), "produced": len(state.produced), "reason": state.reason,
-                     "context_used": self._cache.length(self._slot)}
+                     "context_used": self._cache.length(self._slot), "context": limit,
+                     "prompt_s": timing.get("prompt_s", 0.0), "decode_s": timing.get("decode_s", 0.0)}
         return state.produced
 
     def once(self, ids: Sequence[int], max_tokens: Optional[int] = None) -> List[int]:

@@ -138,6 +138,16 @@ def test_command_line(model_dirs, plain_models, tmp_path):
     assert out.returncode == 0, out.stderr
     got = [int(t) for t in out.stdout.strip().splitlines()[-1].split()]
     assert got == plain_gpt2.generate([5, 17, 3], cfg, w, 6)
+    # --profile: the same tokens from eager steps, prompt and generation rates apart, a table of stages
+    prof = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llm"), model_dirs["tiny_a"], "--prompt",
+                           "5,17,3", "--tokens", "6", "--temp", "0", "--fp32", "--stop", "", "--profile"],
+                          capture_output=True, text=True, env=env, timeout=600)
+    assert prof.returncode == 0, prof.stderr
+    lines = prof.stdout.strip().splitlines()
+    tokens_line = next(l for l in lines if l and all(p.isdigit() for p in l.split()))
+    assert [int(t) for t in tokens_line.split()] == got
+    assert any(l.strip().startswith("prompt 3 tok in") and "generated 5 tok in" in l and "context 9/" in l for l in lines), lines
+    assert any("attention" in l for l in lines) and any("output head" in l for l in lines)
     cfg_file = tmp_path / "config.json"
     cfg_file.write_text(json.dumps(cfg))
     out = subprocess.run([sys.executable, "-m", "math_utils_b200", "--random", "--config", str(cfg_file),
@@ -194,6 +204,10 @@ def test_trace_replay_program(dtype, model_dirs, plain_models, tmp_path):
     # a, b, c hold at most 128 + 64 + 128 positions; so do d, e, f
     replay(model_dirs[name], dtype, steps, out_dir, max_tokens=320)
     plain = {rid: plain_gpt2.forward(r, cfg, w) for rid, r in reqs.items()}
+    with open(os.path.join(out_dir, "manifest.json")) as f:
+        manifest = json.load(f)
+    assert [m["name"] for m in manifest] == [f"{s['step']}.f32" for s in steps]
+    assert all(m["shape"] == [len(wanted[s["step"]]), vocab] for m, s in zip(manifest, steps))
     for s in steps:
         got = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(-1, vocab)
         want = np.stack([plain[rid][p] for rid, p in wanted[s["step"]]])

@@ -26,6 +26,21 @@ def test_plain_matches_reference_code(k, name):
     assert np.abs(logits[rows] - stored["local_model_stepwise"]).max() < 2e-5
 
 
+def test_plain_matches_the_oracle_on_the_options_the_decoder_lacks():
+    """n_inner = 320, erf GELU, scale_attn_by_inverse_layer_idx, eps 1e-6 (the second tiny test configuration):
+    the reference's NumPy oracle run in float64 with its activation exchanged for the erf form and the
+    layer-index scaling folded into the query weights (tests/golden/make_golden.py says how)."""
+    cfg = make_golden.GOLDEN_C
+    weights = {n: w.astype(np.float64) for n, w in make_golden.make_weights(cfg, seed=1236).items()}
+    logits = plain_gpt2.forward(make_golden.GOLDEN_C_IDS, cfg, weights)
+    stored = np.load(os.path.join(GOLDEN, "golden_c.npz"))
+    assert np.abs(logits[stored["rows"]] - stored["oracle_rows"]).max() < 1e-9
+    # and each of the three options moves the logits, so the comparison pins them
+    for change in ({"activation_function": "gelu_new"}, {"scale_attn_by_inverse_layer_idx": False}):
+        other = plain_gpt2.forward(make_golden.GOLDEN_C_IDS, dict(cfg, **change), weights)
+        assert np.abs(other[stored["rows"]] - stored["oracle_rows"]).max() > 1e-5, change
+
+
 def test_inverse_layer_scaling_is_identity_for_one_layer():
     cfg = dict(make_golden.GOLDEN_CONFIGS["golden_a"], n_layer=1)
     w = {n: a.astype(np.float64) for n, a in make_golden.make_weights(cfg, seed=5).items()}

@@ -3,7 +3,8 @@ allocate device memory (a plug-in inside someone else's memory pool, a loop
 that must stay out of the allocator): its scratch is a fixed array inside the
 library.  Called here through its exported C symbol, twice in a row with
 different inputs, and compared with the ordinary entry point, which takes its
-scratch from the caller.  This file is collected last on purpose."""
+scratch from the caller, and with the plain attention of tests/plain_gpt2.py.
+This file is collected last on purpose."""
 import ctypes
 import math
 
@@ -49,6 +50,7 @@ def make_case(seed, dtype, lens, n_heads, n_kv_heads, head_dim):
     q = torch.randn((len(lens), n_heads * head_dim), generator=g, device="cuda").to(dtype)
     qpos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device="cuda")
     qseq = torch.arange(len(lens), dtype=torch.int32, device="cuda")
+    make_case.keys_values = (k.double().cpu().numpy(), v.double().cpu().numpy())      # for the plain attention
     return q, kv, table, qpos, qseq
 
 
@@ -58,7 +60,6 @@ def test_static_scratch_matches_caller_scratch_twice(dtype):
     fn = c_entry()
     n_heads, n_kv_heads, head_dim, n_splits, split_keys = 6, 2, 48, 4, 64
     stream = torch.cuda.current_stream().cuda_stream
-    free_before = None
     for call, lens in enumerate(([200, 37, 129], [64, 250, 5])):          # the second call meets the first one's leftovers
         q, kv, table, qpos, qseq = make_case(10 + call, dtype, lens, n_heads, n_kv_heads, head_dim)
         scale = 1.0 / math.sqrt(head_dim)
@@ -68,20 +69,29 @@ def test_static_scratch_matches_caller_scratch_twice(dtype):
                       split_keys, torch.empty(units * head_dim, device="cuda"), torch.empty(units * 2, device="cuda"))
         got = torch.full_like(q, float("nan"))
         torch.cuda.synchronize()
-        if call == 1:
-            free_before = torch.cuda.mem_get_info()[0]
         rc = fn(q.data_ptr(), q.stride(0), got.data_ptr(), got.stride(0), kv.data_ptr(), table.data_ptr(),
                 table.shape[1], 64, qpos.data_ptr(), qseq.data_ptr(), len(lens), n_heads, n_kv_heads, head_dim,
                 scale, 0, n_splits, split_keys, int(dtype == torch.bfloat16), stream)
         torch.cuda.synchronize()
         assert rc == 0
-        if call == 1:
-            assert torch.cuda.mem_get_info()[0] >= free_before          # nothing was taken from the device
         # same kernels, same order of operations: the two entry points agree to the last bit,
         # which is well inside the 1e-5 x rms that the kernel tests allow
         diff = (got.float() - want.float()).abs().max().item()
         rms = want.float().pow(2).mean().sqrt().item()
         assert torch.isfinite(got.float()).all() and diff <= 1e-5 * rms, (call, diff, rms)
+        # and both are the attention the plain implementation computes: each sequence's last query over all
+        # of its keys, with the bounds of the kernel tests
+        import plain_gpt2
+        from test_kernels_gpu import assert_close
+        keys, values = make_case.keys_values
+        start = 0
+        for s, n in enumerate(lens):
+            qs = np.repeat(q[s:s + 1].double().cpu().numpy(), n, axis=0)
+            plain = plain_gpt2.causal_attention(qs, keys[start:start + n], values[start:start + n], n_heads, n_kv_heads,
+                                                scale)[-1]
+            assert_close(got[s].float().cpu().numpy(), plain, "float32" if dtype == torch.float32 else "bfloat16",
+                         f"call {call} sequence {s}")
+            start += n
 
 
 def test_static_scratch_refuses_what_does_not_fit():

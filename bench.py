@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --config medium|xl          # BASELINE.json's fourth and fifth workloads
     python bench.py --only decode|prefill [--layers N] [--batch B]     # a small case for a profiler
+    python bench.py --only marginal [--batch B]    # each kernel class's share of the recorded decode step
 
 A "step" is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (BASELINE.json's third configuration) with seeded random
@@ -449,6 +450,66 @@ def run_part(args):
     return 0
 
 
+def run_marginal(args):
+    """What each class of launches costs INSIDE the recorded, overlapped single-token step: the step is
+    recorded again with that class left out (its outputs are then stale, which no timing cares about), and
+    the difference to the whole step is the class's share.  A profiler serialises the launches and cannot
+    say this.  Prints one JSON line; not a bench record."""
+    import numpy as np
+    import torch
+    from math_utils_b200.csrc import ops
+    from math_utils_b200.sampling import SamplingParams
+    cfg = baseline_config("small")
+    if args.layers:
+        cfg["n_layer"] = args.layers
+    llm = load_random(cfg, temperature=0.0, context=CONTEXT, max_batch=64)
+    model = llm.model
+    rng = np.random.default_rng(0)
+    greedy = SamplingParams(temperature=0.0)
+    real = {k: getattr(ops, k) for k in ("linear", "attention_decode", "argmax")}
+
+    def linear_without(shapes):
+        def linear(x, weight, bias=None, act=None, residual=None, out=None, out_dtype=None):
+            if tuple(weight.shape) in shapes:
+                rows = x.n_rows if isinstance(x, ops.NormedInput) else x.shape[0]
+                return out if out is not None else torch.empty((rows, weight.shape[0]), dtype=out_dtype or weight.dtype,
+                                                               device=weight.device)
+            return real["linear"](x, weight, bias, act=act, residual=residual, out=out, out_dtype=out_dtype)
+        return linear
+
+    d, i, v = cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"]
+    variants = {
+        "whole step": {},
+        "attention": {"attention_decode": lambda q, k_new, v_new, out, *a, **kw: out},
+        "norm + q|k|v": {"linear": linear_without({(3 * d, d)})},
+        "out-proj": {"linear": linear_without({(d, d)})},
+        "norm + FC": {"linear": linear_without({(i, d)})},
+        "proj": {"linear": linear_without({(d, i)})},
+        "head": {"linear": linear_without({(v, d)})},
+        "argmax": {"argmax": lambda logits, out=None, feed=None: out if out is not None else real["argmax"](logits)},
+    }
+    prompts = [rng.integers(0, v, size=PROMPT_LEN).tolist() for _ in range(args.batch)]
+    times = {}
+    try:
+        for name, patch in variants.items():
+            for key, fn in real.items():
+                setattr(ops, key, fn)
+            for key, fn in patch.items():
+                setattr(ops, key, fn)
+            model.__dict__.pop("_decode_sessions", None)
+            r = time_decode(model, prompts, args.steps, max(args.warmup, 4), greedy, check_steps=0)
+            times[name] = r["seconds"] / args.steps * 1e6
+    finally:
+        for key, fn in real.items():
+            setattr(ops, key, fn)
+    whole = times.pop("whole step")
+    print(json.dumps({"part": "marginal", "batch": args.batch, "layers": cfg["n_layer"], "step_us": round(whole, 1),
+                      "marginal_us": {k: round(whole - t, 1) for k, t in times.items()},
+                      "per_layer_us": {k: round((whole - t) / cfg["n_layer"], 2) for k, t in times.items()
+                                       if k not in ("head", "argmax")}}))
+    return 0
+
+
 # ------------------------------------------------------------------------------------------ the reference arm
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")          # --reference-dir names another checkout
 REF_DRIVER = os.path.join(ROOT, "baseline", "reference_arm.cpp")
@@ -545,8 +606,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="small", choices=["small", "medium", "xl"],
                     help="medium / xl: BASELINE.json's fourth / fifth workload through LLM.generate")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                    help="run one part only and print a short line (for profiling a small case)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "marginal"],
+                    help="run one part only and print a short line (decode / prefill: a small case for a profiler; "
+                         "marginal: what each class of launches costs inside the recorded single-token step)")
     ap.add_argument("--layers", type=int, default=0, help="with --only or --config: fewer layers than the model has")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="with --only decode: tokens per prompt")
     ap.add_argument("--reference-dir", default="", help="with --impl reference: a checkout other than baseline/_ref")
@@ -560,6 +622,8 @@ def main():
         return run_reference(args)
     if args.config != "small":
         return run_workload(args)
+    if args.only == "marginal":
+        return run_marginal(args)
     if args.only != "all":
         return run_part(args)
     return run_ours(args)

@@ -79,6 +79,9 @@ class StepContext:
     q_tiles_wide: Optional[torch.Tensor] = None  # the same in tiles of up to 128 queries
     trace: Optional[object] = None          # callable(name, tensor): told every named intermediate result
     tag: str = ""                           # prefix of the names noted now ("h.3." inside layer run 3)
+    # pinned host memory with this step's positions (``ops.HostView``): an embedding that declares
+    # ``fetches_positions`` reads them there and leaves them in ``tok_pos``; others never see it set
+    positions_from: Optional[object] = None
 
     def note(self, name: str, tensor) -> None:
         """Hands an intermediate result to the step's trace, if there is one.  A

@@ -33,12 +33,14 @@ from .batch import StepContext
 class DecodeSession:
     def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
                  request_ids: Sequence[int], kv_bound: Optional[int] = None, pipelined: bool = False):
-        """``pipelined``: two graphs that take turns; each starts with the copy of
-        the step's positions from a pinned buffer of its own and ends with the
-        copy of the sampled tokens to a pinned buffer of its own, so a step is
-        one launch, and the host may fill the buffers of the next step while
-        this one runs.  Without it a launch leaves the inputs alone, and each
-        step's samples feed the next on the device."""
+        """``pipelined``: two graphs that take turns, each with pinned host
+        buffers of its own: the step's first kernel reads the positions from
+        one (an embedding that cannot has them copied in front of it), its last
+        kernel writes the sampled tokens and the kernels' status word to the
+        others.  So a step is one launch of kernels only, and the host may fill
+        the buffers of the next step while this one runs.  Without it a launch
+        leaves the inputs alone, and each step's samples feed the next on the
+        device."""
         self.model, self.cache = model, cache
         self.pipelined = pipelined
         self.slots = list(slots)
@@ -88,6 +90,11 @@ class DecodeSession:
             self._first_tokens = torch.zeros(n, dtype=torch.int32, pin_memory=True)
             # the kernels' status word as each step left it, read with the step's samples
             self._status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            ops = rt.ops
+            ops.status_word(dev)                         # exists before any capture asks for it
+            self._pos_view_dev = [ops.HostView(t) for t in self._pos_host]
+            self._mirrors = [(ops.HostView(self._out_host[t]), ops.HostView(self._status_host[t])) for t in range(2)]
+            self._fetch_in_kernel = bool(getattr(model.assembly.embedding, "fetches_positions", False))
         self.launches_per_step = 0
         self.logits: Optional[torch.Tensor] = None
         self._tables_host = [None] * len(self.tables_shape)
@@ -175,15 +182,30 @@ class DecodeSession:
         return self._out_host[ticket].tolist()
 
     # ------------------------------------------------------------------- steps
-    def _run_once(self) -> None:
+    def _run_once(self, turn: Optional[int] = None) -> None:
+        """One step.  With ``turn`` (a recorded step of the pipelined kind) the
+        positions come from that turn's host buffer and the samples and the
+        status word go to that turn's host buffers as well."""
         ops = self.model.runtime.ops
-        logits = self.logits = self.model.forward(self.ctx, self.cache)
+        mirror = None
+        if turn is not None:
+            if self._fetch_in_kernel:
+                self.ctx.positions_from = self._pos_view_dev[turn]
+            else:
+                # (the library's own copy: a torch copy from pinned memory would leave the host
+                # allocator with an event recorded during a capture)
+                ops.copy_async(self.tok_pos, self._pos_host[turn])
+            mirror = self._mirrors[turn]
+        try:
+            logits = self.logits = self.model.forward(self.ctx, self.cache)
+        finally:
+            self.ctx.positions_from = None
         feed = (self.token_ids, self.tok_pos, self.kv_bound - 1)     # samples become the next step's inputs
         if self.params.greedy:
-            ops.argmax(logits, out=self.next_tokens, feed=feed)
+            ops.argmax(logits, out=self.next_tokens, feed=feed, mirror=mirror)
         else:
             ops.sample(logits, self.params.temperature, self.params.kept, self.params.seed,
-                       self.request_ids, self.draws, out=self.next_tokens, feed=feed)
+                       self.request_ids, self.draws, out=self.next_tokens, feed=feed, mirror=mirror)
 
     def capture(self) -> None:
         """Runs the step once eagerly (first-use set-up must not happen inside a
@@ -202,14 +224,8 @@ class DecodeSession:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         if self.pipelined:
-            def turn_body(turn):
-                # (the library's own copy: a torch copy from or to pinned memory would leave the host
-                # allocator with an event recorded during a capture)
-                ops.copy_async(self.tok_pos, self._pos_host[turn])
-                self._run_once()
-                ops.copy_async(self._out_host[turn], self.next_tokens)
-                ops.copy_async(self._status_host[turn], ops.status_word(self.model.runtime.device))
-            self._turn_graphs = [self._record_graph(lambda turn=turn: turn_body(turn), side) for turn in range(2)]
+            self._turn_graphs = [self._record_graph(lambda turn=turn: self._run_once(turn), side)
+                                 for turn in range(2)]
         else:
             self.graph = self._record_graph(self._run_once, side)
         self.token_ids.copy_(saved[0]); self.tok_pos.copy_(saved[1]); self.draws.copy_(saved[2])

@@ -13,7 +13,7 @@ import plain_gpt2
 from helpers import check_logits, run_batch, run_tail_one_by_one, run_whole
 from math_utils_b200 import DecoderModel, LLM, Options, register_architecture, write_random_model
 from math_utils_b200.config import Architecture, LayerSpec, ModelPlan, PartSpec, default_schedule
-from math_utils_b200.parts import FeedForward, Linear, PositionEncoding, TensorSpec, register_part
+from math_utils_b200.parts import Embedding, FeedForward, Linear, PositionEncoding, TensorSpec, register_part
 
 pytestmark = pytest.mark.gpu
 
@@ -74,6 +74,26 @@ class ToyRoutedFeedForward(FeedForward):
             residual += y * (choice == e)[:, None]
 
 
+class ToyEmbedding(Embedding):
+    """A token table looked up with torch's own indexing.  It does not read positions from host memory
+    (``fetches_positions`` stays False), so recorded steps copy them to the device in front of it."""
+
+    def tensor_specs(self):
+        return (TensorSpec(self.tensor_name("weight"), (int(self.param("vocab_size")), int(self.param("hidden_size"))),
+                           role="table"),)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.weight = tensors[self.tensor_name("weight")]
+
+    def table(self):
+        return self.weight
+
+    def forward(self, ctx, position_table):
+        assert position_table is None and ctx.positions_from is None
+        return self.weight[ctx.token_ids.long()].float()
+
+
 class ToyConfig2:
     def __init__(self, raw):
         self.raw = dict(raw)
@@ -115,7 +135,7 @@ class ToyConfig2:
         layers = (LayerSpec("pre_norm", norm("l0.n1"), attn(0, r["window"]), norm("l0.n2"), routed),
                   LayerSpec("pre_norm", norm("l1.n1"), attn(1, 0), norm("l1.n2"), dense))
         return ModelPlan("ToyModel2", r["vocab"], d, r["positions"],
-                         PartSpec("token_embedding", {"vocab_size": r["vocab"], "hidden_size": d}, {"weight": "emb"}),
+                         PartSpec("toy_embedding", {"vocab_size": r["vocab"], "hidden_size": d}, {"weight": "emb"}),
                          PartSpec("toy_rotary", {"head_dim": dh, "base": r["base"]}),
                          layers, default_schedule(2), norm("final"),
                          PartSpec("tied_head", {"vocab_size": r["vocab"], "hidden_size": d}))
@@ -159,6 +179,7 @@ def toy2_plain(ids, r, w):
 @pytest.fixture(scope="module")
 def toy2(tmp_path_factory):
     register_part("position", "toy_rotary", ToyRotary, replace=True)
+    register_part("embedding", "toy_embedding", ToyEmbedding, replace=True)
     register_part("feed_forward", "toy_routed_ffn", ToyRoutedFeedForward, replace=True)
     register_architecture(Architecture(names=("toy2", "ToyModel2"), config_class=ToyConfig2), replace=True)
     raw = {"model_type": "toy2", "width": 80, "heads": 4, "kv_heads": 2, "head_dim": 16, "inner": 136, "experts": 3,

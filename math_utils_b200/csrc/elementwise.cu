@@ -2,34 +2,29 @@
 //
 // embed:     x[t, :] = table[id[t], :] + (pos_table ? pos_table[pos[t], :] : 0)
 //            -> float32 residual stream (include/ai/LocalModel.hpp:3686-3697).
-//            With pos_src (pinned host memory that the device can read) the positions are taken
-//            from there and left in pos for the kernels that follow: the step's copy of its
-//            inputs without a copy node of its own.
-// layernorm: y = (x - mean) * rsqrt(var + eps) * gamma + beta, biased variance,
-//            two passes over the row, all in float32
-//            (include/ai/LocalModel.hpp:1355-1367); output in the compute dtype.
+//            With advance the positions first move on by advance[t] (pos[t] += advance[t]): a
+//            recorded single-token step moves its own positions, and the host only sends a new
+//            advance when a sequence stops or jumps.
 #include "common.cuh"
 
 namespace mu {
 
 template <typename TW>
-__global__ void embed_kernel(const int* __restrict__ ids, int* pos, const int* pos_src,
+__global__ void embed_kernel(const int* __restrict__ ids, int* pos, const int* __restrict__ advance,
                              const TW* __restrict__ table, const TW* __restrict__ pos_table,
                              float* __restrict__ x, int hidden) {
-    __shared__ int fetched;
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    if (pos_src) {                              // one read of host memory per token, handed on through pos
-        if (threadIdx.x == 0) {
-            fetched = *reinterpret_cast<const volatile int*>(pos_src + t);
-            pos[t] = fetched;
-        }
+    int p = pos ? pos[t] : 0;
+    if (advance) {                              // every thread reads the old position before one writes the new
+        p += advance[t];
         __syncthreads();
+        if (threadIdx.x == 0) pos[t] = p;
     }
     const long long row = ids[t];
     const TW* src = table + row * hidden;
-    const TW* psrc = pos_table ? pos_table + (long long)(pos_src ? fetched : pos[t]) * hidden : nullptr;
+    const TW* psrc = pos_table ? pos_table + (long long)p * hidden : nullptr;
     float* dst = x + (long long)t * hidden;
 #pragma unroll 4
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
@@ -139,18 +134,17 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
 }  // namespace mu
 
 // table_bf16: 1 if the tables hold bfloat16, 0 for float32.
-// pos_src: null, or n_tokens positions in host memory that the device can read (mu_host_address);
-// they are used and also written to pos.
-MU_EXPORT int mu_embed(const int* ids, int* pos, const int* pos_src, const void* table, const void* pos_table,
+// advance: null, or n_tokens steps that the positions take before they are used (and pos keeps the sum).
+MU_EXPORT int mu_embed(const int* ids, int* pos, const int* advance, const void* table, const void* pos_table,
                        float* x, int n_tokens, int hidden, int table_bf16, void* stream) {
     if (n_tokens <= 0) return MU_OK;
-    if (hidden <= 0 || !ids || !table || !x || (pos_table && !pos) || (pos_src && !pos)) return MU_ERR_BAD_ARGUMENT;
+    if (hidden <= 0 || !ids || !table || !x || (pos_table && !pos) || (advance && !pos)) return MU_ERR_BAD_ARGUMENT;
     const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_bf16)
         return mu::launch_pdl(mu::embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
-                              pos_src, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
-    return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos, pos_src,
+                              advance, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
+    return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos, advance,
                           (const float*)table, (const float*)pos_table, x, hidden);
 }
 
@@ -220,13 +214,6 @@ MU_EXPORT int mu_advance(int* token_ids, int* tok_pos, const int* next_tokens, i
 MU_EXPORT int mu_set_pdl(int enabled) {
     mu::pdl_enabled() = enabled ? 1 : 0;
     return MU_OK;
-}
-
-// The address under which kernels reach a piece of pinned host memory (with unified addressing the same
-// number; asked for all the same, so that memory the device cannot reach is refused here and not in a kernel).
-MU_EXPORT int mu_host_address(void* host, void** device) {
-    if (!host || !device) return MU_ERR_BAD_ARGUMENT;
-    return cudaHostGetDevicePointer(device, host, 0) == cudaSuccess ? MU_OK : MU_ERR_BAD_ARGUMENT;
 }
 
 // A plain asynchronous copy on the stream (either direction; host memory should be pinned).  For copies

@@ -50,7 +50,6 @@ _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 _SIGNATURES = {
     "mu_copy_async": [_c_p, _c_p, _c_ll, _c_p],
     "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p],
-    "mu_host_address": [_c_p, ctypes.POINTER(ctypes.c_void_p)],
     "mu_layernorm": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p],
     "mu_gemm_simt": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                      _c_int, _c_int, _c_int, _c_p],
@@ -73,7 +72,7 @@ _SIGNATURES = {
                                 _c_p, _c_int, _c_p, _c_p],
     "mu_layernorm_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                              _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_p],
-    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p],
+    "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
     "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
@@ -81,7 +80,7 @@ _SIGNATURES = {
     "mu_attention_decode_tc": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
                                _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
-                  _c_p, _c_p, _c_p, _c_p],
+                  _c_p, _c_p, _c_p],
 }
 
 
@@ -169,32 +168,18 @@ def set_pdl(enabled: bool) -> None:
     library().mu_set_pdl(1 if enabled else 0)
 
 
-def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:
+def copy_async(dst: torch.Tensor, src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
     """dst <- src (same size and dtype, contiguous; host tensors pinned) as a
-    plain asynchronous copy on the current stream.  For copies recorded into a
-    CUDA graph: the caller keeps both tensors alive as long as the graph."""
+    plain asynchronous copy on the current stream, or on ``stream``.  The
+    caller keeps both tensors alive until the copy is over (a copy recorded in
+    a CUDA graph: as long as the graph)."""
     if dst.dtype != src.dtype or dst.numel() != src.numel() or not dst.is_contiguous() or not src.is_contiguous():
         raise KernelError("copy_async needs contiguous tensors of one dtype and size")
     for t in (dst, src):
         if not t.is_cuda and not t.is_pinned():
             raise KernelError("copy_async needs pinned host memory")
-    _check(library().mu_copy_async(dst.data_ptr(), src.data_ptr(), dst.numel() * dst.element_size(), _stream()),
-           "copy_async", launches=0)
-
-
-class HostView:
-    """A pinned host tensor of int32 together with the address under which
-    kernels read or write it.  The tensor is kept alive with the view: a CUDA
-    graph that holds the address needs the memory for as long as it replays."""
-
-    def __init__(self, tensor: torch.Tensor):
-        if tensor.is_cuda or not tensor.is_pinned() or tensor.dtype != torch.int32 or not tensor.is_contiguous():
-            raise KernelError("a host view needs a contiguous pinned int32 tensor")
-        address = ctypes.c_void_p()
-        code = library().mu_host_address(tensor.data_ptr(), ctypes.byref(address))
-        if code != 0 or not address.value:
-            raise KernelError("this pinned host memory cannot be reached from the device")
-        self.tensor, self.address, self.numel = tensor, address.value, tensor.numel()
+    _check(library().mu_copy_async(dst.data_ptr(), src.data_ptr(), dst.numel() * dst.element_size(),
+                                   _stream() if stream is None else stream.cuda_stream), "copy_async", launches=0)
 
 
 _workspaces = {}
@@ -219,13 +204,14 @@ def zeroed_workspace(name: str, device, n_bytes: int) -> torch.Tensor:
 # ------------------------------------------------------------------ elementwise
 def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Tensor,
           pos_table: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-          positions_from: Optional[HostView] = None) -> torch.Tensor:
+          advance: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = table[ids[t]] + pos_table[positions[t]] as float32 [T, hidden].
-    With ``positions_from`` the kernel takes the positions from that pinned
-    host memory and leaves them in ``positions`` for the kernels after it."""
-    _need_cuda(ids, positions, table, pos_table)
-    if positions_from is not None and (positions is None or positions_from.numel != ids.numel()):
-        raise KernelError("positions_from needs a device tensor to leave the positions in, and one position a token")
+    With ``advance`` (int32 per token) the positions first move on by that
+    much, in place: ``positions`` then holds what the step ran at."""
+    _need_cuda(ids, positions, table, pos_table, advance)
+    _i32(advance, "advance")
+    if advance is not None and (positions is None or advance.numel() != ids.numel()):
+        raise KernelError("advance needs the positions it moves, and one step a token")
     _i32(ids, "ids"); _i32(positions, "positions")
     n, hidden = ids.numel(), table.shape[1]
     if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != hidden):
@@ -234,7 +220,7 @@ def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Ten
         raise KernelError("embedding tables must be contiguous")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
-    _check(library().mu_embed(_ptr(ids), _ptr(positions), positions_from.address if positions_from else None,
+    _check(library().mu_embed(_ptr(ids), _ptr(positions), _ptr(advance),
                               _ptr(table), _ptr(pos_table), _ptr(out), n, hidden, _is_bf16(table), _stream()),
            "embed")
     return out
@@ -461,23 +447,22 @@ def attention(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor, block_
 
 
 # -------------------------------------------------------------------- sampling
-def _mirror_args(mirror, n: int, device):
-    """``mirror`` = (tokens, status): host views that the sampling kernel writes
-    the tokens and the kernels' status word to."""
-    if mirror is None:
-        return None, None, None
-    tokens, status = mirror
-    if tokens.numel != n or status.numel != 1:
-        raise KernelError("the host mirror needs one word a row and one for the status")
-    return tokens.address, _ptr(status_word(device)), status.address
+def _status_args(status_to: Optional[torch.Tensor], device):
+    if status_to is None:
+        return None, None
+    _i32(status_to, "status_to")
+    if not status_to.is_cuda or status_to.numel() != 1:
+        raise KernelError("status_to must be one int32 word on the device")
+    return _ptr(status_word(device)), _ptr(status_to)
 
 
-def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed=None, mirror=None) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed=None,
+           status_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """First maximum of each row.  ``feed`` = (token_ids, tok_pos, last_pos): the
     tokens also become the next single-token step's inputs and the positions
-    move on by one (what ``advance`` does, without its launch).  ``mirror`` =
-    (tokens, status) as ``HostView``: the kernel writes the tokens and the
-    kernels' status word to that host memory as well."""
+    (if not None) move on by one (what ``advance`` does, without its launch).
+    ``status_to``: a device word that receives the kernels' status word, so
+    that one copy brings tokens and status to the host."""
     _need_cuda(logits, out)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("logits must be float32 [rows, vocab] with unit inner stride")
@@ -487,16 +472,16 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, feed=None, 
     ws = zeroed_workspace("argmax", logits.device, 2 * n * 8)
     ids, pos, last = feed if feed is not None else (None, None, 0)
     _check(library().mu_argmax(_ptr(logits), logits.stride(0), n, vocab, _ptr(out), _ptr(ws), _ptr(ids), _ptr(pos),
-                               int(last), *_mirror_args(mirror, n, logits.device), _stream()), "argmax")
+                               int(last), *_status_args(status_to, logits.device), _stream()), "argmax")
     return out
 
 
 def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
            request_ids: Optional[torch.Tensor], draw_index: torch.Tensor,
-           out: Optional[torch.Tensor] = None, feed=None, mirror=None) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, feed=None, status_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row by temperature / top-k; ``draw_index`` (int32 per row)
     counts the draws of each request and is advanced by one.  ``feed`` and
-    ``mirror`` as for ``argmax``."""
+    ``status_to`` as for ``argmax``."""
     _need_cuda(logits, request_ids, draw_index, out)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("logits must be float32 [rows, vocab] with unit inner stride")
@@ -509,7 +494,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
     _check(library().mu_sample(_ptr(logits), logits.stride(0), n, vocab, float(temperature), int(top_k),
                                int(seed) & ((1 << 64) - 1), _ptr(request_ids), _ptr(draw_index), _ptr(out),
                                _ptr(feed[0]) if feed else None, _ptr(feed[1]) if feed else None,
-                               int(feed[2]) if feed else 0, *_mirror_args(mirror, n, logits.device), _stream()),
+                               int(feed[2]) if feed else 0, *_status_args(status_to, logits.device), _stream()),
            "sample")
     return out
 

@@ -47,18 +47,14 @@ __device__ __forceinline__ double uniform_draw(unsigned long long seed, unsigned
 // The vocabulary of a row is cut over ARGMAX_PARTS blocks.  Each folds (key, ~index) pairs into one
 // 64-bit maximum in global memory; the block that takes the row's last ticket writes the token and
 // puts the workspace back to zero for the next launch.
-// Where the host wants the tokens as well: pinned host memory that the device writes to directly, so that
-// a step recorded in a graph ends with its last kernel and not with copy nodes after it.  Row 0's writer
-// also hands over the kernels' status word, which every kernel before this one has finished with.
-struct HostMirror {
-    int* tokens;                // null: no host copy
-    const int* status;          // the device's status word, or null
+// The kernels' status word handed on with the tokens: row 0's writer copies it to status_out (the word behind
+// the tokens of a recorded step, which one copy then brings to the host).  Every kernel before this one has
+// finished with the word by then.
+struct StatusCopy {
+    const int* status;          // null: nothing to copy
     int* status_out;
-    __device__ __forceinline__ void write(int r, int token) const {
-        if (!tokens) return;
-        *reinterpret_cast<volatile int*>(tokens + r) = token;
-        if (r == 0 && status) *reinterpret_cast<volatile int*>(status_out) = *reinterpret_cast<const volatile int*>(status);
-        __threadfence_system();
+    __device__ __forceinline__ void write(int r) const {
+        if (status && r == 0) *status_out = *reinterpret_cast<const volatile int*>(status);
     }
 };
 
@@ -68,7 +64,7 @@ constexpr int ARGMAX_PARTS = 16;
 __global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out,
               unsigned long long* __restrict__ best_ws, unsigned int* __restrict__ ticket_ws,
-              int* __restrict__ feed_ids, int* __restrict__ feed_pos, int last_pos, HostMirror mirror) {
+              int* __restrict__ feed_ids, int* __restrict__ feed_pos, int last_pos, StatusCopy status_copy) {
     __shared__ unsigned long long best_smem[ARGMAX_THREADS / 32];
     pdl_trigger();
     pdl_wait();
@@ -114,12 +110,12 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __
             ticket_ws[r] = 0;
             const int token = (int)(0xFFFFFFFFu - (unsigned int)(all & 0xFFFFFFFFull));
             out[r] = token;
-            if (feed_ids) {                     // hand the token to the next single-token step
-                feed_ids[r] = token;
+            if (feed_ids) feed_ids[r] = token;  // hand the token to the next single-token step
+            if (feed_pos) {
                 const int p = feed_pos[r] + 1;
                 feed_pos[r] = p < last_pos ? p : last_pos;
             }
-            mirror.write(r, token);
+            status_copy.write(r);
         }
     }
 }
@@ -173,7 +169,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature, int top_k,
               unsigned long long seed, const long long* __restrict__ request_ids,
               int* __restrict__ draw_index, int* __restrict__ out, int* __restrict__ feed_ids,
-              int* __restrict__ feed_pos, int last_pos, HostMirror mirror) {
+              int* __restrict__ feed_pos, int last_pos, StatusCopy status_copy) {
     __shared__ unsigned long long hist[256];
     __shared__ unsigned long long sel[2];
     __shared__ float red[32];
@@ -324,34 +320,33 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         const int token = found_idx < vocab ? found_idx : 0;
         out[r] = token;
         draw_index[r] += 1;
-        if (feed_ids) {
-            feed_ids[r] = token;
+        if (feed_ids) feed_ids[r] = token;
+        if (feed_pos) {
             const int p = feed_pos[r] + 1;
             feed_pos[r] = p < last_pos ? p : last_pos;
         }
-        mirror.write(r, token);
+        status_copy.write(r);
     }
 }
 
 }  // namespace mu
 
 // logits [n_rows, ld] float32 -> out[n_rows] token ids.  workspace: 2 * n_rows 64-bit words that are
-// zero before the first launch (each launch leaves them zero).  With feed_ids / feed_pos (both or
-// neither) the tokens are also written to feed_ids and feed_pos moves on by one, up to last_pos:
-// what mu_advance does, without its launch.  With host_tokens (an address from mu_host_address) the tokens
-// are written there too, and the word at status to host_status (both or neither).
+// zero before the first launch (each launch leaves them zero).  With feed_ids the tokens are also written
+// there, and with feed_pos those positions move on by one, up to last_pos: what mu_advance does, without
+// its launch.  With status (and status_out) the word there is copied to status_out.
 MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out,
                         unsigned long long* workspace, int* feed_ids, int* feed_pos, int last_pos,
-                        int* host_tokens, const int* status, int* host_status, void* stream) {
+                        const int* status, int* status_out, void* stream) {
     if (n_rows <= 0) return MU_OK;
     if (!logits || !out || !workspace || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
-    if ((feed_ids == nullptr) != (feed_pos == nullptr)) return MU_ERR_BAD_ARGUMENT;
-    if ((status == nullptr) != (host_status == nullptr) || (status && !host_tokens)) return MU_ERR_BAD_ARGUMENT;
-    const mu::HostMirror mirror{host_tokens, status, host_status};
+    if (feed_pos && !feed_ids) return MU_ERR_BAD_ARGUMENT;
+    if ((status == nullptr) != (status_out == nullptr)) return MU_ERR_BAD_ARGUMENT;
+    const mu::StatusCopy status_copy{status, status_out};
     dim3 grid(n_rows, mu::ARGMAX_PARTS);
     return mu::launch_pdl(mu::argmax_kernel, grid, dim3(mu::ARGMAX_THREADS), 0, (cudaStream_t)stream, 1, logits, ld,
                           vocab, out, workspace, reinterpret_cast<unsigned int*>(workspace + n_rows), feed_ids,
-                          feed_pos, last_pos, mirror);
+                          feed_pos, last_pos, status_copy);
 }
 
 // request_ids [n_rows] int64 (null: the row index), draw_index [n_rows] int32 is read and
@@ -359,13 +354,13 @@ MU_EXPORT int mu_argmax(const float* logits, long long ld, int n_rows, int vocab
 MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature,
                         int top_k, unsigned long long seed, const long long* request_ids,
                         int* draw_index, int* out, int* feed_ids, int* feed_pos, int last_pos,
-                        int* host_tokens, const int* status, int* host_status, void* stream) {
+                        const int* status, int* status_out, void* stream) {
     if (n_rows <= 0) return MU_OK;
     if (!logits || !out || !draw_index || vocab <= 0 || ld < vocab) return MU_ERR_BAD_ARGUMENT;
     if (!(temperature > 0.0f) || top_k < 0) return MU_ERR_BAD_ARGUMENT;
-    if ((status == nullptr) != (host_status == nullptr) || (status && !host_tokens)) return MU_ERR_BAD_ARGUMENT;
-    const mu::HostMirror mirror{host_tokens, status, host_status};
+    if ((status == nullptr) != (status_out == nullptr)) return MU_ERR_BAD_ARGUMENT;
+    const mu::StatusCopy status_copy{status, status_out};
     return mu::launch_pdl(mu::sample_kernel, dim3(n_rows), dim3(mu::SAMPLE_THREADS), 0, (cudaStream_t)stream, 1,
                           logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out, feed_ids,
-                          feed_pos, last_pos, mirror);
+                          feed_pos, last_pos, status_copy);
 }

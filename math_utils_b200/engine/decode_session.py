@@ -14,10 +14,15 @@ Three ways to drive it:
     the device (``advance``), with no host round trip between steps;
   * ``pipelined``: ``start(tokens)`` once, then ``launch_step(positions)`` and
     ``read_step(ticket)``: the samples feed the next step on the device, the
-    host supplies every step's positions (it alone knows which sequences have
-    ended and stay where they are) and reads every step's samples, one step
-    behind: while it looks at step s, step s + 1 already runs (the generation
-    loop, which has to see stop tokens but should not hold the device up).
+    host says at which positions every step runs (it alone knows which
+    sequences have ended and stay where they are) and reads every step's
+    samples, one step behind: while it looks at step s, step s + 1 already
+    runs (the generation loop, which has to see stop tokens but should not
+    hold the device up).  Neither transfer is in the step's way: the host
+    sends how far each position moves (1, or 0 for a sequence that stays) on a
+    stream of its own while the step before still runs, the step's first
+    kernel adds that to the positions, and the samples are copied to the host
+    on another stream while the next step runs.
 """
 from __future__ import annotations
 
@@ -33,14 +38,11 @@ from .batch import StepContext
 class DecodeSession:
     def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
                  request_ids: Sequence[int], kv_bound: Optional[int] = None, pipelined: bool = False):
-        """``pipelined``: two graphs that take turns, each with pinned host
-        buffers of its own: the step's first kernel reads the positions from
-        one (an embedding that cannot has them copied in front of it), its last
-        kernel writes the sampled tokens and the kernels' status word to the
-        others.  So a step is one launch of kernels only, and the host may fill
-        the buffers of the next step while this one runs.  Without it a launch
-        leaves the inputs alone, and each step's samples feed the next on the
-        device."""
+        """``pipelined``: two graphs that take turns, each with a device buffer
+        and a pinned host buffer of its own for the samples and the kernels'
+        status word; a copy stream brings them to the host after the step while
+        the next step runs.  Without it a launch leaves the inputs alone, and
+        each step's samples feed the next on the device."""
         self.model, self.cache = model, cache
         self.pipelined = pipelined
         self.slots = list(slots)
@@ -82,19 +84,25 @@ class DecodeSession:
         if pipelined:
             self._turn_graphs = None
             self._turn = 0
-            self._pos_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-            self._pos_views = [t.numpy() for t in self._pos_host]
-            self._out_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            # samples of a turn, and behind them the kernels' status word as that step left it
+            self._out_dev = [torch.zeros(n + 1, dtype=torch.int32, device=dev) for _ in range(2)]
+            self._out_host = [torch.zeros(n + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._out_stream = torch.cuda.Stream(device=dev)
+            self._stepped = [torch.cuda.Event() for _ in range(2)]
             self._done = [torch.cuda.Event() for _ in range(2)]
             self._unread = [False, False]
             self._first_tokens = torch.zeros(n, dtype=torch.int32, pin_memory=True)
-            # the kernels' status word as each step left it, read with the step's samples
-            self._status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-            ops = rt.ops
-            ops.status_word(dev)                         # exists before any capture asks for it
-            self._pos_view_dev = [ops.HostView(t) for t in self._pos_host]
-            self._mirrors = [(ops.HostView(self._out_host[t]), ops.HostView(self._status_host[t])) for t in range(2)]
-            self._fetch_in_kernel = bool(getattr(model.assembly.embedding, "fetches_positions", False))
+            # how far each position moves at the start of a turn's step, sent ahead on a stream of its own
+            self._advance_dev = [torch.zeros(n, dtype=torch.int32, device=dev) for _ in range(2)]
+            self._advance_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._in_stream = torch.cuda.Stream(device=dev)
+            self._sent = [torch.cuda.Event() for _ in range(2)]
+            # (staging buffers in turn: a copy may still be queued behind the two steps that can be unread)
+            self._sends = 0
+            self._positions_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+            self._positions_dev: Optional[np.ndarray] = None      # tok_pos as the last launched step leaves it
+            self._in_kernel = bool(getattr(model.assembly.embedding, "advances_positions", False))
+            rt.ops.status_word(dev)                               # exists before any capture asks for it
         self.launches_per_step = 0
         self.logits: Optional[torch.Tensor] = None
         self._tables_host = [None] * len(self.tables_shape)
@@ -147,13 +155,21 @@ class DecodeSession:
     def start(self, tokens: Sequence[int], positions: Sequence[int]) -> None:
         """The tokens the first step of these sequences takes (later steps take
         the samples of the step before, on the device) and its positions."""
-        torch.cuda.current_stream().synchronize()          # no copy from the staging buffer is still under way
+        torch.cuda.current_stream().synchronize()          # no copy from the staging buffers is still under way
         self._unread = [False, False]
         self._first_tokens.numpy()[:] = tokens
         self.token_ids.copy_(self._first_tokens, non_blocking=True)
-        self._pos_views[self._turn][:] = positions
-        self.tok_pos.copy_(self._pos_host[self._turn], non_blocking=True)
+        self._send_positions(np.array(positions, dtype=np.int32))
         self._fed = True
+
+    def _send_positions(self, positions: np.ndarray) -> None:
+        """The positions themselves, on the launching stream (the first step of a batch; every step of a
+        model whose embedding does not move them on itself)."""
+        host = self._positions_host[self._sends % len(self._positions_host)]
+        self._sends += 1
+        host.numpy()[:] = positions
+        self.model.runtime.ops.copy_async(self.tok_pos, host)
+        self._positions_dev = positions
 
     def launch_step(self, positions: Sequence[int]) -> int:
         """Launches a step at these positions; returns the ticket to read its
@@ -161,51 +177,62 @@ class DecodeSession:
         turn = self._turn
         if self._unread[turn]:
             raise RuntimeError("two steps are launched and unread: read the older one first (its buffers come next)")
-        self._unread[turn] = True
-        self._pos_views[turn][:] = positions
         if self._turn_graphs is None:
             self.capture()
+        ops = self.model.runtime.ops
+        positions = np.array(positions, dtype=np.int32)
+        if self._in_kernel:
+            # the step's first kernel adds this to the positions the step before left (this turn's buffers
+            # are free: the step that last used them has been read)
+            self._advance_host[turn].numpy()[:] = positions - self._positions_dev
+            ops.copy_async(self._advance_dev[turn], self._advance_host[turn], stream=self._in_stream)
+            self._sent[turn].record(self._in_stream)
+            torch.cuda.current_stream().wait_event(self._sent[turn])
+            self._positions_dev = positions
+        else:
+            self._send_positions(positions)
+        self._unread[turn] = True
         self._turn_graphs[turn].replay()
-        self._done[turn].record()
-        self.model.runtime.ops.launch_count += self.launches_per_step
+        self._stepped[turn].record()
+        self._out_stream.wait_event(self._stepped[turn])
+        ops.copy_async(self._out_host[turn], self._out_dev[turn], stream=self._out_stream)
+        self._done[turn].record(self._out_stream)
+        ops.launch_count += self.launches_per_step
         self._turn = turn ^ 1
         return turn
 
     def read_step(self, ticket: int) -> List[int]:
         """The samples of the step launched with this ticket (waits for that
-        step only)."""
+        step and the copy of its samples only)."""
         self._done[ticket].synchronize()
         self._unread[ticket] = False
-        code = int(self._status_host[ticket][0])
-        if code != 0:
-            self.model.runtime.ops.raise_status(self.model.runtime.device, code)
-        return self._out_host[ticket].tolist()
+        out = self._out_host[ticket].tolist()
+        if out[-1] != 0:
+            self.model.runtime.ops.raise_status(self.model.runtime.device, out[-1])
+        return out[:-1]
 
     # ------------------------------------------------------------------- steps
     def _run_once(self, turn: Optional[int] = None) -> None:
         """One step.  With ``turn`` (a recorded step of the pipelined kind) the
-        positions come from that turn's host buffer and the samples and the
-        status word go to that turn's host buffers as well."""
+        positions first move on by ``advance`` (the sampling kernel leaves them
+        alone), and the samples and the status word go to that turn's buffer."""
         ops = self.model.runtime.ops
-        mirror = None
+        out, status_to, moves = self.next_tokens, None, self.tok_pos
         if turn is not None:
-            if self._fetch_in_kernel:
-                self.ctx.positions_from = self._pos_view_dev[turn]
-            else:
-                # (the library's own copy: a torch copy from pinned memory would leave the host
-                # allocator with an event recorded during a capture)
-                ops.copy_async(self.tok_pos, self._pos_host[turn])
-            mirror = self._mirrors[turn]
+            out, status_to = self._out_dev[turn][:self.n], self._out_dev[turn][self.n:]
+            moves = None
+            if self._in_kernel:
+                self.ctx.advance = self._advance_dev[turn]
         try:
             logits = self.logits = self.model.forward(self.ctx, self.cache)
         finally:
-            self.ctx.positions_from = None
-        feed = (self.token_ids, self.tok_pos, self.kv_bound - 1)     # samples become the next step's inputs
+            self.ctx.advance = None
+        feed = (self.token_ids, moves, self.kv_bound - 1)            # samples become the next step's inputs
         if self.params.greedy:
-            ops.argmax(logits, out=self.next_tokens, feed=feed, mirror=mirror)
+            ops.argmax(logits, out=out, feed=feed, status_to=status_to)
         else:
             ops.sample(logits, self.params.temperature, self.params.kept, self.params.seed,
-                       self.request_ids, self.draws, out=self.next_tokens, feed=feed, mirror=mirror)
+                       self.request_ids, self.draws, out=out, feed=feed, status_to=status_to)
 
     def capture(self) -> None:
         """Runs the step once eagerly (first-use set-up must not happen inside a

@@ -180,13 +180,13 @@ class PositionEncoding(Part):
 class Embedding(Part):
     """``forward(ctx, position_table)`` -> ``[T, hidden]`` float32 residual.
 
-    ``fetches_positions``: whether ``forward`` honours ``ctx.positions_from``
-    (when set: pinned host memory with the step's positions, which the first
-    kernel reads and leaves in ``ctx.tok_pos``).  The decode session sets it
-    only for an embedding that says so; for any other it copies the positions
-    to the device itself before the step."""
+    ``advances_positions``: whether ``forward`` honours ``ctx.advance`` (when
+    set: before anything uses ``ctx.tok_pos``, it moves on by ``ctx.advance``,
+    in place, in the step's first kernel).  A recorded single-token step sets
+    it only for an embedding that says so; for any other the host sends every
+    step's positions to the device before the step."""
 
-    fetches_positions = False
+    advances_positions = False
 
     def forward(self, ctx, position_table):
         raise NotImplementedError

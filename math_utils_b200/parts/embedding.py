@@ -23,11 +23,10 @@ class TokenEmbedding(Embedding):
     def table(self):
         return self.weight
 
-    fetches_positions = True
+    advances_positions = True
 
     def forward(self, ctx, position_table):
-        return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table,
-                                      positions_from=ctx.positions_from)
+        return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table, advance=ctx.advance)
 
 
 class TiedHead(Head):

@@ -51,16 +51,15 @@ def test_embed(dtype):
     assert np.abs(got - want).max() < 1e-6
     got = ops.embed(ids, None, table, None).cpu().numpy()
     assert np.array_equal(got, table.float().cpu().numpy()[ids.cpu()])
-    # positions read from pinned host memory by the kernel itself, and left on the device
-    host = torch.tensor([7, 1, 18, 0, 2], dtype=torch.int32).pin_memory()
-    left = torch.full((5,), -1, dtype=torch.int32, device="cuda")
-    got = ops.embed(ids, left, table, pos, positions_from=ops.HostView(host)).cpu().numpy()
-    want = table.double().cpu().numpy()[ids.cpu()] + pos.double().cpu().numpy()[host]
-    assert np.abs(got - want).max() < 1e-6 and left.cpu().tolist() == host.tolist()
+    # positions that the kernel moves on itself before it uses them
+    moves = torch.tensor([1, 0, -2, 3, 0], dtype=torch.int32, device="cuda")
+    moved = p.clone()
+    got = ops.embed(ids, moved, table, pos, advance=moves).cpu().numpy()
+    at = (p + moves).cpu()
+    want = table.double().cpu().numpy()[ids.cpu()] + pos.double().cpu().numpy()[at]
+    assert np.abs(got - want).max() < 1e-6 and moved.cpu().tolist() == at.tolist()
     with pytest.raises(ops.KernelError):
-        ops.HostView(torch.zeros(5, dtype=torch.int32))                      # not pinned
-    with pytest.raises(ops.KernelError):
-        ops.embed(ids, left, table, pos, positions_from=ops.HostView(torch.zeros(4, dtype=torch.int32).pin_memory()))
+        ops.embed(ids, moved, table, pos, advance=moves[:4].contiguous())
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
@@ -235,12 +234,11 @@ def test_argmax_first_maximum_wins():
     x[3, 50256] = 11.0
     got = ops.argmax(dev(x)).cpu().tolist()
     assert got == [plain_gpt2.argmax(r) for r in x] and got[1] == 777 and got[2] == 0 and got[3] == 50256
-    # the same tokens written to pinned host memory by the kernel, with the kernels' status word
-    tokens = torch.full((6,), -1, dtype=torch.int32).pin_memory()
-    status = torch.full((1,), -1, dtype=torch.int32).pin_memory()
-    ops.argmax(dev(x), mirror=(ops.HostView(tokens), ops.HostView(status)))
-    torch.cuda.synchronize()
-    assert tokens.tolist() == got and status.tolist() == [0]
+    # the kernels' status word handed on behind the tokens; fed tokens without fed positions
+    out = torch.full((7,), -1, dtype=torch.int32, device="cuda")
+    fed = torch.full((6,), -1, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(x), out=out[:6], feed=(fed, None, 0), status_to=out[6:])
+    assert out.cpu().tolist() == got + [0] and fed.cpu().tolist() == got
 
 
 @pytest.mark.parametrize("vocab,top_k,temperature", [(1031, 0, 0.8), (1031, 20, 0.7), (50257, 40, 1.0),
@@ -263,14 +261,13 @@ def test_sample_follows_the_plain_rule(vocab, top_k, temperature):
             # a disagreement is allowed only where u falls within rounding of a boundary
             assert got[r] == want or margin < 1e-5, (r, n, got[r], want, margin)
     assert draws.cpu().tolist() == [3] * rows
-    tokens = torch.full((rows,), -1, dtype=torch.int32).pin_memory()
-    status = torch.full((1,), -1, dtype=torch.int32).pin_memory()
+    out = torch.full((rows + 1,), -1, dtype=torch.int32, device="cuda")
+    fed = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
     draws.zero_()
     first = ops.sample(logits, temperature, top_k, 42, req, draws).cpu().tolist()
     draws.zero_()
-    ops.sample(logits, temperature, top_k, 42, req, draws, mirror=(ops.HostView(tokens), ops.HostView(status)))
-    torch.cuda.synchronize()
-    assert tokens.tolist() == first and status.tolist() == [0]
+    ops.sample(logits, temperature, top_k, 42, req, draws, out=out[:rows], feed=(fed, None, 0), status_to=out[rows:])
+    assert out.cpu().tolist() == first + [0] and fed.cpu().tolist() == first
 
 
 def test_sample_distribution():

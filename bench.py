@@ -486,7 +486,7 @@ def run_marginal(args):
         "norm + FC": {"linear": linear_without({(i, d)})},
         "proj": {"linear": linear_without({(d, i)})},
         "head": {"linear": linear_without({(v, d)})},
-        "argmax": {"argmax": lambda logits, out=None, feed=None: out if out is not None else real["argmax"](logits)},
+        "argmax": {"argmax": lambda logits, out=None, **kw: out if out is not None else real["argmax"](logits)},
     }
     prompts = [rng.integers(0, v, size=PROMPT_LEN).tolist() for _ in range(args.batch)]
     times = {}

@@ -2,29 +2,23 @@
 //
 // embed:     x[t, :] = table[id[t], :] + (pos_table ? pos_table[pos[t], :] : 0)
 //            -> float32 residual stream (include/ai/LocalModel.hpp:3686-3697).
-//            With advance the positions first move on by advance[t] (pos[t] += advance[t]): a
-//            recorded single-token step moves its own positions, and the host only sends a new
-//            advance when a sequence stops or jumps.
+// layernorm: y = (x - mean) * rsqrt(var + eps) * gamma + beta, biased variance,
+//            two passes over the row, all in float32
+//            (include/ai/LocalModel.hpp:1355-1367); output in the compute dtype.
 #include "common.cuh"
 
 namespace mu {
 
 template <typename TW>
-__global__ void embed_kernel(const int* __restrict__ ids, int* pos, const int* __restrict__ advance,
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ table, const TW* __restrict__ pos_table,
                              float* __restrict__ x, int hidden) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    int p = pos ? pos[t] : 0;
-    if (advance) {                              // every thread reads the old position before one writes the new
-        p += advance[t];
-        __syncthreads();
-        if (threadIdx.x == 0) pos[t] = p;
-    }
     const long long row = ids[t];
     const TW* src = table + row * hidden;
-    const TW* psrc = pos_table ? pos_table + (long long)p * hidden : nullptr;
+    const TW* psrc = pos_table ? pos_table + (long long)pos[t] * hidden : nullptr;
     float* dst = x + (long long)t * hidden;
 #pragma unroll 4
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
@@ -134,17 +128,16 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
 }  // namespace mu
 
 // table_bf16: 1 if the tables hold bfloat16, 0 for float32.
-// advance: null, or n_tokens steps that the positions take before they are used (and pos keeps the sum).
-MU_EXPORT int mu_embed(const int* ids, int* pos, const int* advance, const void* table, const void* pos_table,
+MU_EXPORT int mu_embed(const int* ids, const int* pos, const void* table, const void* pos_table,
                        float* x, int n_tokens, int hidden, int table_bf16, void* stream) {
     if (n_tokens <= 0) return MU_OK;
-    if (hidden <= 0 || !ids || !table || !x || (pos_table && !pos) || (advance && !pos)) return MU_ERR_BAD_ARGUMENT;
+    if (hidden <= 0 || !ids || !table || !x || (pos_table && !pos)) return MU_ERR_BAD_ARGUMENT;
     const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_bf16)
         return mu::launch_pdl(mu::embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
-                              advance, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
-    return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos, advance,
+                              (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, hidden);
+    return mu::launch_pdl(mu::embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 1, ids, pos,
                           (const float*)table, (const float*)pos_table, x, hidden);
 }
 

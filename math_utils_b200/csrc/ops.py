@@ -49,7 +49,7 @@ _c_int, _c_ll, _c_f, _c_p, _c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 
 _SIGNATURES = {
     "mu_copy_async": [_c_p, _c_p, _c_ll, _c_p],
-    "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p],
+    "mu_embed": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p],
     "mu_layernorm": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p],
     "mu_gemm_simt": [_c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll,
                      _c_int, _c_int, _c_int, _c_p],
@@ -203,15 +203,9 @@ def zeroed_workspace(name: str, device, n_bytes: int) -> torch.Tensor:
 
 # ------------------------------------------------------------------ elementwise
 def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Tensor,
-          pos_table: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-          advance: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] + pos_table[positions[t]] as float32 [T, hidden].
-    With ``advance`` (int32 per token) the positions first move on by that
-    much, in place: ``positions`` then holds what the step ran at."""
-    _need_cuda(ids, positions, table, pos_table, advance)
-    _i32(advance, "advance")
-    if advance is not None and (positions is None or advance.numel() != ids.numel()):
-        raise KernelError("advance needs the positions it moves, and one step a token")
+          pos_table: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] + pos_table[positions[t]] as float32 [T, hidden]."""
+    _need_cuda(ids, positions, table, pos_table)
     _i32(ids, "ids"); _i32(positions, "positions")
     n, hidden = ids.numel(), table.shape[1]
     if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != hidden):
@@ -220,7 +214,7 @@ def embed(ids: torch.Tensor, positions: Optional[torch.Tensor], table: torch.Ten
         raise KernelError("embedding tables must be contiguous")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
-    _check(library().mu_embed(_ptr(ids), _ptr(positions), _ptr(advance),
+    _check(library().mu_embed(_ptr(ids), _ptr(positions),
                               _ptr(table), _ptr(pos_table), _ptr(out), n, hidden, _is_bf16(table), _stream()),
            "embed")
     return out

@@ -79,9 +79,6 @@ class StepContext:
     q_tiles_wide: Optional[torch.Tensor] = None  # the same in tiles of up to 128 queries
     trace: Optional[object] = None          # callable(name, tensor): told every named intermediate result
     tag: str = ""                           # prefix of the names noted now ("h.3." inside layer run 3)
-    # int32 per token, on the device: how far ``tok_pos`` moves before this step uses it.  Set only by a
-    # recorded single-token step, and only for an embedding that declares ``advances_positions``
-    advance: Optional[torch.Tensor] = None
 
     def note(self, name: str, tensor) -> None:
         """Hands an intermediate result to the step's trace, if there is one.  A

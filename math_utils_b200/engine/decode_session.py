@@ -18,14 +18,16 @@ Three ways to drive it:
     sequences have ended and stay where they are) and reads every step's
     samples, one step behind: while it looks at step s, step s + 1 already
     runs (the generation loop, which has to see stop tokens but should not
-    hold the device up).  Neither transfer is in the step's way: the host
-    sends how far each position moves (1, or 0 for a sequence that stays) on a
-    stream of its own while the step before still runs, the step's first
-    kernel adds that to the positions, and the samples are copied to the host
-    on another stream while the next step runs.
+    hold the device up).  Neither transfer is in the step's way: the
+    positions go to the device on a stream of their own while the step before
+    still runs, and the samples come back on another stream while the next
+    step runs.  No kernel of a step writes the positions, so a kernel may read
+    them before the kernel in front of it has ended (the attention kernels ask
+    for their pages that early).
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -38,9 +40,10 @@ from .batch import StepContext
 class DecodeSession:
     def __init__(self, model, cache, slots: Sequence[int], params: SamplingParams,
                  request_ids: Sequence[int], kv_bound: Optional[int] = None, pipelined: bool = False):
-        """``pipelined``: two graphs that take turns, each with a device buffer
-        and a pinned host buffer of its own for the samples and the kernels'
-        status word; a copy stream brings them to the host after the step while
+        """``pipelined``: two graphs that take turns, each with device and
+        pinned host buffers of its own: for the positions, which a copy stream
+        sends ahead of the step, and for the samples and the kernels' status
+        word, which another copy stream brings to the host after the step while
         the next step runs.  Without it a launch leaves the inputs alone, and
         each step's samples feed the next on the device."""
         self.model, self.cache = model, cache
@@ -92,16 +95,12 @@ class DecodeSession:
             self._done = [torch.cuda.Event() for _ in range(2)]
             self._unread = [False, False]
             self._first_tokens = torch.zeros(n, dtype=torch.int32, pin_memory=True)
-            # how far each position moves at the start of a turn's step, sent ahead on a stream of its own
-            self._advance_dev = [torch.zeros(n, dtype=torch.int32, device=dev) for _ in range(2)]
-            self._advance_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            # the positions of a turn's step, sent ahead on a stream of its own
+            self._pos_dev = [torch.zeros(n, dtype=torch.int32, device=dev) for _ in range(2)]
+            self._pos_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
             self._in_stream = torch.cuda.Stream(device=dev)
             self._sent = [torch.cuda.Event() for _ in range(2)]
-            # (staging buffers in turn: a copy may still be queued behind the two steps that can be unread)
-            self._sends = 0
-            self._positions_host = [torch.zeros(n, dtype=torch.int32, pin_memory=True) for _ in range(4)]
-            self._positions_dev: Optional[np.ndarray] = None      # tok_pos as the last launched step leaves it
-            self._in_kernel = bool(getattr(model.assembly.embedding, "advances_positions", False))
+            self._turn_ctx = [dataclasses.replace(self.ctx, tok_pos=self._pos_dev[t]) for t in range(2)]
             rt.ops.status_word(dev)                               # exists before any capture asks for it
         self.launches_per_step = 0
         self.logits: Optional[torch.Tensor] = None
@@ -114,6 +113,8 @@ class DecodeSession:
             raise ValueError(f"this session steps {self.n} sequences, got {len(slots)}")
         self.slots = list(slots)
         self.ctx.slots = self.slots
+        for ctx in getattr(self, "_turn_ctx", ()):
+            ctx.slots = self.slots
         h = self.host.numpy()
         o = int(self._offs[4])
         h[o:o + self.n] = np.asarray(self.slots, dtype=np.int32)
@@ -154,22 +155,15 @@ class DecodeSession:
     # ------------------------------------------------ pipelined: one step behind
     def start(self, tokens: Sequence[int], positions: Sequence[int]) -> None:
         """The tokens the first step of these sequences takes (later steps take
-        the samples of the step before, on the device) and its positions."""
+        the samples of the step before, on the device) and its positions (where
+        the set-up run before a recording writes its keys and values)."""
         torch.cuda.current_stream().synchronize()          # no copy from the staging buffers is still under way
         self._unread = [False, False]
         self._first_tokens.numpy()[:] = tokens
         self.token_ids.copy_(self._first_tokens, non_blocking=True)
-        self._send_positions(np.array(positions, dtype=np.int32))
+        self._pos_host[self._turn].numpy()[:] = positions
+        self.tok_pos.copy_(self._pos_host[self._turn], non_blocking=True)
         self._fed = True
-
-    def _send_positions(self, positions: np.ndarray) -> None:
-        """The positions themselves, on the launching stream (the first step of a batch; every step of a
-        model whose embedding does not move them on itself)."""
-        host = self._positions_host[self._sends % len(self._positions_host)]
-        self._sends += 1
-        host.numpy()[:] = positions
-        self.model.runtime.ops.copy_async(self.tok_pos, host)
-        self._positions_dev = positions
 
     def launch_step(self, positions: Sequence[int]) -> int:
         """Launches a step at these positions; returns the ticket to read its
@@ -180,20 +174,15 @@ class DecodeSession:
         if self._turn_graphs is None:
             self.capture()
         ops = self.model.runtime.ops
-        positions = np.array(positions, dtype=np.int32)
-        if self._in_kernel:
-            # the step's first kernel adds this to the positions the step before left (this turn's buffers
-            # are free: the step that last used them has been read)
-            self._advance_host[turn].numpy()[:] = positions - self._positions_dev
-            ops.copy_async(self._advance_dev[turn], self._advance_host[turn], stream=self._in_stream)
-            self._sent[turn].record(self._in_stream)
-            torch.cuda.current_stream().wait_event(self._sent[turn])
-            self._positions_dev = positions
-        else:
-            self._send_positions(positions)
+        # (this turn's buffers are free: the step that last used them has been read)
+        self._pos_host[turn].numpy()[:] = positions
+        ops.copy_async(self._pos_dev[turn], self._pos_host[turn], stream=self._in_stream)
+        self._sent[turn].record(self._in_stream)
+        main = torch.cuda.current_stream()
+        main.wait_event(self._sent[turn])
         self._unread[turn] = True
         self._turn_graphs[turn].replay()
-        self._stepped[turn].record()
+        self._stepped[turn].record(main)
         self._out_stream.wait_event(self._stepped[turn])
         ops.copy_async(self._out_host[turn], self._out_dev[turn], stream=self._out_stream)
         self._done[turn].record(self._out_stream)
@@ -214,19 +203,15 @@ class DecodeSession:
     # ------------------------------------------------------------------- steps
     def _run_once(self, turn: Optional[int] = None) -> None:
         """One step.  With ``turn`` (a recorded step of the pipelined kind) the
-        positions first move on by ``advance`` (the sampling kernel leaves them
-        alone), and the samples and the status word go to that turn's buffer."""
+        positions are that turn's, which the host sends before every launch
+        (the sampling kernel leaves them alone), and the samples and the status
+        word go to that turn's buffer."""
         ops = self.model.runtime.ops
-        out, status_to, moves = self.next_tokens, None, self.tok_pos
+        ctx, out, status_to, moves = self.ctx, self.next_tokens, None, self.tok_pos
         if turn is not None:
+            ctx, moves = self._turn_ctx[turn], None
             out, status_to = self._out_dev[turn][:self.n], self._out_dev[turn][self.n:]
-            moves = None
-            if self._in_kernel:
-                self.ctx.advance = self._advance_dev[turn]
-        try:
-            logits = self.logits = self.model.forward(self.ctx, self.cache)
-        finally:
-            self.ctx.advance = None
+        logits = self.logits = self.model.forward(ctx, self.cache)
         feed = (self.token_ids, moves, self.kv_bound - 1)            # samples become the next step's inputs
         if self.params.greedy:
             ops.argmax(logits, out=out, feed=feed, status_to=status_to)

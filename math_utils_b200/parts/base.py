@@ -178,15 +178,7 @@ class PositionEncoding(Part):
 
 
 class Embedding(Part):
-    """``forward(ctx, position_table)`` -> ``[T, hidden]`` float32 residual.
-
-    ``advances_positions``: whether ``forward`` honours ``ctx.advance`` (when
-    set: before anything uses ``ctx.tok_pos``, it moves on by ``ctx.advance``,
-    in place, in the step's first kernel).  A recorded single-token step sets
-    it only for an embedding that says so; for any other the host sends every
-    step's positions to the device before the step."""
-
-    advances_positions = False
+    """``forward(ctx, position_table)`` -> ``[T, hidden]`` float32 residual."""
 
     def forward(self, ctx, position_table):
         raise NotImplementedError

@@ -23,10 +23,8 @@ class TokenEmbedding(Embedding):
     def table(self):
         return self.weight
 
-    advances_positions = True
-
     def forward(self, ctx, position_table):
-        return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table, advance=ctx.advance)
+        return self.runtime.ops.embed(ctx.token_ids, ctx.tok_pos, self.weight, position_table)
 
 
 class TiedHead(Head):

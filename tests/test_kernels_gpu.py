@@ -51,15 +51,6 @@ def test_embed(dtype):
     assert np.abs(got - want).max() < 1e-6
     got = ops.embed(ids, None, table, None).cpu().numpy()
     assert np.array_equal(got, table.float().cpu().numpy()[ids.cpu()])
-    # positions that the kernel moves on itself before it uses them
-    moves = torch.tensor([1, 0, -2, 3, 0], dtype=torch.int32, device="cuda")
-    moved = p.clone()
-    got = ops.embed(ids, moved, table, pos, advance=moves).cpu().numpy()
-    at = (p + moves).cpu()
-    want = table.double().cpu().numpy()[ids.cpu()] + pos.double().cpu().numpy()[at]
-    assert np.abs(got - want).max() < 1e-6 and moved.cpu().tolist() == at.tolist()
-    with pytest.raises(ops.KernelError):
-        ops.embed(ids, moved, table, pos, advance=moves[:4].contiguous())
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])

@@ -75,8 +75,8 @@ class ToyRoutedFeedForward(FeedForward):
 
 
 class ToyEmbedding(Embedding):
-    """A token table looked up with torch's own indexing.  It does not move positions on itself
-    (``advances_positions`` stays False), so the host sends every recorded step's positions ahead of it."""
+    """A token table looked up with torch's own indexing: recorded single-token steps ask nothing of an
+    embedding beyond ``forward``."""
 
     def tensor_specs(self):
         return (TensorSpec(self.tensor_name("weight"), (int(self.param("vocab_size")), int(self.param("hidden_size"))),
@@ -90,7 +90,7 @@ class ToyEmbedding(Embedding):
         return self.weight
 
     def forward(self, ctx, position_table):
-        assert position_table is None and ctx.advance is None
+        assert position_table is None
         return self.weight[ctx.token_ids.long()].float()
 
 

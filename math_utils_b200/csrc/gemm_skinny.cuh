@@ -78,8 +78,13 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wn = warp % WN, wk = warp / WN;
     const int g = lane >> 2, t = lane & 3;
-    const int n_base = blockIdx.x * ROWS + wn * 16;
     const int rank = CK > 1 ? (int)blockIdx.y : 0;         // the cluster spans grid.y
+    // A block takes the tiles of ROWS output columns blockIdx.x, + gridDim.x, ...: one tile, unless the launcher
+    // starts fewer blocks than tiles (many output columns: as many blocks as are resident at once, each norming
+    // its rows once and then streaming tile after tile).
+    const int n_tiles = (N + ROWS - 1) / ROWS;
+    int tile = blockIdx.x;
+    int n_base = tile * ROWS + wn * 16;
 
     // K is cut into CK * WK slices on 32-element boundaries
     const int k_blocks = (K + 31) / 32;
@@ -87,9 +92,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     const int kb0 = (rank * WK + wk) * per, kb1 = min(k_blocks, kb0 + per);
 
     // rows past the end are clamped for loading and dropped when writing
-    const int r0 = min(n_base + g, N - 1), r1 = min(n_base + g + 8, N - 1);
-    const __nv_bfloat16* w0 = W + (long long)r0 * ldw + 8 * t;
-    const __nv_bfloat16* w1 = W + (long long)r1 * ldw + 8 * t;
+    const __nv_bfloat16* w0 = W + (long long)min(n_base + g, N - 1) * ldw + 8 * t;
+    const __nv_bfloat16* w1 = W + (long long)min(n_base + g + 8, N - 1) * ldw + 8 * t;
 
     // the first weights are asked for before anything else: they do not depend on the activations
     constexpr int UNROLL = 4;
@@ -112,7 +116,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     // bias and norm parameters are weights too: they set off before the wait as well
     __shared__ float bias_s[ROWS];
     if (threadIdx.x < ROWS) {
-        const int n = blockIdx.x * ROWS + threadIdx.x;
+        const int n = tile * ROWS + threadIdx.x;
         bias_s[threadIdx.x] = (bias && n < N) ? bias[n] : 0.0f;
     }
     float* gamma_s = reinterpret_cast<float*>(skinny_dyn + (size_t)MP * act_ld * sizeof(__nv_bfloat16));
@@ -134,7 +138,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int idx = threadIdx.x + i * SK_WARPS * 32;
-            const int m = idx / ROWS, n = blockIdx.x * ROWS + idx % ROWS;
+            const int m = idx / ROWS, n = tile * ROWS + idx % ROWS;
             if (idx < ROWS * M && n < N) res_pre[i] = residual[(long long)m * ldr + n];
         }
     }
@@ -220,6 +224,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         xrow[j] = LN ? act_smem + (long long)m * act_ld + 8 * t : A + (long long)min(m, M - 1) * lda + 8 * t;
     }
 
+    for (;;) {                                     // over this block's tiles
     float acc[MT][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j)
@@ -278,7 +283,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         cluster.sync();
         if (rank != 0) return;
     }
-    const int col0 = blockIdx.x * ROWS;
+    const int col0 = tile * ROWS;
     for (int idx = threadIdx.x; idx < ROWS * M; idx += SK_WARPS * 32) {
         const int m = idx / ROWS, r = idx % ROWS;
         const int n = col0 + r;
@@ -297,6 +302,28 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             v += turn == 0 ? res_pre[0] : turn == 1 ? res_pre[1] : residual[(long long)m * ldr + n];
         }
         C[(long long)m * ldc + n] = from_float<TC>(v);
+    }
+    tile += gridDim.x;
+    if (CK > 1 || tile >= n_tiles) break;
+    // the next tile of this block: its first weights set off, then the shared arrays change hands
+    n_base = tile * ROWS + wn * 16;
+    w0 = W + (long long)min(n_base + g, N - 1) * ldw + 8 * t;
+    w1 = W + (long long)min(n_base + g + 8, N - 1) * ldw + 8 * t;
+    load_weights(kb0);
+    __syncthreads();                               // everyone has read red and bias_s
+    if (threadIdx.x < ROWS) {
+        const int n = tile * ROWS + threadIdx.x;
+        bias_s[threadIdx.x] = (bias && n < N) ? bias[n] : 0.0f;
+    }
+    res_pre[0] = res_pre[1] = 0.0f;
+    if (residual) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = threadIdx.x + i * SK_WARPS * 32;
+            const int m = idx / ROWS, n = tile * ROWS + idx % ROWS;
+            if (idx < ROWS * M && n < N) res_pre[i] = residual[(long long)m * ldr + n];
+        }
+    }
     }
 }
 
@@ -320,7 +347,22 @@ static int launch_skinny_as(const __nv_bfloat16* A, const __nv_bfloat16* W, cons
             }
         }
     }
-    return launch_pdl(kernel, dim3((N + 16 * WN - 1) / (16 * WN), CK, 1), dim3(SK_WARPS * 32), dyn, s, CK, A, W, bias,
+    int blocks = (N + 16 * WN - 1) / (16 * WN);
+    if (CK == 1) {
+        // more tiles than blocks are resident at once: that many blocks, each walking over its tiles (it norms
+        // its rows once, and no second wave of blocks starts from nothing)
+        static int per_sm = 0;
+        static size_t per_sm_dyn = ~(size_t)0;
+        if (per_sm_dyn != dyn) {
+            per_sm = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SK_WARPS * 32, dyn) != cudaSuccess)
+                per_sm = 0;
+            per_sm_dyn = dyn;
+        }
+        const long long resident = (long long)per_sm * sm_count();
+        if (resident > 0 && blocks > resident) blocks = (int)resident;
+    }
+    return launch_pdl(kernel, dim3(blocks, CK, 1), dim3(SK_WARPS * 32), dyn, s, CK, A, W, bias,
                       residual, C, M, N, K, lda, ldw, ldc, ldr, act, norm);
 }
 

@@ -459,7 +459,7 @@ def run_marginal(args):
     import torch
     from math_utils_b200.csrc import ops
     from math_utils_b200.sampling import SamplingParams
-    cfg = baseline_config("small")
+    cfg = baseline_config(args.config)             # --config medium|xl: that model's layer sizes
     if args.layers:
         cfg["n_layer"] = args.layers
     llm = load_random(cfg, temperature=0.0, context=CONTEXT, max_batch=64)
@@ -503,7 +503,7 @@ def run_marginal(args):
         for key, fn in real.items():
             setattr(ops, key, fn)
     whole = times.pop("whole step")
-    print(json.dumps({"part": "marginal", "batch": args.batch, "layers": cfg["n_layer"], "step_us": round(whole, 1),
+    print(json.dumps({"part": "marginal", "config": args.config, "batch": args.batch, "layers": cfg["n_layer"], "step_us": round(whole, 1),
                       "marginal_us": {k: round(whole - t, 1) for k, t in times.items()},
                       "per_layer_us": {k: round((whole - t) / cfg["n_layer"], 2) for k, t in times.items()
                                        if k not in ("head", "argmax")}}))
@@ -620,10 +620,10 @@ def main():
         return 2
     if args.impl == "reference":
         return run_reference(args)
-    if args.config != "small":
-        return run_workload(args)
     if args.only == "marginal":
         return run_marginal(args)
+    if args.config != "small":
+        return run_workload(args)
     if args.only != "all":
         return run_part(args)
     return run_ours(args)

@@ -380,6 +380,11 @@ MU_EXPORT int mu_gemm_rows(const void* A, const void* W, const float* bias, cons
         // share an SM) and a k-block for every block
         splits = 1;
         while (splits * 2 <= limit && tiles * splits * 2 <= sms + sms / 3 && splits * 2 <= num_kb) splits *= 2;
+        // a block that would stream more than 128 KB of weights through its ring is cut once more, up to two
+        // blocks an SM: with that much to read, bytes in flight count for more than a short exchange of parts
+        const long long block_bytes = (long long)mu::GR_BM * K * (long long)sizeof(__nv_bfloat16) / splits;
+        if (block_bytes > 128 * 1024 && splits * 2 <= limit && splits * 2 <= num_kb && tiles * splits * 2 <= 2ll * sms)
+            splits *= 2;
     }
     while (splits > limit || splits > num_kb) splits /= 2;
     const int nb = M <= 16 ? 16 : M <= 32 ? 32 : 64;

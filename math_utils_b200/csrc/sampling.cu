@@ -151,6 +151,50 @@ __device__ __forceinline__ void select_bin(const unsigned long long* hist, unsig
     }
 }
 
+// The first byte of the keys (sign and exponent) takes a handful of values whatever the logits are, so in the
+// first pass of a descent every token would queue on a few shared-memory words.  There the warps add into
+// `groups` histograms (one a warp), in 32-bit words
+// that native shared-memory atomics serve: a count, or a mass (at most 2^40) cut into two limbs of 20 bits.  A
+// group sees at most vocab / groups + 32 tokens, so a limb's sum stays below 2^32 up to 4,000 tokens a group
+// (a vocabulary of 128,000 with a group a warp); beyond that the block's one histogram is used as in the
+// later passes.  fold_private() adds the groups' histograms up into the block's 64-bit one.
+constexpr int SAMPLE_WARPS = SAMPLE_THREADS / 32;
+constexpr int LIMBS = 2, LIMB_BITS = 20;
+constexpr size_t sample_private_bytes(int groups) { return (size_t)groups * 256 * LIMBS * sizeof(unsigned int); }
+
+__device__ __forceinline__ void zero_private(unsigned int* priv, int groups) {
+    for (int i = threadIdx.x; i < groups * 256 * LIMBS; i += SAMPLE_THREADS) priv[i] = 0u;
+}
+__device__ __forceinline__ void fold_private(const unsigned int* priv, int groups, unsigned long long* hist) {
+    if (threadIdx.x < 256) {
+        unsigned long long limb[LIMBS] = {0, 0};
+        for (int g = 0; g < groups; ++g)
+#pragma unroll
+            for (int k = 0; k < LIMBS; ++k) limb[k] += priv[(g * 256 + threadIdx.x) * LIMBS + k];
+        hist[threadIdx.x] = limb[0] + (limb[1] << LIMB_BITS);
+    }
+}
+
+// f(i, logit) for every token i of this thread (tid, tid + SAMPLE_THREADS, ...), in rising order.  Eight
+// logits are asked for before any is used: a pass over the row is a chain of trips to the L2 otherwise.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* row, int vocab, F f) {
+    constexpr int U = 8;
+    for (int i0 = threadIdx.x; i0 < vocab; i0 += SAMPLE_THREADS * U) {
+        float l[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * SAMPLE_THREADS;
+            l[u] = i < vocab ? row[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * SAMPLE_THREADS;
+            if (i < vocab) f(i, l[u]);
+        }
+    }
+}
+
 struct RowView {
     const float* row;
     int vocab;
@@ -161,7 +205,8 @@ struct RowView {
         return key > thr_key || (key == thr_key && i <= idx_cut);
     }
     __device__ __forceinline__ unsigned long long mass(float logit) const {
-        return (unsigned long long)((double)expf(logit / temperature - best) * FIXED_ONE);
+        // (a float times 2^40 is exact, and so is the float's way to the integer: the same number as through double)
+        return __float2ull_rz(expf(logit / temperature - best) * (float)FIXED_ONE);
     }
 };
 
@@ -169,8 +214,14 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature, int top_k,
               unsigned long long seed, const long long* __restrict__ request_ids,
               int* __restrict__ draw_index, int* __restrict__ out, int* __restrict__ feed_ids,
-              int* __restrict__ feed_pos, int last_pos, StatusCopy status_copy) {
+              int* __restrict__ feed_pos, int last_pos, StatusCopy status_copy, int staged, int groups) {
     __shared__ unsigned long long hist[256];
+    // dynamic shared memory: with `staged` the row's logits (every pass reads them there instead of going to the
+    // L2 a dozen times), then the groups' histograms of the first pass of a descent (see above)
+    extern __shared__ __align__(16) unsigned char sample_dyn[];
+    float* row_smem = reinterpret_cast<float*>(sample_dyn);
+    unsigned int* priv = reinterpret_cast<unsigned int*>(sample_dyn + (staged ? ((size_t)vocab * 4 + 15) / 16 * 16 : 0));
+    const bool private_ok = vocab / groups + 32 < (1 << (32 - LIMB_BITS));   // else a limb could overflow
     __shared__ unsigned long long sel[2];
     __shared__ float red[32];
     __shared__ unsigned long long total_smem;
@@ -184,10 +235,15 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     v.temperature = temperature;
     v.thr_key = 0;
     v.idx_cut = vocab;
+    if (staged) {
+        for_each_logit(v.row, vocab, [&](int i, float l) { row_smem[i] = l; });
+        __syncthreads();
+        v.row = row_smem;
+    }
 
     // maximum logit
     float mx = -INFINITY;
-    for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, v.row[i]);
+    for_each_logit(v.row, vocab, [&](int, float l) { mx = fmaxf(mx, l); });
     mx = warp_max(mx);
     if ((tid & 31) == 0) red[tid >> 5] = mx;
     __syncthreads();
@@ -202,19 +258,28 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         for (int shift = 24; shift >= 0; shift -= 8) {
             if (tid < 256) hist[tid] = 0;
             __syncthreads();
-            {
-                // neighbouring tokens mostly share a bin: add up a run before touching shared memory
+            if (shift == 24 && private_ok) {
+                // every token takes part and the bins are few: a histogram per warp
+                zero_private(priv, groups);
+                __syncthreads();
+                unsigned int* mine = priv + (size_t)((tid >> 5) * groups / SAMPLE_WARPS) * 256 * LIMBS;
+                for_each_logit(v.row, vocab, [&](int, float l) { atomicAdd(&mine[(float_key(l) >> 24) * LIMBS], 1u); });
+                __syncthreads();
+                fold_private(priv, groups, hist);
+            } else {
+                // few tokens are left, spread over the bins; a thread adds up a run of one bin before it
+                // touches shared memory
                 int cur = -1;
                 unsigned long long run = 0;
-                for (int i = tid; i < vocab; i += blockDim.x) {
-                    const unsigned int key = float_key(v.row[i]);
-                    if ((key & mask) != prefix) continue;
+                for_each_logit(v.row, vocab, [&](int, float l) {
+                    const unsigned int key = float_key(l);
+                    if ((key & mask) != prefix) return;
                     const int bin = (int)((key >> shift) & 255u);
-                    if (bin == cur) { ++run; continue; }
+                    if (bin == cur) { ++run; return; }
                     if (cur >= 0) atomicAdd(&hist[cur], run);
                     cur = bin;
                     run = 1;
-                }
+                });
                 if (cur >= 0) atomicAdd(&hist[cur], run);
             }
             __syncthreads();
@@ -242,48 +307,60 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         __syncthreads();
     }
 
-    // total mass of the kept tokens
-    if (tid == 0) total_smem = 0;
-    __syncthreads();
-    {
-        unsigned long long local = 0;
-        for (int i = tid; i < vocab; i += blockDim.x) {
-            const float l = v.row[i];
-            if (v.kept(float_key(l), i)) local += v.mass(l);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-        if ((tid & 31) == 0) atomicAdd(&total_smem, local);
-    }
-    __syncthreads();
-    const unsigned long long total = total_smem;
     const long long request = request_ids ? request_ids[r] : r;
     const double u = uniform_draw(seed, (unsigned long long)request, (unsigned long long)draw_index[r]);
-    unsigned long long target = (unsigned long long)(u * (double)total);
-    if (target >= total) target = total - 1;
+    unsigned long long target = 0;                 // u * (total mass of the kept tokens), known after the first pass
 
     // the key at which the running mass, taken from the largest logit down, passes target
     unsigned int prefix = 0, mask = 0;
     for (int shift = 24; shift >= 0; shift -= 8) {
         if (tid < 256) hist[tid] = 0;
         __syncthreads();
-        {
+        if (shift == 24 && private_ok) {
+            zero_private(priv, groups);
+            __syncthreads();
+            unsigned int* mine = priv + (size_t)((tid >> 5) * groups / SAMPLE_WARPS) * 256 * LIMBS;
+            for_each_logit(v.row, vocab, [&](int i, float l) {
+                const unsigned int key = float_key(l);
+                if (!v.kept(key, i)) return;
+                const unsigned long long w = v.mass(l);             // at most 2^40
+                unsigned int* word = &mine[(key >> 24) * LIMBS];
+                atomicAdd(word, (unsigned int)(w & ((1u << LIMB_BITS) - 1)));
+                atomicAdd(word + 1, (unsigned int)(w >> LIMB_BITS));
+            });
+            __syncthreads();
+            fold_private(priv, groups, hist);
+        } else {
             int cur = -1;
             unsigned long long run = 0;
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const float l = v.row[i];
+            for_each_logit(v.row, vocab, [&](int i, float l) {
                 const unsigned int key = float_key(l);
-                if ((key & mask) != prefix || !v.kept(key, i)) continue;
+                if ((key & mask) != prefix || !v.kept(key, i)) return;
                 const int bin = (int)((key >> shift) & 255u);
                 const unsigned long long w = v.mass(l);
-                if (bin == cur) { run += w; continue; }
+                if (bin == cur) { run += w; return; }
                 if (cur >= 0) atomicAdd(&hist[cur], run);
                 cur = bin;
                 run = w;
-            }
+            });
             if (cur >= 0) atomicAdd(&hist[cur], run);
         }
         __syncthreads();
+        if (shift == 24) {
+            // the first histogram holds every kept token: its sum is the total mass the draw is scaled by
+            if (tid == 0) total_smem = 0;
+            __syncthreads();
+            if (tid < 256) {
+                unsigned long long part = hist[tid];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                if ((tid & 31) == 0) atomicAdd(&total_smem, part);
+            }
+            __syncthreads();
+            const unsigned long long total = total_smem;
+            target = (unsigned long long)(u * (double)total);
+            if (target >= total) target = total - 1;
+        }
         if (tid < 32) select_bin(hist, target, sel);
         __syncthreads();
         prefix |= (unsigned int)sel[0] << shift;
@@ -304,8 +381,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     const unsigned long long one = v.mass(group_logit);
     const unsigned long long nth = one ? target / one : 0;
     if (nth == 0) {
-        for (int i = tid; i < vocab; i += blockDim.x)
-            if (float_key(v.row[i]) == prefix && v.kept(prefix, i)) atomicMin(&found_idx, i);
+        for_each_logit(v.row, vocab, [&](int i, float l) {
+            if (float_key(l) == prefix && v.kept(prefix, i)) atomicMin(&found_idx, i);
+        });
     } else if (tid == 0) {
         unsigned long long seen = 0;
         for (int i = 0; i < vocab; ++i)
@@ -360,7 +438,24 @@ MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab
     if (!(temperature > 0.0f) || top_k < 0) return MU_ERR_BAD_ARGUMENT;
     if ((status == nullptr) != (status_out == nullptr)) return MU_ERR_BAD_ARGUMENT;
     const mu::StatusCopy status_copy{status, status_out};
-    return mu::launch_pdl(mu::sample_kernel, dim3(n_rows), dim3(mu::SAMPLE_THREADS), 0, (cudaStream_t)stream, 1,
+    // the row in shared memory if it fits beside a histogram per warp (vocabularies up to some 32,000); else it
+    // is read from the L2 in every pass (fewer histograms to make room cost more than the staging gains)
+    const size_t limit = 224 * 1024;             // (the kernel has a little static shared memory of its own)
+    static bool raised = false;
+    if (!raised) {
+        if (cudaFuncSetAttribute(mu::sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) !=
+            cudaSuccess)
+            return MU_ERR_LAUNCH;
+        raised = true;
+    }
+    const size_t row_bytes = ((size_t)vocab * 4 + 15) / 16 * 16;
+    int staged = 0, groups = mu::SAMPLE_WARPS;
+    size_t dyn = mu::sample_private_bytes(groups);
+    if (row_bytes + mu::sample_private_bytes(groups) <= limit) {
+        staged = 1;
+        dyn += row_bytes;
+    }
+    return mu::launch_pdl(mu::sample_kernel, dim3(n_rows), dim3(mu::SAMPLE_THREADS), dyn, (cudaStream_t)stream, 1,
                           logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out, feed_ids,
-                          feed_pos, last_pos, status_copy);
+                          feed_pos, last_pos, status_copy, staged, groups);
 }

@@ -157,7 +157,11 @@ class DecodeSession:
         """The tokens the first step of these sequences takes (later steps take
         the samples of the step before, on the device) and its positions (where
         the set-up run before a recording writes its keys and values)."""
-        torch.cuda.current_stream().synchronize()          # no copy from the staging buffers is still under way
+        # no copy from or to the staging buffers is still under way (a batch that ended with an error may have
+        # left steps unread)
+        torch.cuda.current_stream().synchronize()
+        self._in_stream.synchronize()
+        self._out_stream.synchronize()
         self._unread = [False, False]
         self._first_tokens.numpy()[:] = tokens
         self.token_ids.copy_(self._first_tokens, non_blocking=True)

@@ -159,6 +159,7 @@ __device__ __forceinline__ void select_bin(const unsigned long long* hist, unsig
 // (a vocabulary of 128,000 with a group a warp); beyond that the block's one histogram is used as in the
 // later passes.  fold_private() adds the groups' histograms up into the block's 64-bit one.
 constexpr int SAMPLE_WARPS = SAMPLE_THREADS / 32;
+constexpr int SAMPLE_CANDIDATES = 1024;
 constexpr int LIMBS = 2, LIMB_BITS = 20;
 constexpr size_t sample_private_bytes(int groups) { return (size_t)groups * 256 * LIMBS * sizeof(unsigned int); }
 
@@ -226,6 +227,13 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     __shared__ float red[32];
     __shared__ unsigned long long total_smem;
     __shared__ int found_idx;
+    // With a top_k of at most SAMPLE_CANDIDATES the kept tokens are gathered here once the threshold is known,
+    // and everything after that (the largest logit, the masses, the second descent, the pick) walks this list
+    // instead of the row.
+    __shared__ float cand_logit[SAMPLE_CANDIDATES];
+    __shared__ int cand_idx[SAMPLE_CANDIDATES];
+    __shared__ int n_cand;
+    const bool gather = top_k > 0 && top_k < vocab && top_k <= SAMPLE_CANDIDATES;
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, r = blockIdx.x;
@@ -241,15 +249,21 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         v.row = row_smem;
     }
 
-    // maximum logit
-    float mx = -INFINITY;
-    for_each_logit(v.row, vocab, [&](int, float l) { mx = fmaxf(mx, l); });
-    mx = warp_max(mx);
-    if ((tid & 31) == 0) red[tid >> 5] = mx;
-    __syncthreads();
-    mx = red[0];
-    for (int w = 1; w < (blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
-    v.best = mx / temperature;
+    // maximum logit (of the row; with a gathered top_k it is the largest of the list, found below)
+    auto block_max = [&](float mx) {
+        mx = warp_max(mx);
+        __syncthreads();                               // (red may still be read from an earlier call)
+        if ((tid & 31) == 0) red[tid >> 5] = mx;
+        __syncthreads();
+        mx = red[0];
+        for (int w = 1; w < SAMPLE_WARPS; ++w) mx = fmaxf(mx, red[w]);
+        return mx;
+    };
+    if (!gather) {
+        float mx = -INFINITY;
+        for_each_logit(v.row, vocab, [&](int, float l) { mx = fmaxf(mx, l); });
+        v.best = block_max(mx) / temperature;
+    }
 
     // the k-th largest key, when top_k cuts anything
     if (top_k > 0 && top_k < vocab) {
@@ -306,6 +320,28 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         v.idx_cut = found_idx;
         __syncthreads();
     }
+    if (gather) {
+        if (tid == 0) n_cand = 0;
+        __syncthreads();
+        for_each_logit(v.row, vocab, [&](int i, float l) {
+            if (v.kept(float_key(l), i)) {
+                const int at = atomicAdd(&n_cand, 1);      // top_k of them at most: the order does not matter
+                if (at < SAMPLE_CANDIDATES) { cand_logit[at] = l; cand_idx[at] = i; }
+            }
+        });
+        __syncthreads();
+        float mx = -INFINITY;
+        for (int c = tid; c < n_cand; c += SAMPLE_THREADS) mx = fmaxf(mx, cand_logit[c]);
+        v.best = block_max(mx) / temperature;
+    }
+    // f(i, logit) for every kept token of this thread: from the list, or from the row (f checks `kept` itself)
+    auto each_kept = [&](auto f) {
+        if (gather) {
+            for (int c = tid; c < n_cand; c += SAMPLE_THREADS) f(cand_idx[c], cand_logit[c]);
+        } else {
+            for_each_logit(v.row, vocab, f);
+        }
+    };
 
     const long long request = request_ids ? request_ids[r] : r;
     const double u = uniform_draw(seed, (unsigned long long)request, (unsigned long long)draw_index[r]);
@@ -320,7 +356,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
             zero_private(priv, groups);
             __syncthreads();
             unsigned int* mine = priv + (size_t)((tid >> 5) * groups / SAMPLE_WARPS) * 256 * LIMBS;
-            for_each_logit(v.row, vocab, [&](int i, float l) {
+            each_kept([&](int i, float l) {
                 const unsigned int key = float_key(l);
                 if (!v.kept(key, i)) return;
                 const unsigned long long w = v.mass(l);             // at most 2^40
@@ -333,7 +369,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         } else {
             int cur = -1;
             unsigned long long run = 0;
-            for_each_logit(v.row, vocab, [&](int i, float l) {
+            each_kept([&](int i, float l) {
                 const unsigned int key = float_key(l);
                 if ((key & mask) != prefix || !v.kept(key, i)) return;
                 const int bin = (int)((key >> shift) & 255u);
@@ -381,16 +417,29 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     const unsigned long long one = v.mass(group_logit);
     const unsigned long long nth = one ? target / one : 0;
     if (nth == 0) {
-        for_each_logit(v.row, vocab, [&](int i, float l) {
+        each_kept([&](int i, float l) {
             if (float_key(l) == prefix && v.kept(prefix, i)) atomicMin(&found_idx, i);
         });
     } else if (tid == 0) {
         unsigned long long seen = 0;
-        for (int i = 0; i < vocab; ++i)
-            if (float_key(v.row[i]) == prefix && v.kept(prefix, i)) {
-                found_idx = i;                       // the last one stands if fewer than nth + 1 exist
+        if (gather) {
+            // the list is in no order: the next larger index among the equal ones, nth + 1 times
+            int last = -1;
+            for (;;) {
+                int next = vocab;
+                for (int c = 0; c < n_cand; ++c)
+                    if (float_key(cand_logit[c]) == prefix && cand_idx[c] > last && cand_idx[c] < next) next = cand_idx[c];
+                if (next == vocab) break;
+                found_idx = last = next;             // the last one stands if fewer than nth + 1 exist
                 if (seen++ == nth) break;
             }
+        } else {
+            for (int i = 0; i < vocab; ++i)
+                if (float_key(v.row[i]) == prefix && v.kept(prefix, i)) {
+                    found_idx = i;                   // the last one stands if fewer than nth + 1 exist
+                    if (seen++ == nth) break;
+                }
+        }
     }
     (void)group_mass;
     __syncthreads();
@@ -440,7 +489,7 @@ MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab
     const mu::StatusCopy status_copy{status, status_out};
     // the row in shared memory if it fits beside a histogram per warp (vocabularies up to some 32,000); else it
     // is read from the L2 in every pass (fewer histograms to make room cost more than the staging gains)
-    const size_t limit = 224 * 1024;             // (the kernel has a little static shared memory of its own)
+    const size_t limit = 214 * 1024;             // (the kernel has some 11 KB of static shared memory of its own)
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(mu::sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) !=

@@ -20,6 +20,10 @@
 // include/math/Random.hpp:27,79-84), n = how many tokens the request has drawn.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
 namespace mu {
 
 constexpr int SAMPLE_THREADS = 1024;
@@ -176,21 +180,23 @@ __device__ __forceinline__ void fold_private(const unsigned int* priv, int group
     }
 }
 
-// f(i, logit) for every token i of this thread (tid, tid + SAMPLE_THREADS, ...), in rising order.  Eight
-// logits are asked for before any is used: a pass over the row is a chain of trips to the L2 otherwise.
+// f(i, logit) for every token i of this thread, in rising order: the tokens tid + SAMPLE_THREADS * (part + parts * k),
+// k = 0, 1, ... (`parts` blocks share a row, block `part` takes every parts-th run of SAMPLE_THREADS tokens).
+// Eight logits are asked for before any is used: a pass over the row is a chain of trips to the L2 otherwise.
 template <typename F>
-__device__ __forceinline__ void for_each_logit(const float* row, int vocab, F f) {
+__device__ __forceinline__ void for_each_logit(const float* row, int vocab, F f, int part = 0, int parts = 1) {
     constexpr int U = 8;
-    for (int i0 = threadIdx.x; i0 < vocab; i0 += SAMPLE_THREADS * U) {
+    const int step = parts * SAMPLE_THREADS;
+    for (int i0 = part * SAMPLE_THREADS + threadIdx.x; i0 < vocab; i0 += step * U) {
         float l[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * SAMPLE_THREADS;
+            const int i = i0 + u * step;
             l[u] = i < vocab ? row[i] : 0.0f;
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * SAMPLE_THREADS;
+            const int i = i0 + u * step;
             if (i < vocab) f(i, l[u]);
         }
     }
@@ -215,8 +221,14 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature, int top_k,
               unsigned long long seed, const long long* __restrict__ request_ids,
               int* __restrict__ draw_index, int* __restrict__ out, int* __restrict__ feed_ids,
-              int* __restrict__ feed_pos, int last_pos, StatusCopy status_copy, int staged, int groups) {
+              int* __restrict__ feed_pos, int last_pos, StatusCopy status_copy, int staged, int groups, int parts) {
+    // `parts` > 1: that many blocks (a thread-block cluster along grid.y) share a row for the passes over the
+    // whole row: each counts its share into a histogram of its own, every block adds the shares up through
+    // distributed shared memory (the same sums in the same order: every block selects the same bin), and the
+    // kept tokens are gathered in block 0, which finishes alone.  Only for a gathered top_k (see below).
     __shared__ unsigned long long hist[256];
+    __shared__ unsigned long long hist_share[2][256];    // this block's share; two, used in turn, so that a block
+                                                         // may start its next pass while others still read this one
     // dynamic shared memory: with `staged` the row's logits (every pass reads them there instead of going to the
     // L2 a dozen times), then the groups' histograms of the first pass of a descent (see above)
     extern __shared__ __align__(16) unsigned char sample_dyn[];
@@ -237,6 +249,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, r = blockIdx.x;
+    const int part = parts > 1 ? (int)blockIdx.y : 0;
+    cg::cluster_group cluster = cg::this_cluster();
+    if (tid == 0) n_cand = 0;                          // (block 0's is the one the cluster fills)
     RowView v;
     v.row = logits + (long long)r * ld;
     v.vocab = vocab;
@@ -270,16 +285,18 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         unsigned int prefix = 0, mask = 0;
         unsigned long long need = (unsigned long long)top_k - 1;   // first bin whose running count exceeds this
         for (int shift = 24; shift >= 0; shift -= 8) {
-            if (tid < 256) hist[tid] = 0;
+            unsigned long long* share = parts > 1 ? hist_share[(shift >> 3) & 1] : hist;
+            if (tid < 256) share[tid] = 0;
             __syncthreads();
             if (shift == 24 && private_ok) {
                 // every token takes part and the bins are few: a histogram per warp
                 zero_private(priv, groups);
                 __syncthreads();
                 unsigned int* mine = priv + (size_t)((tid >> 5) * groups / SAMPLE_WARPS) * 256 * LIMBS;
-                for_each_logit(v.row, vocab, [&](int, float l) { atomicAdd(&mine[(float_key(l) >> 24) * LIMBS], 1u); });
+                for_each_logit(v.row, vocab, [&](int, float l) { atomicAdd(&mine[(float_key(l) >> 24) * LIMBS], 1u); },
+                               part, parts);
                 __syncthreads();
-                fold_private(priv, groups, hist);
+                fold_private(priv, groups, share);
             } else {
                 // few tokens are left, spread over the bins; a thread adds up a run of one bin before it
                 // touches shared memory
@@ -290,11 +307,19 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
                     if ((key & mask) != prefix) return;
                     const int bin = (int)((key >> shift) & 255u);
                     if (bin == cur) { ++run; return; }
-                    if (cur >= 0) atomicAdd(&hist[cur], run);
+                    if (cur >= 0) atomicAdd(&share[cur], run);
                     cur = bin;
                     run = 1;
-                });
-                if (cur >= 0) atomicAdd(&hist[cur], run);
+                }, part, parts);
+                if (cur >= 0) atomicAdd(&share[cur], run);
+            }
+            if (parts > 1) {
+                cluster.sync();                        // every block's share is complete
+                if (tid < 256) {
+                    unsigned long long sum = 0;
+                    for (int c = 0; c < parts; ++c) sum += *cluster.map_shared_rank(&share[tid], c);
+                    hist[tid] = sum;
+                }
             }
             __syncthreads();
             if (tid < 32) select_bin(hist, need, sel);
@@ -321,14 +346,21 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         __syncthreads();
     }
     if (gather) {
-        if (tid == 0) n_cand = 0;
-        __syncthreads();
+        // (n_cand was set to zero at the start, and every block has passed a barrier of the block, and of the
+        // cluster if there is one, since)
+        int* count = parts > 1 ? cluster.map_shared_rank(&n_cand, 0) : &n_cand;
+        float* list_logit = parts > 1 ? cluster.map_shared_rank(cand_logit, 0) : cand_logit;
+        int* list_idx = parts > 1 ? cluster.map_shared_rank(cand_idx, 0) : cand_idx;
         for_each_logit(v.row, vocab, [&](int i, float l) {
             if (v.kept(float_key(l), i)) {
-                const int at = atomicAdd(&n_cand, 1);      // top_k of them at most: the order does not matter
-                if (at < SAMPLE_CANDIDATES) { cand_logit[at] = l; cand_idx[at] = i; }
+                const int at = atomicAdd(count, 1);        // top_k of them at most: the order does not matter
+                if (at < SAMPLE_CANDIDATES) { list_logit[at] = l; list_idx[at] = i; }
             }
-        });
+        }, part, parts);
+        if (parts > 1) {
+            cluster.sync();                            // the list is complete; block 0 goes on alone, reading
+            if (part != 0) return;                     // nothing of the others any more
+        }
         __syncthreads();
         float mx = -INFINITY;
         for (int c = tid; c < n_cand; c += SAMPLE_THREADS) mx = fmaxf(mx, cand_logit[c]);
@@ -489,7 +521,7 @@ MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab
     const mu::StatusCopy status_copy{status, status_out};
     // the row in shared memory if it fits beside a histogram per warp (vocabularies up to some 32,000); else it
     // is read from the L2 in every pass (fewer histograms to make room cost more than the staging gains)
-    const size_t limit = 214 * 1024;             // (the kernel has some 11 KB of static shared memory of its own)
+    const size_t limit = 208 * 1024;             // (the kernel has some 15 KB of static shared memory of its own)
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(mu::sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) !=
@@ -498,13 +530,21 @@ MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab
         raised = true;
     }
     const size_t row_bytes = ((size_t)vocab * 4 + 15) / 16 * 16;
+    // a gathered top_k over a long row: up to eight blocks share the passes over the row
+    const bool gathered = top_k > 0 && top_k < vocab && top_k <= mu::SAMPLE_CANDIDATES;
+    // (a block of this kernel has an SM to itself; clusters of eight find their place only while a third of the
+    // SMs stay free)
+    const int sms = mu::sm_count();
+    int parts = 1;
+    if (gathered && vocab >= 16 * mu::SAMPLE_THREADS && sms > 0)
+        parts = n_rows * 8 <= sms * 2 / 3 ? 8 : n_rows * 4 <= sms * 9 / 10 ? 4 : n_rows * 2 <= sms ? 2 : 1;
     int staged = 0, groups = mu::SAMPLE_WARPS;
     size_t dyn = mu::sample_private_bytes(groups);
-    if (row_bytes + mu::sample_private_bytes(groups) <= limit) {
+    if (parts == 1 && row_bytes + mu::sample_private_bytes(groups) <= limit) {
         staged = 1;
         dyn += row_bytes;
     }
-    return mu::launch_pdl(mu::sample_kernel, dim3(n_rows), dim3(mu::SAMPLE_THREADS), dyn, (cudaStream_t)stream, 1,
+    return mu::launch_pdl(mu::sample_kernel, dim3(n_rows, parts), dim3(mu::SAMPLE_THREADS), dyn, (cudaStream_t)stream, parts,
                           logits, ld, vocab, temperature, top_k, seed, request_ids, draw_index, out, feed_ids,
-                          feed_pos, last_pos, status_copy, staged, groups);
+                          feed_pos, last_pos, status_copy, staged, groups, parts);
 }

@@ -48,9 +48,6 @@ __device__ __forceinline__ double uniform_draw(unsigned long long seed, unsigned
     return (double)(x >> 11) * (1.0 / 9007199254740992.0);
 }
 
-// The vocabulary of a row is cut over ARGMAX_PARTS blocks.  Each folds (key, ~index) pairs into one
-// 64-bit maximum in global memory; the block that takes the row's last ticket writes the token and
-// puts the workspace back to zero for the next launch.
 // The kernels' status word handed on with the tokens: row 0's writer copies it to status_out (the word behind
 // the tokens of a recorded step, which one copy then brings to the host).  Every kernel before this one has
 // finished with the word by then.
@@ -62,6 +59,9 @@ struct StatusCopy {
     }
 };
 
+// The vocabulary of a row is cut over ARGMAX_PARTS blocks.  Each folds (key, ~index) pairs into one
+// 64-bit maximum in global memory; the block that takes the row's last ticket writes the token and
+// puts the workspace back to zero for the next launch.
 constexpr int ARGMAX_THREADS = 256;
 constexpr int ARGMAX_PARTS = 16;
 
@@ -225,8 +225,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     // `parts` > 1: that many blocks (a thread-block cluster along grid.y) share a row for the passes over the
     // whole row: each counts its share into a histogram of its own, every block adds the shares up through
     // distributed shared memory (the same sums in the same order: every block selects the same bin), and the
-    // kept tokens are gathered in block 0, which finishes alone.  Only for a gathered top_k (see below).
+    // kept tokens of a gathered top_k (see below) are collected in block 0, which then finishes alone.
     __shared__ unsigned long long hist[256];
+    __shared__ float max_share;
     __shared__ unsigned long long hist_share[2][256];    // this block's share; two, used in turn, so that a block
                                                          // may start its next pass while others still read this one
     // dynamic shared memory: with `staged` the row's logits (every pass reads them there instead of going to the
@@ -276,8 +277,14 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     };
     if (!gather) {
         float mx = -INFINITY;
-        for_each_logit(v.row, vocab, [&](int, float l) { mx = fmaxf(mx, l); });
-        v.best = block_max(mx) / temperature;
+        for_each_logit(v.row, vocab, [&](int, float l) { mx = fmaxf(mx, l); }, part, parts);
+        mx = block_max(mx);
+        if (parts > 1) {
+            if (tid == 0) max_share = mx;
+            cluster.sync();
+            for (int c = 0; c < parts; ++c) mx = fmaxf(mx, *cluster.map_shared_rank(&max_share, c));
+        }
+        v.best = mx / temperature;
     }
 
     // the k-th largest key, when top_k cuts anything
@@ -367,11 +374,12 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
         v.best = block_max(mx) / temperature;
     }
     // f(i, logit) for every kept token of this thread: from the list, or from the row (f checks `kept` itself)
+    const int sharing = gather ? 1 : parts;         // blocks that share what follows (after a gather: block 0 alone)
     auto each_kept = [&](auto f) {
         if (gather) {
             for (int c = tid; c < n_cand; c += SAMPLE_THREADS) f(cand_idx[c], cand_logit[c]);
         } else {
-            for_each_logit(v.row, vocab, f);
+            for_each_logit(v.row, vocab, f, part, parts);
         }
     };
 
@@ -382,7 +390,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     // the key at which the running mass, taken from the largest logit down, passes target
     unsigned int prefix = 0, mask = 0;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        if (tid < 256) hist[tid] = 0;
+        unsigned long long* share = sharing > 1 ? hist_share[(shift >> 3) & 1] : hist;
+        if (tid < 256) share[tid] = 0;
         __syncthreads();
         if (shift == 24 && private_ok) {
             zero_private(priv, groups);
@@ -397,7 +406,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
                 atomicAdd(word + 1, (unsigned int)(w >> LIMB_BITS));
             });
             __syncthreads();
-            fold_private(priv, groups, hist);
+            fold_private(priv, groups, share);
         } else {
             int cur = -1;
             unsigned long long run = 0;
@@ -407,11 +416,19 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
                 const int bin = (int)((key >> shift) & 255u);
                 const unsigned long long w = v.mass(l);
                 if (bin == cur) { run += w; return; }
-                if (cur >= 0) atomicAdd(&hist[cur], run);
+                if (cur >= 0) atomicAdd(&share[cur], run);
                 cur = bin;
                 run = w;
             });
-            if (cur >= 0) atomicAdd(&hist[cur], run);
+            if (cur >= 0) atomicAdd(&share[cur], run);
+        }
+        if (sharing > 1) {
+            cluster.sync();                            // every block's share is complete
+            if (tid < 256) {
+                unsigned long long sum = 0;
+                for (int c = 0; c < sharing; ++c) sum += *cluster.map_shared_rank(&share[tid], c);
+                hist[tid] = sum;
+            }
         }
         __syncthreads();
         if (shift == 24) {
@@ -475,8 +492,16 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     }
     (void)group_mass;
     __syncthreads();
+    int picked = found_idx;
+    if (sharing > 1) {
+        cluster.sync();                                // every block's smallest index is in place
+        if (nth == 0)
+            for (int c = 0; c < sharing; ++c) picked = min(picked, *cluster.map_shared_rank(&found_idx, c));
+        cluster.sync();                                // nobody leaves while another may read its shared memory
+        if (part != 0) return;
+    }
     if (tid == 0) {
-        const int token = found_idx < vocab ? found_idx : 0;
+        const int token = picked < vocab ? picked : 0;
         out[r] = token;
         draw_index[r] += 1;
         if (feed_ids) feed_ids[r] = token;
@@ -530,13 +555,12 @@ MU_EXPORT int mu_sample(const float* logits, long long ld, int n_rows, int vocab
         raised = true;
     }
     const size_t row_bytes = ((size_t)vocab * 4 + 15) / 16 * 16;
-    // a gathered top_k over a long row: up to eight blocks share the passes over the row
-    const bool gathered = top_k > 0 && top_k < vocab && top_k <= mu::SAMPLE_CANDIDATES;
+    // a long row: up to eight blocks share the passes over it
     // (a block of this kernel has an SM to itself; clusters of eight find their place only while a third of the
     // SMs stay free)
     const int sms = mu::sm_count();
     int parts = 1;
-    if (gathered && vocab >= 16 * mu::SAMPLE_THREADS && sms > 0)
+    if (vocab >= 16 * mu::SAMPLE_THREADS && sms > 0)
         parts = n_rows * 8 <= sms * 2 / 3 ? 8 : n_rows * 4 <= sms * 9 / 10 ? 4 : n_rows * 2 <= sms ? 2 : 1;
     int staged = 0, groups = mu::SAMPLE_WARPS;
     size_t dyn = mu::sample_private_bytes(groups);

@@ -263,13 +263,15 @@ def test_sample_follows_the_plain_rule(vocab, top_k, temperature):
     assert out.cpu().tolist() == first + [0] and fed.cpu().tolist() == first
 
 
+@pytest.mark.parametrize("top_k", [40, 0, 2000])
 @pytest.mark.parametrize("rows", [3, 40, 70, 150])
-def test_sample_with_blocks_sharing_a_row(rows):
-    """With a top_k that is gathered, 8, 4, 2 or 1 blocks share a row's passes, by how many rows there are: the
-    token must not depend on it (ties at the threshold and among the kept tokens included)."""
+def test_sample_with_blocks_sharing_a_row(rows, top_k):
+    """8, 4, 2 or 1 blocks share a row's passes, by how many rows there are: the token must not depend on it
+    (ties at the threshold and among the kept tokens included).  A top_k of 40 is gathered into a list, 2,000 is
+    not, 0 keeps the whole vocabulary."""
     from math_utils_b200.csrc import ops
     rng = np.random.default_rng(rows)
-    vocab, top_k, temperature = 50257, 40, 0.7
+    vocab, temperature = 50257, 0.7
     x = (rng.standard_normal((rows, vocab)) * 2.5).astype(np.float32)
     x[0, 11] = x[0, 30011] = x[0].max() + 1.0      # tied leaders in different blocks' shares
     x[1, :] = 0.25                                  # everything tied: the threshold cuts by index
@@ -281,7 +283,7 @@ def test_sample_with_blocks_sharing_a_row(rows):
         got = ops.sample(logits, temperature, top_k, 3, req, draws).cpu().tolist()
         for r in range(rows if rows <= 40 else 12):
             u = plain_gpt2.uniform_draw(3, 7 + r, n)
-            want, margin = plain_gpt2.sample_top_k(x[r], temperature, top_k, u)
+            want, margin = plain_gpt2.sample_top_k(x[r], temperature, top_k or -1, u)
             assert got[r] == want or margin < 1e-5, (r, n, got[r], want, margin)
     alone = [ops.sample(logits[r:r + 1].contiguous(), temperature, top_k, 3, req[r:r + 1],
                         torch.ones(1, dtype=torch.int32, device="cuda")).item() for r in range(min(rows, 6))]

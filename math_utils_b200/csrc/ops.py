@@ -73,6 +73,9 @@ _SIGNATURES = {
     "mu_layernorm_gemm_tc": [_c_p, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                              _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_p],
     "mu_argmax": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p],
+    "mu_gemm_stream_fits": [_c_int, _c_int, _c_ll, _c_int],
+    "mu_gemm_stream": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
+                       _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_p],
     "mu_gemm_skinny_ln": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                           _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p],
     "mu_attention_decode": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int,
@@ -318,7 +321,8 @@ def _split_workspace(device) -> None:
 
 _WAITS = {1: "tensor-core product: loads", 2: "tensor-core product: tensor cores",
           3: "tensor-core product: epilogue", 4: "single-token attention: a page copy",
-          5: "prompt attention: loads", 6: "prompt attention: tensor cores", 7: "prompt attention: softmax"}
+          5: "prompt attention: loads", 6: "prompt attention: tensor cores", 7: "prompt attention: softmax",
+          8: "streamed product: a weight copy"}
 
 
 def raise_status(device, code: int) -> None:
@@ -532,6 +536,40 @@ def gemm_skinny_ln(x: NormedInput, w: torch.Tensor, bias, act, residual, out, ou
         _ptr(residual), _ptr(out), m, n, k, w.stride(0), out.stride(0),
         residual.stride(0) if residual is not None else 0, ACT_CODES[act], _is_bf16(out), _stream()),
         ("gemm_skinny_ln({}x{}x{})", m, n, k))
+    return out
+
+
+def _stream_kernel(m: int, n: int, k: int, ldw: int, with_norm: bool, device) -> bool:
+    """Whether a product of up to 16 rows goes to ``mu_gemm_stream``: very many output columns (an output head:
+    what the few-rows kernel would run as blocks of 128 columns each), weight rows one after another, and a k
+    short enough for two tiles of 64 weight rows to share an SM's shared memory."""
+    return (m <= 16 and n >= 256 * sm_count(device)
+            and bool(library().mu_gemm_stream_fits(int(m), int(k), int(ldw), 1 if with_norm else 0)))
+
+
+def gemm_stream(x, w: torch.Tensor, bias=None, act=None, out=None, out_dtype=None) -> torch.Tensor:
+    """act(x @ w^T + bias) for up to 16 rows and very many output columns, the weights streamed through shared
+    memory by bulk copies.  ``x``: bfloat16 [m, k], or a ``NormedInput`` (the norm is made inside the kernel)."""
+    normed = isinstance(x, NormedInput)
+    if normed:
+        _need_cuda(x.x, w, bias, out, x.rows)
+        m, k = x.n_rows, x.x.shape[1]
+    else:
+        _need_cuda(x, w, bias, out)
+        m, k = x.shape
+    n = w.shape[0]
+    if w.dtype != torch.bfloat16 or w.shape[1] != k or w.stride(1) != 1:
+        raise KernelError("gemm_stream needs bfloat16 weights [n, k] with unit stride along k")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or w.dtype, device=w.device)
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != n):
+        raise KernelError("gemm bias must be float32 of length n")
+    _check(library().mu_gemm_stream(
+        None if normed else _ptr(x), 0 if normed else x.stride(0),
+        _ptr(x.x) if normed else None, x.x.stride(0) if normed else 0, _ptr(x.rows) if normed else None,
+        _ptr(x.gamma) if normed else None, _ptr(x.beta) if normed else None, float(x.eps) if normed else 0.0,
+        _ptr(w), _ptr(bias), _ptr(out), m, n, k, w.stride(0), out.stride(0), ACT_CODES[act], _is_bf16(out),
+        _ptr(status_word(w.device)), _stream()), ("gemm_stream({}x{}x{})", m, n, k))
     return out
 
 
@@ -768,6 +806,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 16 and fits
                 and k_in % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
+            if (residual is None and x.x.stride(0) % 4 == 0 and x.x.data_ptr() % 16 == 0
+                    and _stream_kernel(x.n_rows, weight.shape[0], k_in, weight.stride(0), True, weight.device)):
+                return gemm_stream(x, weight, bias, act, out, out_dtype)      # an output head
             return gemm_skinny_ln(x, weight, bias, act, residual, out, out_dtype)
         fused = _layernorm_gemm_tc(x, weight, bias, act, residual, out, out_dtype)
         if fused is not None:

@@ -481,6 +481,50 @@ def test_rows_product(m, n, k, splits):
     assert float(wide[:, :8].abs().sum()) == 0.0 and float(wide[:, 8 + n:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 50257, 768), (1, 50257, 768), (5, 40003, 776), (16, 38000, 384), (3, 70, 64),
+                                   (11, 9001, 520)])
+def test_streamed_product(m, n, k):
+    """The product for an output head (few rows, very many columns): weights through shared memory by bulk
+    copies, tile after tile per block.  With given activations and with the norm made inside; a last tile
+    with fewer rows than a strip, or none in a strip; a k that is no multiple of 32; bias and gelu; a
+    strided output; twice, bit for bit the same."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(m + n + k)
+    a = dev(rng.standard_normal((m, k)), torch.bfloat16)
+    w = dev(rng.standard_normal((n, k)) / math.sqrt(k), torch.bfloat16)
+    bias = dev(rng.standard_normal(n))
+    assert ops.library().mu_gemm_stream_fits(m, k, k, 1) == 1
+    z = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    zb = z + bias.double().cpu().numpy()
+    runs = []
+    for _ in range(2):
+        got = ops.gemm_stream(a, w, None, out_dtype=torch.float32)
+        assert_close(got.cpu().numpy(), z, "float32", "plain product", k=k)
+        act = ops.gemm_stream(a, w, bias, act="gelu_new")
+        assert_close(act.float().cpu().numpy(), plain_gpt2.gelu_new(zb), "bfloat16", "bias, gelu, bfloat16 out")
+        runs.append((got, act))
+    assert torch.equal(runs[0][0], runs[1][0]) and torch.equal(runs[0][1], runs[1][1])
+    # the norm made inside: rows picked out of a larger float32 matrix, a mean far from zero
+    x = (rng.standard_normal((m + 3, k)) * 2 + 4).astype(np.float32)
+    rows = rng.permutation(m + 3)[:m].astype(np.int32)
+    gamma, beta = rng.standard_normal(k).astype(np.float32), rng.standard_normal(k).astype(np.float32)
+    normed = plain_gpt2.layer_norm(x[rows].astype(np.float64), gamma.astype(np.float64), beta.astype(np.float64), 1e-5)
+    as_bf16 = dev(normed, torch.bfloat16).double().cpu().numpy()          # the kernel rounds the normed rows
+    lazy = ops.NormedInput(dev(x), dev(gamma), dev(beta), 1e-5, torch.bfloat16, rows=torch.from_numpy(rows).cuda())
+    wide = torch.zeros((m, n + 9), dtype=torch.float32, device="cuda")
+    ops.gemm_stream(lazy, w, None, out=wide[:, 4:4 + n])
+    # a normed value that lands on a rounding boundary may round the other way: allow for a few such flips per
+    # row on top of the float32 bound (2^-9 of one term among k), as for the few-rows kernel
+    z_normed = as_bf16 @ w.double().cpu().numpy().T
+    rms = np.sqrt((z_normed ** 2).mean())
+    assert np.abs(wide[:, 4:4 + n].cpu().numpy() - z_normed).max() < 1e-5 * rms + 2.0 ** -8 * 4.0 / math.sqrt(k) * 3
+    assert float(wide[:, :4].abs().sum()) == 0.0 and float(wide[:, 4 + n:].abs().sum()) == 0.0
+    ops.check_status()
+    # sizes it does not take are refused, not mangled
+    assert ops.library().mu_gemm_stream_fits(17, k, k, 0) == 0 and ops.library().mu_gemm_stream_fits(m, 4096, 4096, 0) == 0
+    assert ops.library().mu_gemm_stream_fits(m, k, k + 8, 0) == 0
+
+
 @pytest.mark.parametrize("m,n,k", [(64, 2304, 768), (64, 768, 3072), (40, 770, 1600), (128, 264, 2048), (200, 72, 520),
                                    (33, 50, 256)])
 @pytest.mark.parametrize("parts", [-1, 2, 5, 64])

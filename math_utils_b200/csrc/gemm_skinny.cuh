@@ -347,6 +347,17 @@ static int launch_skinny_as(const __nv_bfloat16* A, const __nv_bfloat16* W, cons
             }
         }
     }
+    {
+        // Half of an SM's memory as shared memory for these kernels.  Left to itself the driver picks the
+        // smallest split a block fits in, which differs from kernel to kernel, and an SM changes its split
+        // only when it is empty: the blocks of the next kernel then cannot move in beside the last blocks of
+        // this one.  (All of it as shared memory costs more in the L1 than it gains.)
+        static bool asked = false;
+        if (!asked) {
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 50);
+            asked = true;
+        }
+    }
     int blocks = (N + 16 * WN - 1) / (16 * WN);
     if (CK == 1) {
         // more tiles than blocks are resident at once: that many blocks, each walking over its tiles (it norms

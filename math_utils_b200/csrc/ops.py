@@ -623,8 +623,9 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         _i32(t, name)
     n_tokens = q.shape[0]
     if decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens, n_heads, n_kv_heads, head_dim):
-        if not warps:         # many blocks: small ones, three to an SM; few blocks: all pages in flight at once
-            warps = 2 if n_tokens * n_kv_heads >= 2 * sm_count(q.device) else 6
+        if not warps:         # more blocks than SMs: small ones, three to an SM (the large ones, one to an SM,
+                              # would run as two waves); fewer: all pages in flight at once
+            warps = 2 if n_tokens * n_kv_heads > sm_count(q.device) else 6
         _check(library().mu_attention_decode_tc(
             _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
             v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),

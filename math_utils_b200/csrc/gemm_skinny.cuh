@@ -152,7 +152,65 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                      // gamma and beta are in shared memory
         const int n4 = K / 4;
-        for (int m = w; m < MP; m += SK_WARPS) {
+        const bool pairs = MT == 2 && M > SK_WARPS && n4 <= 32 * 8 && (norm.ldx % 4 == 0) && (((uintptr_t)norm.x & 15) == 0);
+        if (pairs) {
+            // sixteen rows, two a warp: both rows are read into registers before either is reduced, so the pair
+            // costs one trip to the L2 (rows of up to 1,024: eight float4 a lane and row)
+            constexpr int LNP = 8;
+            float4 v[2][LNP];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int m = w + h * SK_WARPS;
+                const float4* src4 = reinterpret_cast<const float4*>(
+                    norm.x + (long long)(m < M ? (norm.rows ? norm.rows[m] : m) : 0) * norm.ldx);
+#pragma unroll
+                for (int i = 0; i < LNP; ++i) {
+                    const int idx = ln + 32 * i;
+                    v[h][i] = (m < M && idx < n4) ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+            const float4* g4 = reinterpret_cast<const float4*>(gamma_s);
+            const float4* b4 = reinterpret_cast<const float4*>(beta_s);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int m = w + h * SK_WARPS;
+                __nv_bfloat16* dst = act_smem + (long long)m * act_ld;
+                if (m >= M) {
+                    for (int k = ln * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
+                    continue;
+                }
+                float sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < LNP; ++i) sum += (v[h][i].x + v[h][i].y) + (v[h][i].z + v[h][i].w);
+                const float mean = warp_sum(sum) / (float)K;
+                float sq = 0.0f;
+#pragma unroll
+                for (int i = 0; i < LNP; ++i) {
+                    if (ln + 32 * i < n4) {
+                        const float a = v[h][i].x - mean, b = v[h][i].y - mean, c = v[h][i].z - mean, d = v[h][i].w - mean;
+                        sq += (a * a + b * b) + (c * c + d * d);
+                    }
+                }
+                const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + norm.eps);
+#pragma unroll
+                for (int i = 0; i < LNP; ++i) {
+                    const int idx = ln + 32 * i;
+                    if (idx < n4) {
+                        const float4 gg = g4[idx];
+                        const float4 bb = norm.beta ? b4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        __nv_bfloat162 lo = __floats2bfloat162_rn((v[h][i].x - mean) * inv * gg.x + bb.x,
+                                                                  (v[h][i].y - mean) * inv * gg.y + bb.y);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn((v[h][i].z - mean) * inv * gg.z + bb.z,
+                                                                  (v[h][i].w - mean) * inv * gg.w + bb.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(dst + 4 * idx) = packed;
+                    }
+                }
+            }
+        }
+        for (int m = pairs ? MP : w; m < MP; m += SK_WARPS) {
             __nv_bfloat16* dst = act_smem + (long long)m * act_ld;
             if (m >= M) {
                 for (int k = ln * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);

@@ -38,7 +38,7 @@ MU_EXPORT int mu_gemm_skinny(const void* A, const void* W, const float* bias, co
                            ldw, ldc, ldr, act, out_bf16, nullptr, (cudaStream_t)stream);
 }
 
-// The same product with A = LayerNorm(x[rows]) made inside the kernel, for M <= 16: x float32 [*, K] with
+// The same product with A = LayerNorm(x[rows]) made inside the kernel, for M <= 32: x float32 [*, K] with
 // leading dimension ldx, rows optional int32 [M], gamma and beta (optional) float32 [K].
 MU_EXPORT int mu_gemm_skinny_ln(const float* x, long long ldx, const int* rows, const float* gamma,
                                 const float* beta, float eps, const void* W, const float* bias,
@@ -46,7 +46,7 @@ MU_EXPORT int mu_gemm_skinny_ln(const float* x, long long ldx, const int* rows, 
                                 long long ldc, long long ldr, int act, int out_bf16, void* stream) {
     if (M <= 0 || N <= 0) return MU_OK;
     if (K <= 0 || !x || !gamma || !W || !C) return MU_ERR_BAD_ARGUMENT;
-    if (M > 16) return MU_ERR_UNSUPPORTED_SIZE;
+    if (M > 32) return MU_ERR_UNSUPPORTED_SIZE;
     if (K % 8 != 0 || ldw % 8 != 0) return MU_ERR_ALIGNMENT;
     if ((uintptr_t)W & 15) return MU_ERR_ALIGNMENT;
     if (ldx < K || ldw < K || ldc < N || (residual && ldr < N)) return MU_ERR_BAD_ARGUMENT;

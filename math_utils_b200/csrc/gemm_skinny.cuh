@@ -152,28 +152,32 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                      // gamma and beta are in shared memory
         const int n4 = K / 4;
-        const bool pairs = MT == 2 && M > SK_WARPS && n4 <= 32 * 8 && (norm.ldx % 4 == 0) && (((uintptr_t)norm.x & 15) == 0);
+        const bool pairs = MT >= 2 && n4 <= 32 * 8 && (norm.ldx % 4 == 0) && (((uintptr_t)norm.x & 15) == 0);
         if (pairs) {
-            // sixteen rows, two a warp: both rows are read into registers before either is reduced, so the pair
-            // costs one trip to the L2 (rows of up to 1,024: eight float4 a lane and row)
+            // more than eight rows, MT a warp: two rows at a time are read into registers before either is
+            // reduced, so a pair costs one trip to the L2 (rows of up to 1,024: eight float4 a lane and row)
             constexpr int LNP = 8;
-            float4 v[2][LNP];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int m = w + h * SK_WARPS;
-                const float4* src4 = reinterpret_cast<const float4*>(
-                    norm.x + (long long)(m < M ? (norm.rows ? norm.rows[m] : m) : 0) * norm.ldx);
-#pragma unroll
-                for (int i = 0; i < LNP; ++i) {
-                    const int idx = ln + 32 * i;
-                    v[h][i] = (m < M && idx < n4) ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                }
-            }
             const float4* g4 = reinterpret_cast<const float4*>(gamma_s);
             const float4* b4 = reinterpret_cast<const float4*>(beta_s);
 #pragma unroll
+            for (int h0 = 0; h0 < MT; h0 += 2) {
+            float4 v[2][LNP];
+#pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int m = w + h * SK_WARPS;
+                const int m = w + (h0 + h) * SK_WARPS;
+                const bool real = h0 + h < MT && m < M;
+                const float4* src4 = reinterpret_cast<const float4*>(
+                    norm.x + (long long)(real ? (norm.rows ? norm.rows[m] : m) : 0) * norm.ldx);
+#pragma unroll
+                for (int i = 0; i < LNP; ++i) {
+                    const int idx = ln + 32 * i;
+                    v[h][i] = (real && idx < n4) ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (h0 + h >= MT) continue;
+                const int m = w + (h0 + h) * SK_WARPS;
                 __nv_bfloat16* dst = act_smem + (long long)m * act_ld;
                 if (m >= M) {
                     for (int k = ln * 8; k < K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
@@ -208,6 +212,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                         *reinterpret_cast<uint2*>(dst + 4 * idx) = packed;
                     }
                 }
+            }
             }
         }
         for (int m = pairs ? MP : w; m < MP; m += SK_WARPS) {
@@ -475,7 +480,7 @@ int skinny_rows(const __nv_bfloat16* a, const __nv_bfloat16* w, const float* bia
         if (mt <= 2) return launch_skinny<2, TC, LN>(MU_SKINNY_ARGS);                                        \
         if constexpr (MAX_MT > 2) {                                                                          \
             if (mt <= 4) return launch_skinny<4, TC, LN>(MU_SKINNY_ARGS);                                    \
-            return launch_skinny<8, TC, LN>(MU_SKINNY_ARGS);                                                 \
+            if constexpr (MAX_MT > 4) return launch_skinny<8, TC, LN>(MU_SKINNY_ARGS);                       \
         }                                                                                                    \
         return MU_ERR_UNSUPPORTED_SIZE;                                                                      \
     }

@@ -2,5 +2,5 @@
 #include "gemm_skinny.cuh"
 
 namespace mu {
-MU_SKINNY_ROWS(float, true, 2)
+MU_SKINNY_ROWS(float, true, 4)
 }  // namespace mu

@@ -802,9 +802,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         x = x.materialize()          # a very wide product: the norm as a launch of its own costs less than it saves
     if isinstance(x, NormedInput):
         k_in = x.x.shape[1]
-        # the few-rows kernel keeps the normed rows (8 or 16 of them), gamma and beta in shared memory
-        fits = 8 * (1 if x.n_rows <= 8 else 2) * (k_in + 8) * 2 + 8 * k_in <= SKINNY_LN_SMEM
-        if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 16 and fits
+        # the few-rows kernel keeps the normed rows (8, 16 or 32 of them), gamma and beta in shared memory
+        fits = 8 * (1 if x.n_rows <= 8 else 2 if x.n_rows <= 16 else 4) * (k_in + 8) * 2 + 8 * k_in <= SKINNY_LN_SMEM
+        if (weight.dtype == torch.bfloat16 and x.out_dtype == torch.bfloat16 and x.n_rows <= 32 and fits
                 and k_in % 8 == 0 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
                 and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
             if (residual is None and x.x.stride(0) % 4 == 0 and x.x.data_ptr() % 16 == 0

@@ -390,7 +390,8 @@ def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, w
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 50, 24), (8, 2304, 768), (13, 77, 40), (16, 1031, 96), (3, 130, 1600),
-                                   (12, 130, 8192), (5, 72, 4096)])
+                                   (12, 130, 8192), (5, 72, 4096), (24, 2304, 768), (32, 3072, 768), (17, 130, 1600),
+                                   (29, 77, 40), (20, 768, 1024)])
 @pytest.mark.parametrize("act", [None, "gelu_new"])
 def test_product_with_the_norm_inside(m, n, k, act):
     """LayerNorm folded into the few-rows product against norm-then-product; rows too wide for the

@@ -14,6 +14,18 @@
 // so the sums do not depend on the order threads arrive in and a (seed,
 // request, draw index) always gives the same token.
 //
+// How the passes over a row are kept short (sample_kernel):
+//   * eight logits are asked for before any is used (for_each_logit);
+//   * the first pass of a descent, whose bins are the keys' sign and exponent,
+//     adds into a histogram per warp, in 32-bit words (zero_private / fold_private);
+//   * the total mass is the sum of the first mass histogram, not a pass of its own;
+//   * a top_k of up to SAMPLE_CANDIDATES: the kept tokens are gathered into shared
+//     memory once the threshold is known, and the second descent and the pick walk
+//     that list;
+//   * up to eight blocks (a thread-block cluster, fewer as the rows grow) share a
+//     row's passes: each counts its share, every block adds the shares up through
+//     distributed shared memory in rank order and selects the same bin.
+//
 // u comes from a counter-based stream per request: key = splitmix64(seed ^
 // request * 0x9E3779B97F4A7C15), x = splitmix64(key + n * 0xD1B54A32D192ED03),
 // u = (x >> 11) * 2^-53 (splitmix64 and the 53-bit mantissa rule as in

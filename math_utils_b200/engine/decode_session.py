@@ -253,9 +253,15 @@ class DecodeSession:
         ops = self.model.runtime.ops
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
+        # One memory pool for every graph of this model: what a session's recording allocated goes back there
+        # when the session is dropped and serves the next recording.  (A pool per graph keeps its memory
+        # reserved after the graph is gone: a process that keeps meeting new batch shapes would run out.)
+        pool = self.model.__dict__.get("_graph_pool")
+        if pool is None:
+            pool = self.model.__dict__["_graph_pool"] = torch.cuda.graph_pool_handle()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            graph.capture_begin()
+            graph.capture_begin(pool=pool)
             try:
                 body()
             finally:

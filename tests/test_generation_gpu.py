@@ -101,6 +101,33 @@ def test_conversation_keeps_its_cache(model_dirs, plain_models):
     assert llm.prompt([3, 1, 4]) == first
 
 
+def test_new_batch_shapes_do_not_pile_up_memory(model_dirs):
+    """Every new (cache, batch size, sampling rule) records graphs of its own and the oldest are dropped: what
+    they held must serve the next recordings (one memory pool for all of a model's graphs), not stay reserved
+    by the allocator until the device is full."""
+    import torch
+    from math_utils_b200 import LLM, Options
+    from math_utils_b200.engine.generate import generate
+    from math_utils_b200.sampling import SamplingParams
+    llm = LLM(model_dirs["tiny_b"], Options(dtype="bfloat16", temperature=0.0))
+    rng = np.random.default_rng(0)
+    vocab = llm.model.vocab_size
+
+    def some_calls(first_seed, count):
+        for seed in range(first_seed, first_seed + count):
+            n = int(rng.integers(1, 7))
+            prompts = [rng.integers(0, vocab, size=int(rng.integers(1, 30))).tolist() for _ in range(n)]
+            generate(llm.model, prompts, 5, SamplingParams(temperature=0.9, top_k=-1, seed=seed), stop_ids=[])
+
+    some_calls(0, 30)                                   # more than the sessions that are kept: the first are gone
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_reserved()
+    some_calls(100, 60)
+    torch.cuda.synchronize()
+    assert llm.model.__dict__.get("_graph_pool") is not None
+    assert torch.cuda.memory_reserved() - before < 64 * 2 ** 20, "recorded graphs that were dropped keep their memory"
+
+
 def test_a_given_up_wait_stops_generation(model_dirs, monkeypatch):
     """Kernels with bounded waits report a wait that ran out through a status word.  The word is set by
     hand here (nothing faults): the loop must raise where it next reads samples, give its slots back,

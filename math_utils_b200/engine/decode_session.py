@@ -258,7 +258,19 @@ class DecodeSession:
         # reserved after the graph is gone: a process that keeps meeting new batch shapes would run out.)
         pool = self.model.__dict__.get("_graph_pool")
         if pool is None:
-            pool = self.model.__dict__["_graph_pool"] = torch.cuda.graph_pool_handle()
+            # the pool lives as long as a graph recorded into it does: a graph of one small fill, kept with the
+            # model, holds it when every session has been dropped (a pool without a graph may not be used again)
+            pool = torch.cuda.graph_pool_handle()
+            keeper = torch.cuda.CUDAGraph()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                keeper.capture_begin(pool=pool)
+                try:
+                    held = torch.zeros(16, dtype=torch.int32, device=self.model.runtime.device)
+                finally:
+                    keeper.capture_end()
+            self.model.__dict__["_graph_pool_keeper"] = (keeper, held)
+            self.model.__dict__["_graph_pool"] = pool
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             graph.capture_begin(pool=pool)

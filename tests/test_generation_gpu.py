@@ -126,6 +126,11 @@ def test_new_batch_shapes_do_not_pile_up_memory(model_dirs):
     torch.cuda.synchronize()
     assert llm.model.__dict__.get("_graph_pool") is not None
     assert torch.cuda.memory_reserved() - before < 64 * 2 ** 20, "recorded graphs that were dropped keep their memory"
+    # with every session gone the pool must still take the next recording
+    llm.model.__dict__.pop("_decode_sessions")
+    import gc
+    gc.collect()
+    some_calls(500, 3)
 
 
 def test_a_given_up_wait_stops_generation(model_dirs, monkeypatch):

@@ -105,12 +105,18 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """The parts of one layer and the arrangement that wires them."""
+    """The parts of one layer and the arrangement that wires them.
+
+    ``extra``: further parts for an arrangement that wants more than the four
+    (a third norm, a gate): ``(name, role, PartSpec)`` each, built like the
+    others and handed to the arrangement as ``layer.extra[name]``.  The cache
+    of a layer is its ``mixer``'s; an extra part keeps no cache."""
     arrangement: str
     norm1: PartSpec
     mixer: PartSpec
     norm2: PartSpec
     feed_forward: PartSpec
+    extra: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -144,6 +150,14 @@ class ModelPlan:
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("a model needs at least one layer")
+        for n, layer in enumerate(self.layers):
+            names = [item[0] for item in getattr(layer, "extra", ())]
+            for item in getattr(layer, "extra", ()):
+                if len(item) != 3 or not isinstance(item[2], PartSpec):
+                    raise ConfigError(f"layer {n}: an extra part is (name, role, PartSpec), got {item!r}")
+            taken = [x for x in names if x in ("norm1", "mixer", "norm2", "feed_forward") or names.count(x) > 1]
+            if taken:
+                raise ConfigError(f"layer {n}: the extra part name '{taken[0]}' is taken")
         for i, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ConfigError(f"schedule[{i}] names layer {entry.layer}, model has {len(self.layers)}")

@@ -93,6 +93,21 @@ def test_schedule_validation():
         replace(plan, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 0), ScheduleEntry(1, 1))).validate()
 
 
+def test_extra_parts_of_a_layer_are_checked():
+    """A layer may carry parts beyond the four; their names are its own and each is (name, role, PartSpec)."""
+    from dataclasses import replace
+    plan = Gpt2Config.from_json(TINY_A).plan()
+    first = plan.layers[0]
+    third = ("norm3", "norm", first.norm1)
+    replace(plan, layers=(replace(first, extra=(third,)),) + plan.layers[1:]).validate()
+    with pytest.raises(ConfigError, match="is taken"):
+        replace(plan, layers=(replace(first, extra=(("mixer", "norm", first.norm1),)),) + plan.layers[1:]).validate()
+    with pytest.raises(ConfigError, match="is taken"):
+        replace(plan, layers=(replace(first, extra=(third, third)),) + plan.layers[1:]).validate()
+    with pytest.raises(ConfigError, match="an extra part is"):
+        replace(plan, layers=(replace(first, extra=(("norm3", first.norm1),)),) + plan.layers[1:]).validate()
+
+
 def test_stop_ids_of_generation_config_are_added(tmp_path):
     """eos_token_id of generation_config.json joins config.json's (include/ai/LocalModel.hpp:1788-1792)."""
     import json

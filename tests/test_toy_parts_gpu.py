@@ -13,7 +13,8 @@ import plain_gpt2
 from helpers import check_logits, run_batch, run_tail_one_by_one, run_whole
 from math_utils_b200 import DecoderModel, LLM, Options, register_architecture, write_random_model
 from math_utils_b200.config import Architecture, LayerSpec, ModelPlan, PartSpec, default_schedule
-from math_utils_b200.parts import Embedding, FeedForward, Linear, PositionEncoding, TensorSpec, register_part
+from math_utils_b200.parts import (Arrangement, Embedding, FeedForward, Linear, PositionEncoding, TensorSpec,
+                                   register_part)
 
 pytestmark = pytest.mark.gpu
 
@@ -227,3 +228,81 @@ def test_toy_model_generates_through_the_front_door(toy2):
         for tok in g:
             assert tok == int(np.argmax(toy2_plain(ids, raw, w)[-1]))
             ids.append(tok)
+
+
+# ------------------------------------------------------------------ a layer with a part beyond the four
+class ToySandwich(Arrangement):
+    """x += mixer(norm1(x)); x += norm3(feed_forward(norm2(x))): a third norm, on the feed-forward's way back
+    into the residual stream, which the layer carries as an extra part."""
+
+    def forward(self, x, layer, ctx, cache, owns_cache):
+        layer.mixer.forward(layer.norm1.forward(x), x, ctx, cache, owns_cache)
+        branch = torch.zeros_like(x)
+        layer.feed_forward.forward(layer.norm2.forward(x), branch, ctx)
+        x += layer.extra["norm3"].forward(branch).float()
+
+
+class ToyConfig3:
+    def __init__(self, raw):
+        self.raw = dict(raw)
+
+    @classmethod
+    def from_json(cls, raw):
+        return cls(raw)
+
+    def to_json(self):
+        return dict(self.raw)
+
+    def init_distribution(self, rule):
+        return {"norm_weight": (1.0, 0.05)}.get(rule, (0.0, 0.1))
+
+    def plan(self):
+        r = self.raw
+        d, heads = r["width"], r["heads"]
+
+        def norm(name):
+            return PartSpec("layer_norm", {"size": d, "eps": 1e-5}, {"weight": name + ".w", "bias": name + ".b"})
+
+        attn = PartSpec("causal_attention", {"hidden_size": d, "n_heads": heads, "n_kv_heads": heads, "head_dim": d // heads,
+                                             "softmax_scale": (d // heads) ** -0.5, "window": 0},
+                        {"qkv_weight": "qkv.w", "qkv_bias": "qkv.b", "out_weight": "o.w", "out_bias": "o.b"})
+        ffn = PartSpec("dense_ffn", {"hidden_size": d, "inner_size": r["inner"], "activation": "gelu_new"},
+                       {"up_weight": "up.w", "up_bias": "up.b", "down_weight": "down.w", "down_bias": "down.b"})
+        layer = LayerSpec("toy_sandwich", norm("n1"), attn, norm("n2"), ffn, extra=(("norm3", "norm", norm("n3")),))
+        return ModelPlan("ToyModel3", r["vocab"], d, r["positions"],
+                         PartSpec("token_embedding", {"vocab_size": r["vocab"], "hidden_size": d}, {"weight": "emb"}),
+                         PartSpec("learned_absolute", {"max_positions": r["positions"], "hidden_size": d}, {"weight": "pos"}),
+                         (layer,), default_schedule(1), norm("final"),
+                         PartSpec("tied_head", {"vocab_size": r["vocab"], "hidden_size": d}))
+
+
+def test_layer_with_an_extra_part(tmp_path):
+    """A third norm in a layer: declared in the plan's LayerSpec, built, loaded and handed to the arrangement by
+    name, with no change to the package."""
+    register_part("arrangement", "toy_sandwich", ToySandwich, replace=True)
+    register_architecture(Architecture(names=("toy3", "ToyModel3"), config_class=ToyConfig3), replace=True)
+    raw = {"model_type": "toy3", "width": 48, "heads": 3, "inner": 72, "vocab": 97, "positions": 90}
+    write_random_model(str(tmp_path), raw, seed=9)
+    w = plain_gpt2.read_safetensors(str(tmp_path / "model.safetensors"))
+    assert "n3.w" in w and "n3.b" in w
+
+    def plain(ids):
+        n = len(ids)
+        x = w["emb"][ids] + w["pos"][:n]
+        h = plain_gpt2.layer_norm(x, w["n1.w"], w["n1.b"], 1e-5)
+        qkv = h @ w["qkv.w"].T + w["qkv.b"]
+        a = plain_gpt2.causal_attention(qkv[:, :48], qkv[:, 48:96], qkv[:, 96:], 3, 3, 16 ** -0.5, 0)
+        x = x + a @ w["o.w"].T + w["o.b"]
+        h = plain_gpt2.layer_norm(x, w["n2.w"], w["n2.b"], 1e-5)
+        y = plain_gpt2.gelu_new(h @ w["up.w"].T + w["up.b"]) @ w["down.w"].T + w["down.b"]
+        x = x + plain_gpt2.layer_norm(y, w["n3.w"], w["n3.b"], 1e-5)
+        return plain_gpt2.layer_norm(x, w["final.w"], w["final.b"], 1e-5) @ w["emb"].T
+
+    model = DecoderModel.from_dir(str(tmp_path), dtype="float32")
+    cache = model.new_cache(max_tokens=256, n_slots=3)
+    rng = np.random.default_rng(4)
+    reqs = [rng.integers(0, 97, size=n).tolist() for n in (70, 9, 33)]
+    check_logits(run_whole(model, cache, reqs[0]), plain(reqs[0]), "float32", "toy3 whole")
+    check_logits(run_tail_one_by_one(model, cache, reqs[0], 20), plain(reqs[0]), "float32", "toy3 tail")
+    for g, r in zip(run_batch(model, cache, reqs, [40, 9, 1]), reqs):
+        check_logits(g, plain(r), "float32", "toy3 batch")

@@ -24,12 +24,9 @@ class LayerNorm(Norm):
     def forward(self, x, rows=None):
         return self.runtime.ops.layernorm(x, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)
 
+    def lazy(self, x, rows=None):
+        """Not computed yet: the product kernels know this norm and make it while they load their rows."""
+        return self.runtime.ops.NormedInput(x, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)
+
 
 register_part("norm", "layer_norm", LayerNorm, replace=True)
-
-
-def _lazy(self, x, rows=None):
-    return self.runtime.ops.NormedInput(x, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)
-
-
-LayerNorm.lazy = _lazy

@@ -79,23 +79,35 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, flo
 // MANY: the instantiation for the many rows of a prompt step (it prefers shared memory over L1 like the
 // kernels around it there, see prefer_shared_memory); the code is the same.
 template <typename TO, bool MANY>
-__global__ void __launch_bounds__(LN_WARPS * 32)
+__global__ void __launch_bounds__(LN_WARPS * 32, 4)
 layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                       const float* __restrict__ gamma, const float* __restrict__ beta,
                       TO* __restrict__ y, int n_rows, int hidden, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * LN_WARPS + warp;
+    const int n4 = hidden / 4;
+    // weight and bias are no kernel's output: they are on their way into shared memory while the kernel
+    // before this one still runs, so that nothing is fetched after the statistics
+    __shared__ __align__(16) float gamma_s[32 * LN_V * 4];
+    __shared__ __align__(16) float beta_s[32 * LN_V * 4];
+    for (int idx = threadIdx.x; idx < n4; idx += LN_WARPS * 32) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(gamma_s + 4 * idx)),
+                     "l"(gamma + 4 * idx) : "memory");
+        if (beta)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(beta_s + 4 * idx)),
+                         "l"(beta + 4 * idx) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     pdl_trigger();
     pdl_wait();
-    if (r >= n_rows) return;
-    const long long src_row = rows ? rows[r] : r;
+    const bool real = r < n_rows;
+    const long long src_row = real ? (rows ? rows[r] : r) : 0;
     const float4* src4 = reinterpret_cast<const float4*>(x + src_row * hidden);
-    const int n4 = hidden / 4;
     float4 v[LN_V];
 #pragma unroll
     for (int i = 0; i < LN_V; ++i) {
         const int idx = lane + 32 * i;
-        v[i] = idx < n4 ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        v[i] = (real && idx < n4) ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     float sum = 0.0f;
 #pragma unroll
@@ -110,8 +122,11 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
         }
     }
     const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)hidden + eps);
-    const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (!real) return;
+    const float4* g4 = reinterpret_cast<const float4*>(gamma_s);
+    const float4* b4 = reinterpret_cast<const float4*>(beta_s);
     TO* dst = y + (long long)r * hidden;
 #pragma unroll
     for (int i = 0; i < LN_V; ++i) {

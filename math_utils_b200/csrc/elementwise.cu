@@ -195,29 +195,6 @@ MU_EXPORT int mu_layernorm(const float* x, const int* rows, const float* gamma, 
     return MU_OK;
 }
 
-namespace mu {
-__global__ void advance_kernel(int* __restrict__ token_ids, int* __restrict__ tok_pos,
-                               const int* __restrict__ next_tokens, int n, int last_pos) {
-    pdl_trigger();
-    pdl_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    token_ids[i] = next_tokens[i];
-    const int p = tok_pos[i] + 1;
-    tok_pos[i] = p < last_pos ? p : last_pos;
-}
-}  // namespace mu
-
-// After a single-token step: the sampled tokens become the next step's inputs and every
-// position moves on by one (never past last_pos, the last position the cache can hold).
-MU_EXPORT int mu_advance(int* token_ids, int* tok_pos, const int* next_tokens, int n, int last_pos,
-                         void* stream) {
-    if (n <= 0) return MU_OK;
-    if (!token_ids || !tok_pos || !next_tokens) return MU_ERR_BAD_ARGUMENT;
-    return mu::launch_pdl(mu::advance_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, 1,
-                          token_ids, tok_pos, next_tokens, n, last_pos);
-}
-
 // Turns programmatic dependent launch of the single-token kernels on (1, the default) or off (0).
 MU_EXPORT int mu_set_pdl(int enabled) {
     mu::pdl_enabled() = enabled ? 1 : 0;

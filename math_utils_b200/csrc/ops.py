@@ -64,7 +64,6 @@ _SIGNATURES = {
                      _c_int, _c_p, _c_int, _c_p, _c_int, _c_p],
     "mu_attention": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int,
                      _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p],
-    "mu_advance": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p],
     "mu_attention_prefill": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int,
                              _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p],
     "mu_attention_prefill_tc": [_c_p, _c_ll, _c_int, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_p, _c_p,
@@ -240,15 +239,6 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor]
     _check(library().mu_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), n, hidden,
                                   float(eps), _is_bf16(out), _stream()), ("layernorm(hidden={})", hidden))
     return out
-
-
-def advance(token_ids: torch.Tensor, tok_pos: torch.Tensor, next_tokens: torch.Tensor, last_pos: int) -> None:
-    """token_ids <- next_tokens, tok_pos <- min(tok_pos + 1, last_pos): feeds a
-    single-token step's samples to the next step without leaving the device."""
-    _need_cuda(token_ids, tok_pos, next_tokens)
-    _i32(token_ids, "token_ids"); _i32(tok_pos, "tok_pos"); _i32(next_tokens, "next_tokens")
-    _check(library().mu_advance(_ptr(token_ids), _ptr(tok_pos), _ptr(next_tokens), token_ids.numel(),
-                                int(last_pos), _stream()), "advance")
 
 
 # ------------------------------------------------------------------------ GEMM

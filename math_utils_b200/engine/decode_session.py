@@ -11,7 +11,8 @@ Three ways to drive it:
   * ``feed(tokens, positions)`` then ``launch()`` then ``read_tokens()``: the
     host supplies every step's inputs and reads every step's tokens;
   * ``launch()`` repeatedly: each step's samples are the next step's inputs on
-    the device (``advance``), with no host round trip between steps;
+    the device (the sampling kernel hands them over and moves the positions on),
+    with no host round trip between steps;
   * ``pipelined``: ``start(tokens)`` once, then ``launch_step(positions)`` and
     ``read_step(ticket)``: the samples feed the next step on the device, the
     host says at which positions every step runs (it alone knows which

@@ -152,47 +152,59 @@ class StepContext:
 def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts: Sequence[int],
                   ring: PinnedRing, workspace: dict, trace=None, tokens=None) -> StepContext:
     """Packs the step's index arrays and sends them to the device.  ``tokens``: the entries' tokens as
-    integer arrays, if the caller has them already."""
-    q_lens = [len(e.tokens) for e in entries]
-    n_tokens, n_seqs = sum(q_lens), len(entries)
-    n_want = sum(len(e.want) for e in entries)
-    tables = [cache.block_table_rows(g.index, [e.slot for e in entries]) for g in cache.kv_groups]
+    integer arrays, if the caller has them already.  Everything here is array arithmetic over the step's
+    sequences: the device waits while it runs."""
+    if tokens is None:
+        tokens = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+    n_seqs = len(entries)
+    q_lens = [int(t.shape[0]) for t in tokens]
+    lens = np.asarray(q_lens, dtype=np.int64)
+    first = np.asarray(starts, dtype=np.int64)                 # each sequence's length before this step
+    flat0 = np.cumsum(lens) - lens                             # where each sequence begins in the flat token list
+    n_tokens = sum(q_lens)
+    slots = [e.slot for e in entries]
+    tables = [cache.block_table_rows(g.index, slots) for g in cache.kv_groups]
+    want = []
+    for s, e in enumerate(entries):
+        if len(e.want):
+            base, n = int(flat0[s]), q_lens[s]
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"want index {w} is outside the {n} tokens given for slot {e.slot}")
+                want.append(base + w)
+    n_want = len(want)
+
     def cut(width):
         """Query tiles of `width` tokens, none across two sequences, those with the most keys first
-        (the attention kernels' blocks take them in this order)."""
-        found, ends, flat = [], [], 0
-        for n, start in zip(q_lens, starts):
-            for o in range(0, n, width):
-                found.append((flat + o, min(width, n - o)))
-                ends.append(start + o + found[-1][1])
-            flat += n
-        return [found[i] for i in sorted(range(len(found)), key=lambda i: -ends[i])]
+        (the attention kernels' blocks take them in this order): (first flat token, count) each."""
+        found = []
+        for base, n, start in zip(flat0.tolist(), q_lens, starts):
+            found += [(start + min(o + width, n), base + o, min(width, n - o)) for o in range(0, n, width)]
+        found.sort(key=lambda tile: -tile[0])                  # stable: equal ends keep their order
+        return np.asarray([tile[1:] for tile in found], dtype=np.int32)
 
-    tiles, wide = [], []                  # query tiles for the prompt attention kernels
-    if max(q_lens) > 1:
+    max_q_len = max(q_lens)
+    tiles = wide = None                   # query tiles for the prompt attention kernels
+    if max_q_len > 1:
         tiles, wide = cut(TILE_QUERIES), cut(2 * TILE_QUERIES)
-    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * len(tiles), 2 * len(wide)] + [t.size for t in tables]
-    offsets = np.concatenate([[0], np.cumsum([-(-s // 4) * 4 for s in sizes])])   # 16-byte aligned parts
-    total = int(offsets[-1])
+    n_tiles, n_wide = (len(tiles), len(wide)) if tiles is not None else (0, 0)
+    sizes = [n_tokens, n_tokens, n_tokens, n_want, n_seqs, 2 * n_tiles, 2 * n_wide] + [t.size for t in tables]
+    offsets = [0]
+    for size in sizes:
+        offsets.append(offsets[-1] + -(-size // 4) * 4)       # 16-byte aligned parts
+    total = offsets[-1]
     host = ring.next(total)
     h = host.numpy()
-    o = 0
-    flat = 0
-    for s, e in enumerate(entries):
-        n = q_lens[s]
-        h[offsets[0] + flat: offsets[0] + flat + n] = tokens[s] if tokens is not None else np.asarray(e.tokens, dtype=np.int32)
-        h[offsets[1] + flat: offsets[1] + flat + n] = np.arange(starts[s], starts[s] + n, dtype=np.int32)
-        h[offsets[2] + flat: offsets[2] + flat + n] = s
-        for w in e.want:
-            if not 0 <= w < n:
-                raise ValueError(f"want index {w} is outside the {n} tokens given for slot {e.slot}")
-            h[offsets[3] + o] = flat + w
-            o += 1
-        flat += n
-    h[offsets[4]: offsets[4] + n_seqs] = np.asarray([e.slot for e in entries], dtype=np.int32)
-    if tiles:
-        h[offsets[5]: offsets[5] + 2 * len(tiles)] = np.asarray(tiles, dtype=np.int32).reshape(-1)
-        h[offsets[6]: offsets[6] + 2 * len(wide)] = np.asarray(wide, dtype=np.int32).reshape(-1)
+    seq_of = np.repeat(np.arange(n_seqs), lens)
+    h[offsets[0]: offsets[0] + n_tokens] = tokens[0] if n_seqs == 1 else np.concatenate(tokens)
+    h[offsets[1]: offsets[1] + n_tokens] = np.arange(n_tokens) + (first - flat0)[seq_of]
+    h[offsets[2]: offsets[2] + n_tokens] = seq_of
+    if n_want:
+        h[offsets[3]: offsets[3] + n_want] = want
+    h[offsets[4]: offsets[4] + n_seqs] = slots
+    if n_tiles:
+        h[offsets[5]: offsets[5] + 2 * n_tiles] = tiles.reshape(-1)
+        h[offsets[6]: offsets[6] + 2 * n_wide] = wide.reshape(-1)
     for i, t in enumerate(tables):
         h[offsets[7 + i]: offsets[7 + i] + t.size] = t.reshape(-1)
     dev = torch.empty(total, dtype=torch.int32, device=runtime.device)
@@ -208,8 +220,8 @@ def build_context(runtime, position, cache, entries: Sequence[StepEntry], starts
         want_rows=part(3, n_want) if n_want else None,
         block_tables=[part(7 + i, t.size).view(t.shape) for i, t in enumerate(tables)],
         seq_slots=part(4, n_seqs),
-        q_tiles=part(5, 2 * len(tiles)).view(len(tiles), 2) if tiles else None,
-        q_tiles_wide=part(6, 2 * len(wide)).view(len(wide), 2) if wide else None,
-        slots=[e.slot for e in entries], starts=list(starts), q_lens=q_lens,
-        max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
+        q_tiles=part(5, 2 * n_tiles).view(n_tiles, 2) if n_tiles else None,
+        q_tiles_wide=part(6, 2 * n_wide).view(n_wide, 2) if n_wide else None,
+        slots=slots, starts=list(starts), q_lens=q_lens,
+        max_q_len=max_q_len, max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
         workspace=workspace, trace=trace)

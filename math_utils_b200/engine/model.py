@@ -98,10 +98,16 @@ class DecoderModel:
             raise ValueError("a slot appears twice in one step")
         # the tokens once as arrays: checked here, packed for the device by build_context
         tokens = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
-        for ids in tokens:
-            if ids.ndim != 1 or int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
-                bad = [int(t) for t in ids.reshape(-1) if not 0 <= int(t) < self.vocab_size]
-                raise ValueError(f"token id {bad[0] if bad else ids} is outside the vocabulary of {self.vocab_size}")
+        if any(ids.ndim != 1 for ids in tokens):
+            raise ValueError("the tokens of an entry are a flat list of ids")
+        every = tokens[0] if len(tokens) == 1 else np.concatenate(tokens)
+        if int(every.min()) < 0 or int(every.max()) >= self.vocab_size:
+            bad = every[(every < 0) | (every >= self.vocab_size)]
+            raise ValueError(f"token id {int(bad[0])} is outside the vocabulary of {self.vocab_size}")
+        for e, ids in zip(entries, tokens):
+            for w in e.want:
+                if not 0 <= w < ids.shape[0]:
+                    raise ValueError(f"want index {w} is outside the {ids.shape[0]} tokens given for slot {e.slot}")
         starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
         ctx = build_context(self.runtime, self.assembly.position, cache, entries, starts,
                             self._ring, self._workspace, trace, tokens)

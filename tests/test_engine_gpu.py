@@ -148,3 +148,30 @@ def test_stage_trace_matches_plain(dtype, engines, plain_models):
     a = model.step(cache, [StepEntry(slot, tokens[:40], [39])]).cpu().numpy()
     cache.release(slot)
     assert np.array_equal(a, got_prompt["logits"])
+
+
+def test_step_refuses_what_it_cannot_run(engines, plain_models):
+    """A token outside the vocabulary, a wanted place outside the tokens given, a slot named twice: each is an
+    error before anything runs, and the cache holds what it held."""
+    from math_utils_b200 import StepEntry
+    cfg, _ = plain_models["tiny_a"]
+    model = engines("tiny_a", "float32")
+    cache = model.new_cache(max_tokens=256, n_slots=3)
+    a, b = cache.acquire(), cache.acquire()
+    model.step(cache, [StepEntry(a, [1, 2, 3])])
+    free = cache.free_pages(0)
+    with pytest.raises(ValueError, match=f"token id {cfg['vocab_size']} is outside the vocabulary"):
+        model.step(cache, [StepEntry(a, [4]), StepEntry(b, [1, cfg["vocab_size"], 2])])
+    with pytest.raises(ValueError, match="token id -1 is outside"):
+        model.step(cache, [StepEntry(b, [-1])])
+    with pytest.raises(ValueError, match="twice"):
+        model.step(cache, [StepEntry(a, [4]), StepEntry(a, [5])])
+    with pytest.raises(ValueError, match="flat list"):
+        model.step(cache, [StepEntry(b, [[1, 2], [3, 4]])])
+    with pytest.raises(ValueError, match="want index 3"):
+        model.step(cache, [StepEntry(b, [1, 2, 3], [3])])
+    assert cache.length(a) == 3 and cache.length(b) == 0 and cache.free_pages(0) == free
+    out = model.step(cache, [StepEntry(b, [1, 2, 3], [2])])          # the slot still works
+    assert out.shape == (1, cfg["vocab_size"]) and cache.length(b) == 3
+    cache.release(a); cache.release(b)
+    assert cache.slots.n_free == 3 and cache.free_pages(0) == cache.n_pages

@@ -54,8 +54,9 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hidden,eps", [(48, 1e-5), (1000, 1e-6), (1600, 1e-3)])
+@pytest.mark.parametrize("hidden,eps", [(48, 1e-5), (1000, 1e-6), (1600, 1e-3), (2048, 1e-5), (2052, 1e-5), (50, 1e-5)])
 def test_layernorm(hidden, eps, out_dtype):
+    """Widths on both sides of what the warp-per-row kernel takes (a multiple of 4 up to 2,048)."""
     from math_utils_b200.csrc import ops
     rng = np.random.default_rng(1)
     x = (rng.standard_normal((11, hidden)) * 3 + 5).astype(np.float32)     # a mean far from zero
@@ -67,6 +68,26 @@ def test_layernorm(hidden, eps, out_dtype):
     rows = torch.tensor([10, 0, 3], dtype=torch.int32, device="cuda")
     got = ops.layernorm(dev(x), dev(g), dev(b), eps, DT[out_dtype], rows=rows).float().cpu().numpy()
     assert_close(got, want[[10, 0, 3]], out_dtype, "layernorm of picked rows")
+
+
+@pytest.mark.parametrize("n_rows", [1, 5, 64, 301])
+def test_layernorm_row_counts_and_no_bias(n_rows):
+    """Row counts that leave the last block of four rows partly empty, the many-rows variant (more than 64),
+    and a norm without a bias; twice in a row, so that a second launch finds the first one's parameters
+    gone from shared memory and stages its own."""
+    from math_utils_b200.csrc import ops
+    rng = np.random.default_rng(n_rows)
+    hidden = 200
+    x = (rng.standard_normal((n_rows, hidden)) * 2 - 1).astype(np.float32)
+    for trial in range(2):
+        g = rng.standard_normal(hidden).astype(np.float32)
+        b = rng.standard_normal(hidden).astype(np.float32)
+        want = plain_gpt2.layer_norm(x.astype(np.float64), g.astype(np.float64), b.astype(np.float64), 1e-5)
+        got = ops.layernorm(dev(x), dev(g), dev(b), 1e-5, torch.float32).cpu().numpy()
+        assert_close(got, want, "float32", f"layernorm of {n_rows} rows")
+        want = plain_gpt2.layer_norm(x.astype(np.float64), g.astype(np.float64), np.zeros(hidden), 1e-5)
+        got = ops.layernorm(dev(x), dev(g), None, 1e-5, torch.bfloat16).float().cpu().numpy()
+        assert_close(got, want, "bfloat16", f"layernorm of {n_rows} rows without a bias")
 
 
 GEMM_SHAPES = [(1, 50, 24), (13, 77, 40), (64, 96, 320), (130, 257, 136), (5, 1031, 96), (200, 64, 8)]

@@ -372,9 +372,11 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
 
 }  // namespace mu
 
-// Arguments as mu_attention_decode (bfloat16 only).  n_warps 2 (many blocks: three of them share an SM) or
-// 6 (few blocks: all pages in flight at once) groups of warps, each group a ring of pages; `status` is a
-// device word that is set to 4 if a wait for a copy runs out.
+// Arguments as mu_attention_decode (bfloat16 only).  n_warps: how the block is built, by how many blocks there
+// are.  6: six groups of one warp, a block an SM (no more blocks than SMs: all pages of a sequence in flight at
+// once).  3: three groups of two warps that share each page, two blocks an SM (up to twice as many blocks as
+// SMs; head size 64).  2: two groups of two warps, three blocks an SM (more blocks than that).  Each group has
+// a ring of pages.  `status` is a device word that is set to 4 if a wait for a copy runs out.
 MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k_new, long long ldk,
                                      const void* v_new, long long ldv, void* out, long long ldo, void* kv,
                                      const int* block_table, int max_pages, int page_tokens,
@@ -416,12 +418,13 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
     // six groups with their rings and many query heads per kv head may not fit: then two groups do it.  With
     // many blocks (two groups each, three blocks an SM) two warps share each page where the head is small
     // enough for the registers to allow it: more chains of work for the SM to switch between.  With few blocks
-    // a warp per page is the shorter chain.
+    // a warp per page is the shorter chain.  In between, three groups of two warps: a group walks over a
+    // third of the pages instead of half of them, and two blocks still share an SM.
     const size_t six = (size_t)6 * 2 * 2 * mu::TD_PAGE * head_dim * sizeof(__nv_bfloat16) +
                        (size_t)6 * rows * (head_dim + 1) * sizeof(float);
     const bool wide = n_warps >= 6 && six <= 200 * 1024;
     if (head_dim == 32) { if (wide) MU_TR(2, 6, 1); else MU_TR(2, 2, 2); }
-    else if (head_dim == 64) { if (wide) MU_TR(4, 6, 1); else MU_TR(4, 2, 2); }
+    else if (head_dim == 64) { if (wide) MU_TR(4, 6, 1); else if (n_warps >= 3) MU_TR(4, 3, 2); else MU_TR(4, 2, 2); }
     else if (head_dim == 96) MU_TR(6, 2, 1);
     else MU_TR(8, 2, 1);
 #undef MU_TR

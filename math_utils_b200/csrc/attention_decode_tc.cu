@@ -29,9 +29,12 @@
 // to 16 query heads per kv head; pages of 64 positions.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
 #include <math.h>
 
 namespace mu {
+
+namespace cg = cooperative_groups;
 
 constexpr int TD_PAGE = 64;
 
@@ -85,7 +88,13 @@ __device__ __forceinline__ bool td_wait(uint64_t* bar, uint32_t parity) {
 // sequence; its SUB warps share each page, KPW = 64 / SUB keys a warp.  More warps on the same bytes in
 // flight: a warp's work on a page is a chain of dependent steps (fragments in, scores, softmax, weighted
 // values), and an SM hides one chain behind the others only if there are enough of them.
-template <int KD, int NG, int SUB, int RING>
+//
+// CL blocks of a thread-block cluster (grid.y; 1, 2 or 4) may share a (sequence, kv head): with few sequences
+// there are far fewer blocks than SMs, and one SM alone draws a sequence's pages more slowly than several do.
+// The NG * CL groups of the cluster take the pages in turn; every block merges its own warps, the others hand
+// their merged part (maximum, sum, weighted values) to block 0 through distributed shared memory, and block 0
+// merges the parts in rank order and writes the result.
+template <int KD, int NG, int SUB, int RING, int CL>
 __global__ void __launch_bounds__(NG * SUB * 32)
 attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
                              const __nv_bfloat16* __restrict__ k_new, long long ldk,
@@ -112,14 +121,20 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     __shared__ float part_m[NW][16], part_l[NW][16];
     __shared__ float weight[NW][16];
     __shared__ int failed;
+    // with CL > 1: this block's merged maximum per row, and in block 0 what the other blocks hand over
+    __shared__ float blk_m[16];
+    __shared__ float peer_m[CL > 1 ? CL - 1 : 1][16], peer_l[CL > 1 ? CL - 1 : 1][16];
+    __shared__ int cl_failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = warp / SUB, sub = warp % SUB;
     const int g = lane >> 2, t = lane & 3;
     const int tk = blockIdx.x / n_kv_heads, kvh = blockIdx.x % n_kv_heads;
     const int rows = n_heads / n_kv_heads;
+    const int part = CL > 1 ? (int)blockIdx.y : 0;            // the cluster spans grid.y
+    constexpr int LANES = NG * CL;                             // groups that share a sequence's pages
     pdl_trigger();
-    if (threadIdx.x == 0) failed = 0;
+    if (threadIdx.x == 0) { failed = 0; cl_failed = 0; }
     if (lane == 0 && sub == 0) {
 #pragma unroll
         for (int r = 0; r < RING; ++r) {
@@ -129,20 +144,21 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if constexpr (CL > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // set up; waited for before anything is handed over
     const int* pages = block_table + (long long)(tok_seq ? tok_seq[tk] : tk) * max_pages;
     const int pos = tok_pos[tk];
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = first / TD_PAGE, last_page = pos / TD_PAGE;
     const long long head_stride = (long long)PAGE_ELEMS;
-    const int my_first = first_page + group;
-    const int n_mine = my_first <= last_page ? (last_page - my_first) / NG + 1 : 0;
+    const int my_first = first_page + group * CL + part;
+    const int n_mine = my_first <= last_page ? (last_page - my_first) / LANES + 1 : 0;
     __nv_bfloat16* my_ring = ring + (size_t)group * RING * 2 * PAGE_ELEMS;
     const bool issuer = sub == 0 && lane == 0;
 
     // one lane asks for the group's i-th page: two contiguous runs of the cache, one barrier
     auto issue = [&](int i) {
         const int slot = i % RING;
-        const long long page = pages[my_first + i * NG];
+        const long long page = pages[my_first + i * LANES];
         const __nv_bfloat16* ksrc = kv + (page * 2 * n_kv_heads + kvh) * head_stride;
         const __nv_bfloat16* vsrc = ksrc + (long long)n_kv_heads * head_stride;
         const uint32_t bar = td_smem(&full[group][slot]);
@@ -193,7 +209,7 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     bool ok = true;
     for (int i = 0; i < n_mine; ++i) {
         const int slot = i % RING;
-        const int page_idx = my_first + i * NG;
+        const int page_idx = my_first + i * LANES;
         if (!td_wait(&full[group][slot], (uint32_t)((i / RING) & 1))) { ok = false; break; }
         const __nv_bfloat16* ks = my_ring + (size_t)slot * 2 * PAGE_ELEMS;
         const __nv_bfloat16* vs = ks + PAGE_ELEMS;
@@ -349,24 +365,79 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
         part_l[warp][g] = l_run[0]; part_l[warp][g + 8] = l_run[1];
     }
     __syncthreads();
-    if (failed) return;
+    if (CL == 1 && failed) return;
     if (threadIdx.x < NW * 16) {
         const int w = threadIdx.x / 16, r = threadIdx.x % 16;
         float big = -INFINITY;
 #pragma unroll
         for (int x = 0; x < NW; ++x) big = fmaxf(big, part_m[x][r]);
         weight[w][r] = part_m[w][r] == -INFINITY ? 0.0f : exp2f(part_m[w][r] - big);
+        if (w == 0) blk_m[r] = big;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32) {
-        const int r = idx / DH, d = idx % DH;
-        float total = 0.0f, o = 0.0f;
+    if constexpr (CL == 1) {
+        for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32) {
+            const int r = idx / DH, d = idx % DH;
+            float total = 0.0f, o = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            total = fmaf(part_l[w][r], weight[w][r], total);
-            o = fmaf(part_o[(w * rows + r) * (DH + 1) + d], weight[w][r], o);
+            for (int w = 0; w < NW; ++w) {
+                total = fmaf(part_l[w][r], weight[w][r], total);
+                o = fmaf(part_o[(w * rows + r) * (DH + 1) + d], weight[w][r], o);
+            }
+            out[(long long)tk * ldo + (long long)(kvh * rows + r) * DH + d] = __float2bfloat16_rn(o / total);
         }
-        out[(long long)tk * ldo + (long long)(kvh * rows + r) * DH + d] = __float2bfloat16_rn(o / total);
+    } else {
+        // this block's warps merged: (blk_m, total, o) per row, relative to blk_m.  Block 0 keeps its own in
+        // place of warp 0's partials; the others write theirs into block 0's shared memory.
+        float* peer_o = part_o + (size_t)NW * rows * (DH + 1);                  // [CL - 1][rows][DH], used in block 0
+        cg::cluster_group cluster = cg::this_cluster();
+        float* to_o = part == 0 ? nullptr : cluster.map_shared_rank(peer_o, 0) + (size_t)(part - 1) * rows * DH;
+        float* to_m = part == 0 ? nullptr : cluster.map_shared_rank(&peer_m[0][0], 0) + (part - 1) * 16;
+        float* to_l = part == 0 ? nullptr : cluster.map_shared_rank(&peer_l[0][0], 0) + (part - 1) * 16;
+        float mine_o[(16 * DH + NW * 32 - 1) / (NW * 32)], mine_l[(16 * DH + NW * 32 - 1) / (NW * 32)];
+        int n_held = 0;
+        for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32, ++n_held) {
+            const int r = idx / DH, d = idx % DH;
+            float total = 0.0f, o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                total = fmaf(part_l[w][r], weight[w][r], total);
+                o = fmaf(part_o[(w * rows + r) * (DH + 1) + d], weight[w][r], o);
+            }
+            mine_o[n_held] = o;
+            mine_l[n_held] = total;
+        }
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");    // every block of the cluster is set up
+        if (part != 0) {
+            n_held = 0;
+            for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32, ++n_held) {
+                const int r = idx / DH, d = idx % DH;
+                to_o[r * DH + d] = mine_o[n_held];
+                if (d == 0) { to_l[r] = mine_l[n_held]; to_m[r] = blk_m[r]; }
+            }
+            if (failed && threadIdx.x == 0) *cluster.map_shared_rank(&cl_failed, 0) = 1;
+        } else if (failed && threadIdx.x == 0) {
+            cl_failed = 1;
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");    // the parts are in block 0
+        if (part != 0 || cl_failed) return;
+        n_held = 0;
+        for (int idx = threadIdx.x; idx < rows * DH; idx += NW * 32, ++n_held) {
+            const int r = idx / DH, d = idx % DH;
+            float big = blk_m[r];
+#pragma unroll
+            for (int c = 0; c < CL - 1; ++c) big = fmaxf(big, peer_m[c][r]);
+            float wgt = blk_m[r] == -INFINITY ? 0.0f : exp2f(blk_m[r] - big);
+            float total = mine_l[n_held] * wgt, o = mine_o[n_held] * wgt;
+#pragma unroll
+            for (int c = 0; c < CL - 1; ++c) {                                  // in rank order
+                wgt = peer_m[c][r] == -INFINITY ? 0.0f : exp2f(peer_m[c][r] - big);
+                total = fmaf(peer_l[c][r], wgt, total);
+                o = fmaf(peer_o[((size_t)c * rows + r) * DH + d], wgt, o);
+            }
+            out[(long long)tk * ldo + (long long)(kvh * rows + r) * DH + d] = __float2bfloat16_rn(o / total);
+        }
     }
 }
 
@@ -374,9 +445,11 @@ attention_decode_ring_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
 
 // Arguments as mu_attention_decode (bfloat16 only).  n_warps: how the block is built, by how many blocks there
 // are.  6: six groups of one warp, a block an SM (no more blocks than SMs: all pages of a sequence in flight at
-// once).  3: three groups of two warps that share each page, two blocks an SM (up to twice as many blocks as
-// SMs; head size 64).  2: two groups of two warps, three blocks an SM (more blocks than that).  Each group has
-// a ring of pages.  `status` is a device word that is set to 4 if a wait for a copy runs out.
+// once); 12 or 24: two or four such blocks share each (sequence, kv head) as a cluster (blocks on at most
+// half or a quarter of the SMs; head size 64).  3: three groups of two warps that share each page, two blocks
+// an SM (up to twice as many blocks as SMs; head size 64).  2: two groups of two warps, three blocks an SM
+// (more blocks than that).  Each group has a ring of pages.  `status` is a device word that is set to 4 if a
+// wait for a copy runs out.
 MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k_new, long long ldk,
                                      const void* v_new, long long ldv, void* out, long long ldo, void* kv,
                                      const int* block_table, int max_pages, int page_tokens,
@@ -397,11 +470,12 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
     cudaStream_t s = (cudaStream_t)stream;
     int rc = MU_ERR_UNSUPPORTED_SIZE;
     const int rows = n_heads / n_kv_heads;
-#define MU_TR(KD, NG, SUB)                                                                                     \
+#define MU_TR(KD, NG, SUB, CL)                                                                                 \
     do {                                                                                                       \
-        auto kernel = mu::attention_decode_ring_kernel<KD, NG, SUB, 2>;                                        \
+        auto kernel = mu::attention_decode_ring_kernel<KD, NG, SUB, 2, CL>;                                    \
         const size_t smem = (size_t)NG * 2 * 2 * mu::TD_PAGE * 16 * KD * sizeof(__nv_bfloat16) +               \
-                            (size_t)NG * SUB * rows * (16 * KD + 1) * sizeof(float);                           \
+                            (size_t)NG * SUB * rows * (16 * KD + 1) * sizeof(float) +                          \
+                            (size_t)(CL - 1) * rows * 16 * KD * sizeof(float);                                 \
         static bool raised = false;                                                                            \
         if (!raised) {                                                                                         \
             if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=       \
@@ -410,7 +484,7 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
             raised = true;                                                                                     \
         }                                                                                                      \
         if (smem > 200 * 1024) return MU_ERR_UNSUPPORTED_SIZE;                                                 \
-        rc = mu::launch_pdl(kernel, dim3((unsigned)blocks), dim3(NG * SUB * 32), smem, s, 1,                   \
+        rc = mu::launch_pdl(kernel, dim3((unsigned)blocks, CL), dim3(NG * SUB * 32), smem, s, CL,              \
             (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_new, ldk, (const __nv_bfloat16*)v_new, ldv,  \
             (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)kv, block_table, max_pages, tok_pos, tok_seq, n_heads,   \
             n_kv_heads, scale, window, status);                                                                \
@@ -419,14 +493,23 @@ MU_EXPORT int mu_attention_decode_tc(const void* q, long long ldq, const void* k
     // many blocks (two groups each, three blocks an SM) two warps share each page where the head is small
     // enough for the registers to allow it: more chains of work for the SM to switch between.  With few blocks
     // a warp per page is the shorter chain.  In between, three groups of two warps: a group walks over a
-    // third of the pages instead of half of them, and two blocks still share an SM.
+    // third of the pages instead of half of them, and two blocks still share an SM.  With very few blocks,
+    // two or four of the large ones share each (sequence, kv head) as a cluster (head size 64).
     const size_t six = (size_t)6 * 2 * 2 * mu::TD_PAGE * head_dim * sizeof(__nv_bfloat16) +
                        (size_t)6 * rows * (head_dim + 1) * sizeof(float);
     const bool wide = n_warps >= 6 && six <= 200 * 1024;
-    if (head_dim == 32) { if (wide) MU_TR(2, 6, 1); else MU_TR(2, 2, 2); }
-    else if (head_dim == 64) { if (wide) MU_TR(4, 6, 1); else if (n_warps >= 3) MU_TR(4, 3, 2); else MU_TR(4, 2, 2); }
-    else if (head_dim == 96) MU_TR(6, 2, 1);
-    else MU_TR(8, 2, 1);
+    const int shared_by = !wide || head_dim != 64 ? 1 : n_warps >= 24 ? 4 : n_warps >= 12 ? 2 : 1;
+    const bool fits = six + (size_t)(shared_by - 1) * rows * head_dim * sizeof(float) <= 200 * 1024;
+    if (head_dim == 32) { if (wide) MU_TR(2, 6, 1, 1); else MU_TR(2, 2, 2, 1); }
+    else if (head_dim == 64) {
+        if (wide && shared_by == 4 && fits) MU_TR(4, 6, 1, 4);
+        else if (wide && shared_by == 2 && fits) MU_TR(4, 6, 1, 2);
+        else if (wide) MU_TR(4, 6, 1, 1);
+        else if (n_warps >= 3) MU_TR(4, 3, 2, 1);
+        else MU_TR(4, 2, 2, 1);
+    }
+    else if (head_dim == 96) MU_TR(6, 2, 1, 1);
+    else MU_TR(8, 2, 1, 1);
 #undef MU_TR
     return rc;
 }

@@ -607,17 +607,22 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
     given), attends page by page, merges in shared memory.  ``n_splits``: how
     many warps share a sequence's pages (its page count is a good choice; at most
     16 are used).  ``tok_seq`` None: token t is sequence t.  ``warps``: the shape of a
-    block (tensor-core kernel: 2, 3 or 6 groups of warps; CUDA-core kernel: an upper
-    bound on its warps); 0: chosen here."""
+    block (tensor-core kernel: 2, 3 or 6 groups of warps, 12 or 24 for six groups in
+    each of two or four blocks that share a sequence; CUDA-core kernel: an upper bound
+    on its warps); 0: chosen here."""
     _need_cuda(q, k_new, v_new, out, kv_pages, block_table, tok_pos, tok_seq)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     n_tokens = q.shape[0]
     if decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens, n_heads, n_kv_heads, head_dim):
         if not warps:         # no more blocks than SMs: large ones, all pages in flight at once; up to twice as
-                              # many: two an SM; more: small ones, three an SM (the large ones would run in waves)
+                              # many: two an SM; more: small ones, three an SM (the large ones would run in waves).
+                              # Very few: four or two large blocks share a sequence's pages as a cluster, while the
+                              # clusters fill two thirds or half of the SMs at most (they are placed within one
+                              # part of the chip each, so a fuller grid runs in waves)
             blocks, sms = n_tokens * n_kv_heads, sm_count(q.device)
-            warps = 6 if blocks <= sms else 3 if blocks <= 2 * sms else 2
+            warps = (24 if 6 * blocks <= sms else 12 if 4 * blocks <= sms else 6 if blocks <= sms
+                     else 3 if blocks <= 2 * sms else 2)
         _check(library().mu_attention_decode_tc(
             _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
             v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),

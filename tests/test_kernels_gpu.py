@@ -363,14 +363,14 @@ def test_single_token_attention_kernel(n_heads, n_kv_heads, head_dim, window, dt
     assert_close(out2.float().cpu().numpy(), want, dtype, "after the append")
 
 
-@pytest.mark.parametrize("warps", [2, 3, 6])
+@pytest.mark.parametrize("warps", [2, 3, 6, 12, 24])
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
     (5, 5, 64, 0), (16, 1, 64, 0), (12, 4, 32, 0), (9, 3, 64, 100), (6, 3, 32, 64), (22, 2, 64, 0), (34, 2, 32, 0),
     (4, 2, 128, 0), (6, 1, 96, 70), (3, 3, 128, 200)])
 def test_single_token_attention_on_tensor_cores(n_heads, n_kv_heads, head_dim, window, warps):
     """The tensor-core kernel of single-token steps (pages staged in shared
-    memory by bulk copies) at its three shapes of block (several pages per warp, more
-    pages than the ring holds), with grouped heads up to 16 per kv head and windows
+    memory by bulk copies) at its shapes of block, with and without blocks that share a
+    sequence as a cluster (several pages per warp, more pages than the ring holds), with grouped heads up to 16 per kv head and windows
     that start inside a page; one key far back is made to carry most of the weight
     of its head, so a misplaced column shows."""
     from math_utils_b200.csrc import ops

@@ -114,7 +114,8 @@ def wide(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-@pytest.mark.parametrize("members", [range(0, 24), range(24, 64), range(0, 64)], ids=["b24", "b40", "b64"])
+@pytest.mark.parametrize("members", [range(3, 4), range(38, 41), range(0, 24), range(24, 64), range(0, 64)],
+                         ids=["b1", "b3", "b24", "b40", "b64"])
 def test_wide_batches_step_by_step(wide, members, dtype):
     """Prompts in one step, then one token each through ``model.step``; logits of each prompt's last
     position and of every single-token step against the plain model; shorter requests end early; the
@@ -148,7 +149,8 @@ def test_wide_batches_step_by_step(wide, members, dtype):
         assert cache.slots.n_free == len(members) and cache.free_pages() == cache.n_pages
 
 
-@pytest.mark.parametrize("members", [range(0, 24), range(24, 64), range(0, 64)], ids=["b24", "b40", "b64"])
+@pytest.mark.parametrize("members", [range(3, 4), range(38, 41), range(0, 24), range(24, 64), range(0, 64)],
+                         ids=["b1", "b3", "b24", "b40", "b64"])
 def test_wide_batches_generate(wide, members):
     """The same batches through ``LLM.generate`` (graph replay, the host one step behind): greedy tokens
     against the plain model fed the same history, requests of unequal budgets, twice on one cache."""
@@ -165,12 +167,12 @@ def test_wide_batches_generate(wide, members):
         rows = plain_rows(i, len(p) - 1, p + g[:-1])
         tokens_near_plain(rows, g, f"request {i}")
     # a stop token ends some requests early: what they produced is a prefix of the free run
-    stop = {first[0][5], first[1][9]}
+    stop = {first[0][5]} | ({first[1][9]} if len(first) > 1 else set())
     cut = llm.generate(prompts, max_tokens=N_DECODE, stop_ids=sorted(stop))
     for g, f in zip(cut, first):
         n = next((k for k, t in enumerate(f) if t in stop), len(f))
         assert g == f[:n]
-    assert len(cut[0]) <= 5 and len(cut[1]) <= 9
+    assert len(cut[0]) <= 5 and (len(cut) == 1 or len(cut[1]) <= 9)
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])

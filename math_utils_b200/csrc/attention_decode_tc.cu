@@ -18,9 +18,10 @@
 //   * O = P V.  Values lie dimension-major in the page (attention.cu), so thread
 //     (g, t) loads for each tile of 8 dimensions the 16 consecutive positions
 //     [16 t, 16 t + 16) of dimension row 8 j + g: again one 32-byte run.
-// One block per (sequence, kv head); its warps share out the pages, fold
-// several pages into a running (max, sum, output) when there are more pages
-// than warps, and merge in shared memory in warp order.  The step's own key and
+// One block per (sequence, kv head), or with very few sequences a cluster of
+// two or four; its warps share out the pages, fold several pages into a
+// running (max, sum, output) when there are more pages than warps, and merge
+// in shared memory in warp order (the blocks of a cluster then in rank order).  The step's own key and
 // value are read from the step's projections and appended by the kernel, as in
 // attention_decode.cu.  Softmax in float32; probabilities rounded to bfloat16
 // for the second product, as in the prompt kernel.

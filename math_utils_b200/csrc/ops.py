@@ -599,6 +599,22 @@ def decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens: int, n_heads: int, n_kv
     return True
 
 
+def decode_block_shape(blocks: int, sms: int) -> int:
+    """The shape of the tensor-core single-token attention kernel's blocks for this many (sequence, kv head)
+    pairs, as the code ``mu_attention_decode_tc`` takes.  No more blocks than SMs: large ones (6), all pages of
+    a sequence in flight at once; up to twice as many: three groups of two warps, two blocks an SM (3); more:
+    small ones, three an SM (2; the large ones would run in waves).  Very few: four (24) or two (12) large
+    blocks share a sequence's pages as a cluster, while the clusters fill two thirds or half of the SMs at
+    most (a cluster is placed within one part of the chip, so a fuller grid of clusters runs in waves)."""
+    if 6 * blocks <= sms:
+        return 24
+    if 4 * blocks <= sms:
+        return 12
+    if blocks <= sms:
+        return 6
+    return 3 if blocks <= 2 * sms else 2
+
+
 def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
                      out: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, page_tokens: int,
                      tok_pos, tok_seq, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
@@ -615,14 +631,8 @@ def attention_decode(q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Opti
         _i32(t, name)
     n_tokens = q.shape[0]
     if decode_tc_ok(q, k_new, v_new, kv_pages, page_tokens, n_heads, n_kv_heads, head_dim):
-        if not warps:         # no more blocks than SMs: large ones, all pages in flight at once; up to twice as
-                              # many: two an SM; more: small ones, three an SM (the large ones would run in waves).
-                              # Very few: four or two large blocks share a sequence's pages as a cluster, while the
-                              # clusters fill two thirds or half of the SMs at most (they are placed within one
-                              # part of the chip each, so a fuller grid runs in waves)
-            blocks, sms = n_tokens * n_kv_heads, sm_count(q.device)
-            warps = (24 if 6 * blocks <= sms else 12 if 4 * blocks <= sms else 6 if blocks <= sms
-                     else 3 if blocks <= 2 * sms else 2)
+        if not warps:
+            warps = decode_block_shape(n_tokens * n_kv_heads, sm_count(q.device))
         _check(library().mu_attention_decode_tc(
             _ptr(q), q.stride(0), _ptr(k_new), k_new.stride(0) if k_new is not None else 0, _ptr(v_new),
             v_new.stride(0) if v_new is not None else 0, _ptr(out), out.stride(0), _ptr(kv_pages),
